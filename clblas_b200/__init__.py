@@ -1,0 +1,205 @@
+"""clblas_b200 -- host-side mirror of the clBLAS level-3 entry points over the B200 C-ABI library.
+
+The functions keep the reference's names, argument order and status-code convention
+(src/clBLAS.h:7382-7405 clblasSgemm, :7463-7486 clblasDgemm, :7988-8008 clblasStrsm,
+:8063-8083 clblasDtrsm): they return a ``clblasStatus`` integer and raise nothing on a bad
+argument.  Buffers are CUDA device pointers (a ``torch.Tensor`` on a CUDA device or a raw
+integer address); queues are CUDA streams; events are CUDA events.
+
+All work is done by ``lib/libclblas_b200.so`` (hand-written sm_100a kernels behind
+``include/clblas_b200.h``).  There is no CPU path: importing this package without the built
+library raises ``ImportError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libclblas_b200.so")
+
+# enums (src/clBLAS.h:78-113)
+clblasRowMajor, clblasColumnMajor = 0, 1
+clblasNoTrans, clblasTrans, clblasConjTrans = 0, 1, 2
+clblasUpper, clblasLower = 0, 1
+clblasUnit, clblasNonUnit = 0, 1
+clblasLeft, clblasRight = 0, 1
+
+# status codes (src/clBLAS.h:123-155)
+STATUS = {
+    "clblasSuccess": 0, "clblasInvalidValue": -30, "clblasInvalidCommandQueue": -36,
+    "clblasInvalidContext": -34, "clblasInvalidMemObject": -38, "clblasInvalidDevice": -33,
+    "clblasInvalidEventWaitList": -57, "clblasOutOfResources": -5, "clblasOutOfHostMemory": -6,
+    "clblasInvalidOperation": -59, "clblasCompilerNotAvailable": -3, "clblasBuildProgramFailure": -11,
+    "clblasNotImplemented": -1024, "clblasNotInitialized": -1023, "clblasInvalidMatA": -1022,
+    "clblasInvalidMatB": -1021, "clblasInvalidMatC": -1020, "clblasInvalidVecX": -1019,
+    "clblasInvalidVecY": -1018, "clblasInvalidDim": -1017, "clblasInvalidLeadDimA": -1016,
+    "clblasInvalidLeadDimB": -1015, "clblasInvalidLeadDimC": -1014, "clblasInvalidIncX": -1013,
+    "clblasInvalidIncY": -1012, "clblasInsufficientMemMatA": -1011, "clblasInsufficientMemMatB": -1010,
+    "clblasInsufficientMemMatC": -1009, "clblasInsufficientMemVecX": -1008, "clblasInsufficientMemVecY": -1007,
+}
+globals().update(STATUS)
+STATUS_NAME = {v: k for k, v in STATUS.items()}
+
+
+class ClblasError(RuntimeError):
+    def __init__(self, status: int, what: str = ""):
+        self.status = status
+        super().__init__(f"{what}: {STATUS_NAME.get(status, status)} ({status})")
+
+
+def check(status: int, what: str = "clblas call") -> None:
+    """Raise ClblasError unless status is clblasSuccess (convenience; the entry points never raise)."""
+    if status != 0:
+        raise ClblasError(status, what)
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m clblas_b200.build` "
+            "(there is no CPU or PyTorch fallback for these routines)")
+    lib = ctypes.CDLL(LIB_PATH)
+    sz, u, i, vp = ctypes.c_size_t, ctypes.c_uint, ctypes.c_int, ctypes.c_void_p
+    pvp = ctypes.POINTER(ctypes.c_void_p)
+    for name, ft in (("clblasSgemm", ctypes.c_float), ("clblasDgemm", ctypes.c_double)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, sz, sz, sz, ft, vp, sz, sz, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
+        f.restype = i
+    for name, ft in (("clblasStrsm", ctypes.c_float), ("clblasDtrsm", ctypes.c_double)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, u, pvp, u, pvp, pvp]
+        f.restype = i
+    lib.clblasSetup.argtypes = []
+    lib.clblasSetup.restype = i
+    lib.clblasTeardown.argtypes = []
+    lib.clblasTeardown.restype = None
+    lib.clblasGetVersion.argtypes = [ctypes.POINTER(u)] * 3
+    lib.clblasGetVersion.restype = i
+    lib.clblasB200PlanShards.argtypes = [sz, u, sz, ctypes.POINTER(sz)]
+    lib.clblasB200PlanShards.restype = i
+    lib.clblasB200LaunchCount.argtypes = []
+    lib.clblasB200LaunchCount.restype = ctypes.c_ulonglong
+    lib.clblasB200LastGemmKernel.argtypes = []
+    lib.clblasB200LastGemmKernel.restype = ctypes.c_char_p
+    lib.clblasB200SetGemmPath.argtypes = [i]
+    lib.clblasB200SetGemmPath.restype = i
+    return lib
+
+
+lib = _load()
+
+EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "clblasDgemm", "clblasStrsm",
+           "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
+           "clblasB200SetGemmPath"]
+
+
+def _ptr(x) -> Optional[int]:
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()      # torch.Tensor
+
+
+def _handle(x) -> Optional[int]:
+    """CUDA stream / event handle from a torch object or a raw integer."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    for attr in ("cuda_stream", "cuda_event"):
+        if hasattr(x, attr):
+            return getattr(x, attr)
+    raise TypeError(f"not a CUDA stream or event: {x!r}")
+
+
+def _handle_array(items: Optional[Sequence], default_current_stream: bool = False):
+    if items is None:
+        if not default_current_stream:
+            return 0, None
+        import torch
+        items = [torch.cuda.current_stream()]
+    arr = (ctypes.c_void_p * max(len(items), 1))()
+    for k, it in enumerate(items):
+        arr[k] = _handle(it)
+    return len(items), arr
+
+
+def _queues_events(queues, wait, events):
+    nq, q = _handle_array(queues, default_current_stream=True)
+    nw, w = _handle_array(wait)
+    _, e = _handle_array(events)
+    return nq, q, nw, w, e
+
+
+def clblasSetup() -> int:
+    return lib.clblasSetup()
+
+
+def clblasTeardown() -> None:
+    lib.clblasTeardown()
+
+
+def clblasGetVersion():
+    a, b, c = ctypes.c_uint(), ctypes.c_uint(), ctypes.c_uint()
+    st = lib.clblasGetVersion(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+    return st, (a.value, b.value, c.value)
+
+
+def _gemm(fn, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+          queues, wait, events):
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return fn(order, transA, transB, M, N, K, alpha, _ptr(A), offA, lda, _ptr(B), offB, ldb, beta,
+              _ptr(C), offC, ldc, nq, q, nw, w, e)
+
+
+def clblasSgemm(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues=None, wait=None, events=None) -> int:
+    """float GEMM; `queues` defaults to torch's current stream, like passing one command queue."""
+    return _gemm(lib.clblasSgemm, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta,
+                 C, offC, ldc, queues, wait, events)
+
+
+def clblasDgemm(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues=None, wait=None, events=None) -> int:
+    return _gemm(lib.clblasDgemm, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta,
+                 C, offC, ldc, queues, wait, events)
+
+
+def _trsm(fn, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, queues, wait, events):
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return fn(order, side, uplo, transA, diag, M, N, alpha, _ptr(A), offA, lda, _ptr(B), offB, ldb,
+              nq, q, nw, w, e)
+
+
+def clblasStrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                queues=None, wait=None, events=None) -> int:
+    return _trsm(lib.clblasStrsm, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                 queues, wait, events)
+
+
+def clblasDtrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                queues=None, wait=None, events=None) -> int:
+    return _trsm(lib.clblasDtrsm, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                 queues, wait, events)
+
+
+def plan_shards(total: int, parts: int, align: int = 128):
+    """Column-block boundaries for `parts` devices (clblasB200PlanShards)."""
+    out = (ctypes.c_size_t * (parts + 1))()
+    check(lib.clblasB200PlanShards(total, parts, align, out), "clblasB200PlanShards")
+    return list(out)
+
+
+def launch_count() -> int:
+    return int(lib.clblasB200LaunchCount())
+
+
+def last_gemm_kernel() -> str:
+    return lib.clblasB200LastGemmKernel().decode()
+
+
+def set_gemm_path(path: int) -> int:
+    return lib.clblasB200SetGemmPath(path)

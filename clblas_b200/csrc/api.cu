@@ -1,0 +1,312 @@
+// Host front end of the C ABI declared in include/clblas_b200.h: argument checks with the
+// reference's status codes and check order, row-major -> column-major normalisation, stream
+// and event ordering, then the CUDA dispatchers.  No computation happens on the host.
+#include "common.h"
+
+#include <atomic>
+#include <mutex>
+
+namespace cb200 {
+
+namespace {
+
+std::atomic<unsigned long long> g_launches{0};
+std::atomic<int> g_forced_path{0};
+std::atomic<int> g_initialized{0};
+thread_local const char* t_last_kernel = "none";
+
+// cuMemGetAddressRange through the runtime's driver entry point query: the extent of the CUDA
+// allocation that holds a pointer stands in for clGetMemObjectInfo(CL_MEM_SIZE) of the
+// reference's checkMatrixSizes (src/library/blas/generic/common.c:651-681).
+typedef int (*MemGetAddressRangeFn)(unsigned long long*, size_t*, unsigned long long);
+
+MemGetAddressRangeFn address_range_fn()
+{
+    static MemGetAddressRangeFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<MemGetAddressRangeFn>(f);
+    }();
+    return fn;
+}
+
+// Bytes available from `ptr` to the end of its allocation; false when the pointer is not a
+// device allocation known to the driver.
+bool bytes_after(const void* ptr, size_t* avail)
+{
+    MemGetAddressRangeFn fn = address_range_fn();
+    if (!fn) return false;
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (fn(&base, &size, (unsigned long long)(uintptr_t)ptr) != 0) {
+        cudaGetLastError();
+        return false;
+    }
+    *avail = size - (size_t)((unsigned long long)(uintptr_t)ptr - base);
+    return true;
+}
+
+enum ErrSet { SET_A = 0, SET_B = 1, SET_C = 2 };
+
+clblasStatus pick(ErrSet e, clblasStatus a, clblasStatus b, clblasStatus c)
+{
+    return e == SET_A ? a : (e == SET_B ? b : c);
+}
+
+// checkMatrixSizes of the reference (src/library/blas/generic/common.c:585-686) for a non-packed
+// rows x cols matrix op(X).
+clblasStatus check_matrix_sizes(size_t tsize, clblasOrder order, clblasTranspose trans, size_t rows, size_t cols,
+                                const void* buf, size_t off, size_t ld, ErrSet e)
+{
+    if (rows == 0 || cols == 0) return clblasInvalidDim;
+    const bool tra = (order == clblasRowMajor && trans != clblasNoTrans) ||
+                     (order == clblasColumnMajor && trans == clblasNoTrans);
+    size_t matr;
+    if (tra) {
+        if (ld < rows) return pick(e, clblasInvalidLeadDimA, clblasInvalidLeadDimB, clblasInvalidLeadDimC);
+        matr = ((cols - 1) * ld + rows) * tsize;
+    } else {
+        if (ld < cols) return pick(e, clblasInvalidLeadDimA, clblasInvalidLeadDimB, clblasInvalidLeadDimC);
+        matr = ((rows - 1) * ld + cols) * tsize;
+    }
+    size_t avail = 0;
+    if (!bytes_after(buf, &avail)) return pick(e, clblasInvalidMatA, clblasInvalidMatB, clblasInvalidMatC);
+    const size_t offb = off * tsize;
+    if (offb + matr > avail || offb + matr < offb)
+        return pick(e, clblasInsufficientMemMatA, clblasInsufficientMemMatB, clblasInsufficientMemMatC);
+    return clblasSuccess;
+}
+
+// checkQueues / checkEventWaitList (src/library/blas/functor/include/functor_utils.h:22-60).  A
+// NULL cudaStream_t inside the array is the legacy default stream and therefore legal here.
+clblasStatus check_queues(unsigned n, clblasQueue* q)
+{
+    if (n == 0 || q == nullptr) return clblasInvalidCommandQueue;
+    return clblasSuccess;
+}
+
+clblasStatus check_events(unsigned n, const clblasEvent* ev)
+{
+    if (n > 0 && ev == nullptr) return clblasInvalidEventWaitList;
+    for (unsigned i = 0; i < n; i++)
+        if (ev[i] == nullptr) return clblasInvalidEventWaitList;
+    return clblasSuccess;
+}
+
+clblasStatus from_cuda(cudaError_t e)
+{
+    switch (e) {
+        case cudaSuccess: return clblasSuccess;
+        case cudaErrorMemoryAllocation: return clblasOutOfResources;
+        case cudaErrorInvalidValue: return clblasInvalidValue;
+        case cudaErrorInvalidResourceHandle: return clblasInvalidCommandQueue;
+        case cudaErrorNotSupported: return clblasNotImplemented;
+        default: return clblasInvalidOperation;
+    }
+}
+
+clblasStatus wait_all(cudaStream_t s, unsigned n, const clblasEvent* ev)
+{
+    for (unsigned i = 0; i < n; i++) {
+        cudaError_t e = cudaStreamWaitEvent(s, reinterpret_cast<cudaEvent_t>(ev[i]), 0);
+        if (e != cudaSuccess) { cudaGetLastError(); return clblasInvalidEventWaitList; }
+    }
+    return clblasSuccess;
+}
+
+clblasStatus record_out(cudaStream_t s, clblasEvent* events)
+{
+    if (events != nullptr && events[0] != nullptr) {
+        cudaError_t e = cudaEventRecord(reinterpret_cast<cudaEvent_t>(events[0]), s);
+        if (e != cudaSuccess) { cudaGetLastError(); return clblasInvalidValue; }
+    }
+    return clblasSuccess;
+}
+
+template <typename T>
+clblasStatus gemm_entry(clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+                        size_t M, size_t N, size_t K, T alpha,
+                        const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb,
+                        T beta, void* C, size_t offC, size_t ldc,
+                        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    // xgemm.cc:685-706: memory objects first, then (K != 0) A and B sizes, then C sizes.
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)transA > 2u || (unsigned)transB > 2u) return clblasInvalidValue;
+    clblasStatus st;
+    if (K != 0) {
+        if ((st = check_matrix_sizes(sizeof(T), order, transA, M, K, A, offA, lda, SET_A)) != clblasSuccess) return st;
+        if ((st = check_matrix_sizes(sizeof(T), order, transB, K, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    }
+    if ((st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, M, N, C, offC, ldc, SET_C)) != clblasSuccess) return st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+
+    GemmProblem<T> p;
+    p.alpha = alpha; p.beta = beta; p.K = K;
+    p.C = static_cast<T*>(C) + offC; p.ldc = ldc;
+    const bool ta = transA != clblasNoTrans, tb = transB != clblasNoTrans;   // ConjTrans == Trans for reals
+    if (order == clblasColumnMajor) {
+        p.ta = ta; p.tb = tb; p.M = M; p.N = N;
+        p.A = static_cast<const T*>(A) + offA; p.lda = lda;
+        p.B = static_cast<const T*>(B) + offB; p.ldb = ldb;
+    } else {
+        // Row-major C (MxN) is column-major C^T (NxM) = op(B)^T * op(A)^T: swap the operands, their
+        // transposition flags and M with N (the reference's force_gemm_column_major, xgemm.cc:40-61).
+        p.ta = tb; p.tb = ta; p.M = N; p.N = M;
+        p.A = static_cast<const T*>(B) + offB; p.lda = ldb;
+        p.B = static_cast<const T*>(A) + offA; p.ldb = lda;
+    }
+    cudaError_t e = gemm_colmajor<T>(p, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
+template <typename T>
+clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                        size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda,
+                        void* B, size_t offB, size_t ldb,
+                        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    // xtrsm.cc:1623-1624 then functor_xtrsm.cc:57-75.
+    clblasStatus st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u || (unsigned)transA > 2u || (unsigned)diag > 1u) return clblasInvalidValue;
+    const size_t msize = (side == clblasLeft) ? M : N;
+    if ((st = check_matrix_sizes(sizeof(T), order, transA, msize, msize, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, M, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        // A row-major matrix is its transpose in column-major: B^T gets solved from the other side
+        // with the other triangle (the reference's force_trsm_column_major, xtrsm.cc:54-64).
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = trsm_colmajor<T>(right, lower, transA != clblasNoTrans, diag == clblasUnit, M, N, alpha,
+                                     static_cast<const T*>(A) + offA, lda, static_cast<T*>(B) + offB, ldb, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
+}  // namespace
+
+void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+void set_last_kernel(const char* name) { t_last_kernel = name; }
+int forced_gemm_path() { return g_forced_path.load(std::memory_order_relaxed); }
+
+void* get_tensor_map_encoder()
+{
+    static void* fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return f;
+    }();
+    return fn;
+}
+
+}  // namespace cb200
+
+using namespace cb200;
+
+extern "C" {
+
+clblasStatus clblasGetVersion(unsigned* major, unsigned* minor, unsigned* patch)
+{
+    if (!major || !minor || !patch) return clblasInvalidValue;
+    *major = 2; *minor = 12; *patch = 0;
+    return clblasSuccess;
+}
+
+clblasStatus clblasSetup(void)
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { cudaGetLastError(); return clblasInvalidDevice; }
+    g_initialized.store(1);
+    return clblasSuccess;
+}
+
+void clblasTeardown(void)
+{
+    trsm_release_workspaces();
+    g_initialized.store(0);
+}
+
+clblasStatus clblasSgemm(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                         float alpha, const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb,
+                         float beta, clblasMem C, size_t offC, size_t ldc, unsigned nq, clblasQueue* queues,
+                         unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return gemm_entry<float>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                             nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasDgemm(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                         double alpha, const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb,
+                         double beta, clblasMem C, size_t offC, size_t ldc, unsigned nq, clblasQueue* queues,
+                         unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return gemm_entry<double>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                              nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasStrsm(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, float alpha, const clblasMem A, size_t offA, size_t lda,
+                         clblasMem B, size_t offB, size_t ldb, unsigned nq, clblasQueue* queues,
+                         unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return trsm_entry<float>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                             nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasDtrsm(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, double alpha, const clblasMem A, size_t offA, size_t lda,
+                         clblasMem B, size_t offB, size_t ldb, unsigned nq, clblasQueue* queues,
+                         unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return trsm_entry<double>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                              nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasB200PlanShards(size_t total, unsigned parts, size_t align, size_t* bounds)
+{
+    if (parts == 0 || bounds == nullptr) return clblasInvalidValue;
+    if (align == 0) align = 1;
+    // Equal shares rounded up to the alignment; trailing devices may get less (or nothing).
+    const size_t units = (total + align - 1) / align;
+    const size_t per = (units + parts - 1) / parts;
+    bounds[0] = 0;
+    for (unsigned i = 1; i <= parts; i++) {
+        size_t b = (size_t)i * per * align;
+        bounds[i] = b < total ? b : total;
+    }
+    bounds[parts] = total;
+    return clblasSuccess;
+}
+
+unsigned long long clblasB200LaunchCount(void) { return g_launches.load(); }
+const char* clblasB200LastGemmKernel(void) { return t_last_kernel; }
+int clblasB200SetGemmPath(int path) { return g_forced_path.exchange(path); }
+
+}  // extern "C"

@@ -1,0 +1,62 @@
+// Internal declarations shared by the host layer and the kernel translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/clblas_b200.h"
+
+namespace cb200 {
+
+// Column-major GEMM problem after the front end has normalised order/ConjTrans
+// (row-major calls arrive here with operands swapped, as in the reference's
+// force_gemm_column_major, src/library/blas/xgemm.cc:40-61).
+// ta / tb: op(X) = X^T when true.  Pointers already include the element offsets.
+template <typename T>
+struct GemmProblem {
+    bool ta, tb;
+    size_t M, N, K;
+    T alpha;
+    const T* A; size_t lda;
+    const T* B; size_t ldb;
+    T beta;
+    T* C; size_t ldc;
+};
+
+// Kernel families (reported by clblasB200LastGemmKernel).
+enum GemmPath { PATH_AUTO = 0, PATH_SIMT_LDG = 1 };
+
+void count_launch(unsigned n = 1);
+void set_last_kernel(const char* name);
+int forced_gemm_path();
+
+// Scales C by beta (beta == 0 stores zeros without reading C).  Used for K == 0 and alpha == 0.
+template <typename T>
+cudaError_t launch_scale(size_t M, size_t N, T beta, T* C, size_t ldc, cudaStream_t s);
+
+// Alignment-free path: predicated, coalesced LDG -> shared -> register-blocked FMA.
+template <typename T>
+cudaError_t launch_gemm_simt(const GemmProblem<T>& p, cudaStream_t s);
+
+// TMA-staged paths (need 16-byte aligned bases and leading dimensions); return
+// cudaErrorNotSupported when the problem does not meet their requirements.
+cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s);
+cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s);
+
+// Dispatcher keyed on precision, transposes, shape and alignment.
+template <typename T>
+cudaError_t gemm_colmajor(const GemmProblem<T>& p, cudaStream_t s);
+
+// Blocked triangular solve on a column-major problem (B overwritten by X).
+template <typename T>
+cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
+                          const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
+void trsm_release_workspaces();
+
+// cuTensorMapEncodeTiled obtained through the runtime's driver entry point query (no libcuda link).
+void* get_tensor_map_encoder();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace cb200

@@ -1,0 +1,247 @@
+// Blocked triangular solve: op(A) X = alpha B (Left) or X op(A) = alpha B (Right), X over B.
+//
+// Same two ingredients as the reference's DTRSM (src/library/blas/xtrsm.cc:1136-1507): explicit
+// inverses of the NB x NB diagonal blocks of A, and GEMM for everything else.  Differences:
+//  * one kernel launch inverts all diagonal blocks (the reference needs a diag_dtrtri launch plus
+//    six triple_dgemm_update launches, xtrsm.cc:790-1134);
+//  * the substitution is recursive (solve first half, one large-K GEMM update of the second half,
+//    solve second half) instead of a rank-NB update per block step, so the updates are large GEMMs;
+//  * X is produced in place: only an NB-wide panel is staged, not an M x N copy of B
+//    (the reference allocates X = M x N and copies it back, xtrsm.cc:1183-1192, :1480-1497);
+//  * the same code serves float (the reference's STRSM goes through its legacy generated kernels,
+//    src/library/blas/functor/functor_xtrsm.cc:130-152) and double.
+// Only the referenced triangle of A is ever loaded; a unit diagonal is never loaded.
+#include "common.h"
+
+#include <algorithm>
+
+namespace cb200 {
+
+namespace {
+
+constexpr int NB = 128;           // order of the inverted diagonal blocks
+constexpr int TRTRI_THREADS = 512;
+
+// Inverts every NB x NB diagonal block of the triangular matrix A (order n) into
+// inv[b] (dense NB x NB, column-major, ld = NB, zeros outside the triangle).  Rows/columns of the
+// last block beyond n are completed with the identity.
+//
+// The block is held in shared memory as a lower-triangular L (an upper-triangular block is loaded
+// transposed and the result stored transposed).  X = L^-1 lives in registers, 32 entries per
+// thread, and is computed by right-looking forward substitution on the identity:
+//   for k: X[k,:] /= L[k,k];  X[i,:] -= L[i,k] * X[k,:]  for all i > k,
+// one barrier per k; row k travels through a double-buffered shared row.
+template <typename T>
+__global__ void __launch_bounds__(TRTRI_THREADS)
+trtri_diag_kernel(const T* __restrict__ A, size_t lda, size_t n, bool lower, bool unit, T* __restrict__ inv)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* Ls = reinterpret_cast<T*>(smem_raw);                 // Ls[k*NB + i] = L[i][k]
+    T* rowbuf = Ls + NB * NB;                               // 2 x NB
+
+    const size_t b = blockIdx.x;
+    const size_t r0 = b * NB;
+    const int nv = (n - r0 < (size_t)NB) ? (int)(n - r0) : NB;   // valid order of this block
+    const T* Ab = A + r0 + r0 * lda;
+    const int t = threadIdx.x;
+
+    for (int e = t; e < NB * NB; e += TRTRI_THREADS) {
+        const int i = e % NB, k = e / NB;                   // L[i][k], i >= k is the triangle
+        T v = T(0);
+        if (i == k) {
+            v = (i < nv && !unit) ? Ab[(size_t)i + (size_t)i * lda] : T(1);
+        } else if (i > k && i < nv) {
+            v = lower ? Ab[(size_t)i + (size_t)k * lda] : Ab[(size_t)k + (size_t)i * lda];
+        }
+        Ls[k * NB + i] = v;
+    }
+
+    // thread (tr, tc) owns X[i][j], i = tr + 16*ii (ii < 8), j = tc + 32*jj (jj < 4)
+    const int tc = t % 32, tr = t / 32;
+    T x[8][4];
+#pragma unroll
+    for (int ii = 0; ii < 8; ii++)
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) x[ii][jj] = (tr + 16 * ii == tc + 32 * jj) ? T(1) : T(0);
+    __syncthreads();
+
+    for (int k = 0; k < NB; k++) {
+        T* rb = rowbuf + (k & 1) * NB;
+        if (tr == (k & 15)) {
+            const T d = Ls[k * NB + k];
+#pragma unroll
+            for (int ii = 0; ii < 8; ii++) {
+                if (ii == (k >> 4)) {
+#pragma unroll
+                    for (int jj = 0; jj < 4; jj++) {
+                        x[ii][jj] = x[ii][jj] / d;
+                        rb[tc + 32 * jj] = x[ii][jj];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        T xr[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) xr[jj] = rb[tc + 32 * jj];
+#pragma unroll
+        for (int ii = 0; ii < 8; ii++) {
+            const int i = tr + 16 * ii;
+            if (i > k) {
+                const T l = Ls[k * NB + i];
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) x[ii][jj] = fma(-l, xr[jj], x[ii][jj]);
+            }
+        }
+    }
+
+    T* out = inv + b * (size_t)(NB * NB);
+#pragma unroll
+    for (int ii = 0; ii < 8; ii++)
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+            const int i = tr + 16 * ii, j = tc + 32 * jj;
+            if (lower) out[i + j * NB] = x[ii][jj]; else out[j + i * NB] = x[ii][jj];
+        }
+}
+
+template <typename T>
+struct TrsmCtx {
+    bool right, lower, trans, eff_lower;
+    size_t M, N, n;              // n = order of A
+    const T* A; size_t lda;
+    T* B; size_t ldb;
+    T* inv;                      // NB*NB per diagonal block
+    T* tmp;                      // staging panel for one leaf
+    cudaStream_t s;
+};
+
+template <typename T>
+cudaError_t gemm_call(bool ta, bool tb, size_t M, size_t N, size_t K, T alpha, const T* A, size_t lda,
+                      const T* B, size_t ldb, T beta, T* C, size_t ldc, cudaStream_t s)
+{
+    GemmProblem<T> p;
+    p.ta = ta; p.tb = tb; p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.A = A; p.lda = lda;
+    p.B = B; p.ldb = ldb; p.beta = beta; p.C = C; p.ldc = ldc;
+    return gemm_colmajor<T>(p, s);
+}
+
+// X_b = alpha * op(inv_b) * B_b (Left) or alpha * B_b * op(inv_b) (Right) for diagonal block b.
+template <typename T>
+cudaError_t solve_leaf(const TrsmCtx<T>& c, size_t b, T alpha)
+{
+    const size_t r = b * NB, nv = std::min<size_t>(NB, c.n - r);
+    const T* invb = c.inv + b * (size_t)(NB * NB);
+    cudaError_t e;
+    if (!c.right) {
+        T* Bb = c.B + r;
+        e = gemm_call<T>(c.trans, false, nv, c.N, nv, alpha, invb, NB, Bb, c.ldb, T(0), c.tmp, nv, c.s);
+        if (e != cudaSuccess) return e;
+        return cudaMemcpy2DAsync(Bb, c.ldb * sizeof(T), c.tmp, nv * sizeof(T), nv * sizeof(T), c.N,
+                                 cudaMemcpyDeviceToDevice, c.s);
+    }
+    T* Bb = c.B + r * c.ldb;
+    e = gemm_call<T>(false, c.trans, c.M, nv, nv, alpha, Bb, c.ldb, invb, NB, T(0), c.tmp, c.M, c.s);
+    if (e != cudaSuccess) return e;
+    return cudaMemcpy2DAsync(Bb, c.ldb * sizeof(T), c.tmp, c.M * sizeof(T), c.M * sizeof(T), nv,
+                             cudaMemcpyDeviceToDevice, c.s);
+}
+
+// Solves for the diagonal blocks [b0, b1) of the system; the right-hand side has already been
+// updated with every block outside the range that precedes it in substitution order.
+template <typename T>
+cudaError_t solve_range(const TrsmCtx<T>& c, size_t b0, size_t b1, T alpha)
+{
+    if (b1 - b0 == 1) return solve_leaf(c, b0, alpha);
+    const size_t mid = b0 + (b1 - b0 + 1) / 2;
+    const size_t r0 = b0 * NB, r1 = mid * NB, r2 = std::min<size_t>(b1 * NB, c.n);
+    const size_t n1 = r1 - r0, n2 = r2 - r1;        // orders of the first / second half
+    cudaError_t e;
+    // Which half is solved first: the one op(A) couples only to itself.
+    const bool first_half_first = (c.eff_lower != c.right);
+    if (first_half_first) {
+        if ((e = solve_range(c, b0, mid, alpha)) != cudaSuccess) return e;
+        if (!c.right) {
+            // B2 = alpha*B2 - op(A)[2,1] * X1 ; op(A)[2,1] is A[2,1] or A[1,2]^T
+            const T* A21 = c.trans ? c.A + r0 + r1 * c.lda : c.A + r1 + r0 * c.lda;
+            e = gemm_call<T>(c.trans, false, n2, c.N, n1, T(-1), A21, c.lda, c.B + r0, c.ldb, alpha, c.B + r1, c.ldb, c.s);
+        } else {
+            // X op(A) = alpha B with op(A) upper: B2 = alpha*B2 - X1 * op(A)[1,2]
+            const T* A12 = c.trans ? c.A + r1 + r0 * c.lda : c.A + r0 + r1 * c.lda;
+            e = gemm_call<T>(false, c.trans, c.M, n2, n1, T(-1), c.B + r0 * c.ldb, c.ldb, A12, c.lda, alpha,
+                             c.B + r1 * c.ldb, c.ldb, c.s);
+        }
+        if (e != cudaSuccess) return e;
+        return solve_range(c, mid, b1, T(1));
+    }
+    if ((e = solve_range(c, mid, b1, alpha)) != cudaSuccess) return e;
+    if (!c.right) {
+        // op(A) upper: B1 = alpha*B1 - op(A)[1,2] * X2
+        const T* A12 = c.trans ? c.A + r1 + r0 * c.lda : c.A + r0 + r1 * c.lda;
+        e = gemm_call<T>(c.trans, false, n1, c.N, n2, T(-1), A12, c.lda, c.B + r1, c.ldb, alpha, c.B + r0, c.ldb, c.s);
+    } else {
+        // X op(A) = alpha B with op(A) lower: B1 = alpha*B1 - X2 * op(A)[2,1]
+        const T* A21 = c.trans ? c.A + r0 + r1 * c.lda : c.A + r1 + r0 * c.lda;
+        e = gemm_call<T>(false, c.trans, c.M, n1, n2, T(-1), c.B + r1 * c.ldb, c.ldb, A21, c.lda, alpha,
+                         c.B + r0 * c.ldb, c.ldb, c.s);
+    }
+    if (e != cudaSuccess) return e;
+    return solve_range(c, b0, mid, T(1));
+}
+
+}  // namespace
+
+template <typename T>
+cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
+                          const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s)
+{
+    if (M == 0 || N == 0) return cudaSuccess;
+    if (alpha == T(0)) return launch_scale<T>(M, N, T(0), B, ldb, s);   // BLAS: B <- 0, A not referenced
+
+    TrsmCtx<T> c;
+    c.right = right; c.lower = lower; c.trans = trans; c.eff_lower = (lower != trans);
+    c.M = M; c.N = N; c.n = right ? N : M; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.s = s;
+    const size_t nblk = (c.n + NB - 1) / NB;
+    const size_t inv_elems = nblk * (size_t)(NB * NB);
+    const size_t tmp_elems = (size_t)NB * (right ? M : N);
+
+    T* ws = nullptr;
+    cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&ws), (inv_elems + tmp_elems) * sizeof(T), s);
+    if (e != cudaSuccess) return e;
+    c.inv = ws;
+    c.tmp = ws + inv_elems;
+
+    const size_t smem = (size_t)(NB * NB + 2 * NB) * sizeof(T);
+    // The opt-in to more than 48 KB of dynamic shared memory is a per-device function attribute.
+    static bool attr_done[2][64] = {};
+    const int ti = sizeof(T) == 8;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[ti][dev]) {
+        e = cudaFuncSetAttribute(trtri_diag_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { cudaFreeAsync(ws, s); return e; }
+        if (dev >= 0 && dev < 64) attr_done[ti][dev] = true;
+    }
+    trtri_diag_kernel<T><<<(unsigned)nblk, TRTRI_THREADS, smem, s>>>(A, lda, c.n, lower, unit, c.inv);
+    count_launch();
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = solve_range<T>(c, 0, nblk, alpha);
+    cudaError_t e2 = cudaFreeAsync(ws, s);
+    return e != cudaSuccess ? e : e2;
+}
+
+void trsm_release_workspaces()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return; }
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) cudaMemPoolTrimTo(pool, 0);
+    cudaGetLastError();
+}
+
+template cudaError_t trsm_colmajor<float>(bool, bool, bool, bool, size_t, size_t, float, const float*, size_t,
+                                          float*, size_t, cudaStream_t);
+template cudaError_t trsm_colmajor<double>(bool, bool, bool, bool, size_t, size_t, double, const double*, size_t,
+                                           double*, size_t, cudaStream_t);
+
+}  // namespace cb200

@@ -1,0 +1,162 @@
+/*
+ * clblas_b200.h -- C ABI of the B200 (sm_100a) level-3 hot path behind the clBLAS call shape.
+ *
+ * Every entry point below keeps the argument list of the clBLAS function it replaces
+ * (reference header src/clBLAS.h).  The OpenCL handle types are mapped one-to-one:
+ *
+ *     cl_mem            ->  clblasMem    (void*, a CUDA device pointer)
+ *     cl_command_queue  ->  clblasQueue  (cudaStream_t)
+ *     cl_event          ->  clblasEvent  (cudaEvent_t)
+ *     cl_uint/cl_float/cl_double -> unsigned/float/double
+ *
+ * Offsets are counted in elements, exactly as in the reference (src/clBLAS.h:7345-7346).
+ * Errors are reported only through the returned clblasStatus; no exception crosses this ABI.
+ * The library has no CPU code path: every call either launches CUDA kernels on the stream it
+ * was given or returns an error status.
+ */
+#ifndef CLBLAS_B200_H_
+#define CLBLAS_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void*               clblasMem;
+typedef struct CUstream_st* clblasQueue;
+typedef struct CUevent_st*  clblasEvent;
+
+/* Enumerations: same names and the same numeric values as src/clBLAS.h:78-113. */
+typedef enum clblasOrder_     { clblasRowMajor = 0, clblasColumnMajor = 1 } clblasOrder;
+typedef enum clblasTranspose_ { clblasNoTrans = 0, clblasTrans = 1, clblasConjTrans = 2 } clblasTranspose;
+typedef enum clblasUplo_      { clblasUpper = 0, clblasLower = 1 } clblasUplo;
+typedef enum clblasDiag_      { clblasUnit = 0, clblasNonUnit = 1 } clblasDiag;
+typedef enum clblasSide_      { clblasLeft = 0, clblasRight = 1 } clblasSide;
+
+/* Status codes: same names and values as src/clBLAS.h:123-155.  The first block aliases
+ * OpenCL error numbers there; the numbers are the OpenCL specification's constants. */
+typedef enum clblasStatus_ {
+    clblasSuccess               = 0,
+    clblasInvalidValue          = -30,
+    clblasInvalidCommandQueue   = -36,
+    clblasInvalidContext        = -34,
+    clblasInvalidMemObject      = -38,
+    clblasInvalidDevice         = -33,
+    clblasInvalidEventWaitList  = -57,
+    clblasOutOfResources        = -5,
+    clblasOutOfHostMemory       = -6,
+    clblasInvalidOperation      = -59,
+    clblasCompilerNotAvailable  = -3,
+    clblasBuildProgramFailure   = -11,
+    clblasNotImplemented        = -1024,
+    clblasNotInitialized        = -1023,
+    clblasInvalidMatA           = -1022,
+    clblasInvalidMatB           = -1021,
+    clblasInvalidMatC           = -1020,
+    clblasInvalidVecX           = -1019,
+    clblasInvalidVecY           = -1018,
+    clblasInvalidDim            = -1017,
+    clblasInvalidLeadDimA       = -1016,
+    clblasInvalidLeadDimB       = -1015,
+    clblasInvalidLeadDimC       = -1014,
+    clblasInvalidIncX           = -1013,
+    clblasInvalidIncY           = -1012,
+    clblasInsufficientMemMatA   = -1011,
+    clblasInsufficientMemMatB   = -1010,
+    clblasInsufficientMemMatC   = -1009,
+    clblasInsufficientMemVecX   = -1008,
+    clblasInsufficientMemVecY   = -1007
+} clblasStatus;
+
+/* ---- life cycle: replaces src/clBLAS.h:176-213 (src/library/blas/init.c:34-263) ---------- */
+
+/* Version of the clBLAS API this library is a drop-in for (2.12.0, src/CMakeLists.txt:107-118). */
+clblasStatus clblasGetVersion(unsigned* major, unsigned* minor, unsigned* patch);
+/* Idempotent; creates per-device state lazily.  Not thread safe (src/clBLAS.h:59-61). */
+clblasStatus clblasSetup(void);
+/* Releases cached per-device state (TRSM workspaces). */
+void clblasTeardown(void);
+
+/* ---- GEMM: replaces clblasSgemm (src/clBLAS.h:7382-7405) and clblasDgemm (:7463-7486),
+ *      implemented by src/library/blas/xgemm.cc:341-783 in the reference.
+ *      C <- alpha*op(A)*op(B) + beta*C.  Row-major is served by the reference's operand swap
+ *      (xgemm.cc:40-61); ConjTrans means Trans for real types (xgemm.cc:330-335).
+ *      Argument checks, in the reference's order (xgemm.cc:685-706, generic/common.c:585-686):
+ *      NULL A/B/C -> InvalidMat{A,B,C}; if K != 0: A then B sizes; always C sizes;
+ *      M == 0 or N == 0 -> InvalidDim; short ld -> InvalidLeadDim{A,B,C}; matrix extent beyond
+ *      the CUDA allocation holding the pointer -> InsufficientMemMat{A,B,C}.
+ *      numCommandQueues >= 1; only commandQueues[0] is used (one call = one device).
+ *      The call is asynchronous: work is ordered after every event of eventWaitList and, when
+ *      events != NULL, events[0] must be a created cudaEvent_t that is recorded on completion. */
+clblasStatus clblasSgemm(
+    clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+    size_t M, size_t N, size_t K,
+    float alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    float beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasDgemm(
+    clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+    size_t M, size_t N, size_t K,
+    double alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    double beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+/* ---- TRSM: replaces clblasStrsm (src/clBLAS.h:7988-8008, src/library/blas/xtrsm.cc:1601-1661)
+ *      and clblasDtrsm (src/clBLAS.h:8063-8083, xtrsm.cc:1664-1785, blocked algorithm :1136-1507).
+ *      Solves op(A)*X = alpha*B (Left) or X*op(A) = alpha*B (Right); X overwrites B.
+ *      Checks follow the reference's STRSM order (xtrsm.cc:1623-1624,
+ *      functor/functor_xtrsm.cc:57-75): queues, events, NotInitialized (clblasSetup not called),
+ *      NULL A/B, A sizes (order x order), B sizes.  Row-major is served by the side/uplo flip of
+ *      xtrsm.cc:54-64 for both precisions.  The out-of-triangle part of A is never read. */
+clblasStatus clblasStrsm(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    float alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasDtrsm(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    double alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+/* ---- partition planning: replaces the per-queue problem split of
+ *      src/library/blas/generic/solution_seq_make.c:764-866 (stripeDivision over the N
+ *      dimension, pieces aligned to DIVISION_ALIGNMENT = 128).
+ *      Splits `total` columns over `parts` devices in contiguous blocks whose boundaries are
+ *      multiples of `align` (the last block takes the remainder).  Writes parts+1 boundaries to
+ *      `bounds` (bounds[0] = 0, bounds[parts] = total).  Pure host arithmetic; no CUDA call. */
+clblasStatus clblasB200PlanShards(size_t total, unsigned parts, size_t align, size_t* bounds);
+
+/* ---- introspection used by the benchmark client and the tests (no reference counterpart
+ *      beyond the AUTOGEMM_PRINT_DEBUG kernel-name print of xgemm.cc:437-445) ------------- */
+
+/* Number of CUDA kernels this library has launched in the calling process so far. */
+unsigned long long clblasB200LaunchCount(void);
+/* Name of the kernel family the most recent GEMM of the calling thread dispatched to
+ * ("dgemm_mma_tma", "sgemm_ffma_tma", "gemm_simt_ldg", ...).  Static storage; never NULL. */
+const char* clblasB200LastGemmKernel(void);
+/* Forces a kernel family for GEMM calls of the whole process: 0 = automatic dispatch,
+ * 1 = always the alignment-free LDG path.  Returns the previous value. */
+int clblasB200SetGemmPath(int path);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLBLAS_B200_H_ */

@@ -1,0 +1,118 @@
+/*
+ * oracle_blas.c -- TEST INFRASTRUCTURE ONLY.  CPU restatement of the reference's own CPU BLAS
+ * for the level-3 hot path (GEMM and TRSM, float and double).
+ *
+ * It restates NaiveBlas::gemm (src/library/tools/ktest/naive/naive_blas.cpp:546-578) and
+ * NaiveBlas::trsm (:632-690) together with the index mapping of MatrixAccessor (:487-543):
+ * the same loop nests, the same order of floating point operations (so results are bit-identical
+ * to the reference code compiled without FMA contraction), written as plain C over raw pointers.
+ * Parity is pinned: tests/test_oracle.py checks this file against the reference's own
+ * naive_blas.cpp compiled from where it lies (oracle/_ref), against the reference's known-answer
+ * TRSM test (src/tests/correctness/corr-trsm.cpp:240-452) and against committed golden vectors.
+ *
+ * Nothing in the product (clblas_b200/, include/) may call into this file; only tests/, the
+ * smoke check and the benchmark's CPU-baseline leg do.
+ *
+ * Rows of the result are independent, so the outer loop may be split over OpenMP threads
+ * without changing a single bit of the output.
+ */
+#include <stddef.h>
+
+enum { ORowMajor = 0, OColumnMajor = 1 };           /* clblasOrder      */
+enum { ONoTrans = 0, OTrans = 1, OConjTrans = 2 };   /* clblasTranspose  */
+enum { OUpper = 0, OLower = 1 };                     /* clblasUplo       */
+enum { OUnit = 0, ONonUnit = 1 };                    /* clblasDiag       */
+enum { OLeft = 0, ORight = 1 };                      /* clblasSide       */
+
+/* MatrixAccessor (naive_blas.cpp:487-543): logical (row, col) -> physical index.
+ * "tra" is true when logical rows are contiguous in memory steps of 1 (column-major, no
+ * transposition, or row-major with transposition). */
+typedef struct { size_t ld; int tra; } acc_t;
+
+static acc_t make_acc(int order, int trans, size_t ld)
+{
+    acc_t a;
+    a.ld = ld;
+    a.tra = ((order == OColumnMajor && trans == ONoTrans) ||
+             (order == ORowMajor && trans != ONoTrans));
+    return a;
+}
+
+static size_t at(acc_t a, size_t row, size_t col)
+{
+    return a.tra ? (row + col * a.ld) : (row * a.ld + col);
+}
+
+#define DEFINE_GEMM(NAME, T)                                                                   \
+void NAME(int order, int transA, int transB, size_t M, size_t N, size_t K, T alpha,            \
+          const T* A, size_t lda, const T* B, size_t ldb, T beta, T* C, size_t ldc)            \
+{                                                                                              \
+    acc_t ma = make_acc(order, transA, lda);                                                   \
+    acc_t mb = make_acc(order, transB, ldb);                                                   \
+    acc_t mc = make_acc(order, ONoTrans, ldc);                                                 \
+    long long i;                                                                               \
+    _Pragma("omp parallel for schedule(static)")                                               \
+    for (i = 0; i < (long long)M; i++) {                                                       \
+        size_t j, k;                                                                           \
+        for (j = 0; j < N; j++) {                                                              \
+            T tmp = (T)0.0;                                                                    \
+            for (k = 0; k < K; k++) {                                                          \
+                tmp = tmp + A[at(ma, (size_t)i, k)] * B[at(mb, k, j)];                         \
+            }                                                                                  \
+            C[at(mc, (size_t)i, j)] = C[at(mc, (size_t)i, j)] * beta + tmp * alpha;            \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_GEMM(oracle_sgemm, float)
+DEFINE_GEMM(oracle_dgemm, double)
+
+/* NaiveBlas::trsm (naive_blas.cpp:632-690).  side == Right is handled, as there, by flipping
+ * both accessors (solving the transposed system) and reversing the pass direction.  The solve
+ * runs row by row of the (possibly flipped) system; within a row the right-hand-side columns
+ * are independent, so the j loop is the one split over threads. */
+#define DEFINE_TRSM(NAME, T)                                                                   \
+void NAME(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, T alpha,    \
+          const T* A, size_t lda, T* B, size_t ldb)                                            \
+{                                                                                              \
+    size_t rowsA = (side == OLeft) ? M : N;                                                    \
+    size_t colsB = (side == OLeft) ? N : M;                                                    \
+    acc_t ma = make_acc(order, transA, lda);                                                   \
+    acc_t mb = make_acc(order, ONoTrans, ldb);                                                 \
+    int revPass = (uplo == OUpper) ^ (transA != ONoTrans);                                     \
+    size_t i;                                                                                  \
+    if (side == ORight) {                                                                      \
+        ma.tra = !ma.tra;                                                                      \
+        mb.tra = !mb.tra;                                                                      \
+        revPass = !revPass;                                                                    \
+    }                                                                                          \
+    for (i = 0; i < rowsA; i++) {                                                              \
+        size_t row = revPass ? (rowsA - i - 1) : i;                                            \
+        size_t boundK = revPass ? (rowsA - row - 1) : row;                                     \
+        long long j;                                                                           \
+        _Pragma("omp parallel for schedule(static)")                                           \
+        for (j = 0; j < (long long)colsB; j++) {                                               \
+            T tmp = (T)0.0;                                                                    \
+            size_t k;                                                                          \
+            for (k = 0; k <= boundK; k++) {                                                    \
+                size_t col = revPass ? (rowsA - k - 1) : k;                                    \
+                if (col == row) {                                                              \
+                    T a = (diag == OUnit) ? (T)1.0 : A[at(ma, row, col)];                      \
+                    tmp = (B[at(mb, row, (size_t)j)] - tmp) / a;                               \
+                } else {                                                                       \
+                    tmp = tmp + A[at(ma, row, col)] * B[at(mb, col, (size_t)j)];               \
+                }                                                                              \
+            }                                                                                  \
+            B[at(mb, row, (size_t)j)] = tmp;                                                   \
+        }                                                                                      \
+    }                                                                                          \
+    for (i = 0; i < rowsA; i++) {                                                              \
+        size_t j;                                                                              \
+        for (j = 0; j < colsB; j++) {                                                          \
+            B[at(mb, i, j)] = B[at(mb, i, j)] * alpha;                                         \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_TRSM(oracle_strsm, float)
+DEFINE_TRSM(oracle_dtrsm, double)

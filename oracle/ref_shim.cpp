@@ -1,0 +1,58 @@
+/*
+ * ref_shim.cpp -- TEST INFRASTRUCTURE ONLY.  Builds the reference's own CPU BLAS,
+ * src/library/tools/ktest/naive/naive_blas.cpp, from where it lies in the reference tree
+ * (the include directory is given on the compiler command line by oracle/Makefile; no copy of
+ * the reference source is kept in this repository) and exports NaiveBlas::gemm / NaiveBlas::trsm
+ * for float and double with C linkage.  The output goes to oracle/_ref/libnaive_ref.so.
+ *
+ * naive_blas.cpp expects the OpenCL scalar and 2-vector typedefs; the few it uses are declared
+ * here so that no OpenCL header is needed.
+ */
+#include <cstddef>
+#include <cmath>
+#include <string>
+
+typedef int                cl_int;
+typedef unsigned int       cl_uint;
+typedef unsigned long long cl_ulong;
+typedef float              cl_float;
+typedef double             cl_double;
+typedef struct { float s[2]; }  cl_float2;
+typedef struct { double s[2]; } cl_double2;
+using std::isnan;
+
+#include "naive_blas.cpp"
+
+extern "C" {
+
+void ref_sgemm(int order, int transA, int transB, size_t M, size_t N, size_t K, float alpha,
+               const float* A, size_t lda, const float* B, size_t ldb, float beta, float* C, size_t ldc)
+{
+    NaiveBlas::gemm<float>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasTranspose)transA,
+                           (NaiveBlas::clblasTranspose)transB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+void ref_dgemm(int order, int transA, int transB, size_t M, size_t N, size_t K, double alpha,
+               const double* A, size_t lda, const double* B, size_t ldb, double beta, double* C, size_t ldc)
+{
+    NaiveBlas::gemm<double>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasTranspose)transA,
+                            (NaiveBlas::clblasTranspose)transB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+void ref_strsm(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, float alpha,
+               const float* A, size_t lda, float* B, size_t ldb)
+{
+    NaiveBlas::trsm<float>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasSide)side,
+                           (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)transA,
+                           (NaiveBlas::clblasDiag)diag, M, N, alpha, A, lda, B, ldb);
+}
+
+void ref_dtrsm(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, double alpha,
+               const double* A, size_t lda, double* B, size_t ldb)
+{
+    NaiveBlas::trsm<double>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasSide)side,
+                            (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)transA,
+                            (NaiveBlas::clblasDiag)diag, M, N, alpha, A, lda, B, ldb);
+}
+
+}  // extern "C"

@@ -1,0 +1,43 @@
+"""Generates tests/golden/level3_golden.npz from the reference's own CPU BLAS.
+
+Run in a container that holds the reference tree (it needs oracle/_ref/libnaive_ref.so, which
+oracle/Makefile builds from the reference's src/library/tools/ktest/naive/naive_blas.cpp):
+
+    python tests/golden/make_golden.py
+
+Each case stores the seeded inputs' parameters and the output buffer NaiveBlas produced, so
+that on a machine without the reference tree the C restatement (and the CUDA path) can still
+be checked against the reference's results.  Inputs are regenerated from the seed by
+tests/cases.py; only outputs are stored.
+"""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "..", ".."))
+import oracle  # noqa: E402
+from tests import cases  # noqa: E402
+
+
+def main():
+    oracle.build()
+    assert oracle.have_ref(), "oracle/_ref/libnaive_ref.so missing: reference tree not present"
+    out = {}
+    for name, c in cases.golden_gemm_cases().items():
+        A, B, C = cases.gemm_buffers(c)
+        oracle.gemm(c["order"], c["transA"], c["transB"], c["M"], c["N"], c["K"], c["alpha"], A, c["offA"],
+                    c["lda"], B, c["offB"], c["ldb"], c["beta"], C, c["offC"], c["ldc"], impl="ref")
+        out[name] = C
+    for name, c in cases.golden_trsm_cases().items():
+        A, B = cases.trsm_buffers(c)
+        oracle.trsm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A,
+                    c["offA"], c["lda"], B, c["offB"], c["ldb"], impl="ref")
+        out[name] = B
+    path = os.path.join(os.path.dirname(__file__), "level3_golden.npz")
+    np.savez_compressed(path, **out)
+    print(f"wrote {path}: {len(out)} cases, {os.path.getsize(path)} bytes")
+
+
+if __name__ == "__main__":
+    main()
