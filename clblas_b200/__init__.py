@@ -58,7 +58,7 @@ def check(status: int, what: str = "clblas call") -> None:
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m clblas_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python clblas_b200/build.py` "
             "(there is no CPU or PyTorch fallback for these routines)")
     lib = ctypes.CDLL(LIB_PATH)
     sz, u, i, vp = ctypes.c_size_t, ctypes.c_uint, ctypes.c_int, ctypes.c_void_p
@@ -81,6 +81,10 @@ def _load() -> ctypes.CDLL:
     lib.clblasB200PlanShards.restype = i
     lib.clblasB200LaunchCount.argtypes = []
     lib.clblasB200LaunchCount.restype = ctypes.c_ulonglong
+    lib.clblasB200ProbePeak.argtypes = [i, ctypes.c_double]
+    lib.clblasB200ProbePeak.restype = ctypes.c_double
+    lib.clblasB200DeviceFault.argtypes = []
+    lib.clblasB200DeviceFault.restype = ctypes.c_uint
     lib.clblasB200LastGemmKernel.argtypes = []
     lib.clblasB200LastGemmKernel.restype = ctypes.c_char_p
     lib.clblasB200SetGemmPath.argtypes = [i]
@@ -92,7 +96,7 @@ lib = _load()
 
 EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "clblasDgemm", "clblasStrsm",
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
-           "clblasB200SetGemmPath"]
+           "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -195,6 +199,16 @@ def plan_shards(total: int, parts: int, align: int = 128):
 
 def launch_count() -> int:
     return int(lib.clblasB200LaunchCount())
+
+
+def probe_peak(kind: str, seconds: float = 0.2) -> float:
+    """Measured issue-rate peak in TFLOP/s: kind "fp32" (FFMA) or "fp64" (FP64 tensor-core MMA)."""
+    return float(lib.clblasB200ProbePeak(0 if kind == "fp32" else 1, seconds))
+
+
+def device_fault() -> int:
+    """Synchronises and returns the sticky bounded-wait failure flags (0 = healthy)."""
+    return int(lib.clblasB200DeviceFault())
 
 
 def last_gemm_kernel() -> str:

@@ -1,6 +1,6 @@
 """Builds libclblas_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-    python -m clblas_b200.build [--force]
+    python clblas_b200/build.py [--force]
 
 Every .cu file under csrc/ is compiled to an object under build/ and linked into
 lib/libclblas_b200.so; the native benchmark client (client/client.cpp) is linked against it.

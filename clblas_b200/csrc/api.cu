@@ -306,6 +306,12 @@ clblasStatus clblasB200PlanShards(size_t total, unsigned parts, size_t align, si
 }
 
 unsigned long long clblasB200LaunchCount(void) { return g_launches.load(); }
+
+unsigned clblasB200DeviceFault(void)
+{
+    if (cudaDeviceSynchronize() != cudaSuccess) { cudaGetLastError(); return 0x80000000u; }
+    return dgemm_tma_fault_flag() | sgemm_tma_fault_flag();
+}
 const char* clblasB200LastGemmKernel(void) { return t_last_kernel; }
 int clblasB200SetGemmPath(int path) { return g_forced_path.exchange(path); }
 

@@ -54,6 +54,10 @@ cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t 
                           const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
 void trsm_release_workspaces();
 
+// Sticky per-translation-unit flags set when a bounded mbarrier wait inside a kernel ran out.
+unsigned dgemm_tma_fault_flag();
+unsigned sgemm_tma_fault_flag();
+
 // cuTensorMapEncodeTiled obtained through the runtime's driver entry point query (no libcuda link).
 void* get_tensor_map_encoder();
 

@@ -1,0 +1,246 @@
+// SGEMM in true FP32 (FFMA), TMA-staged: C = alpha*op(A)*op(B) + beta*C, column-major, for
+// operands whose base addresses and leading dimensions are multiples of 16 bytes.
+//
+// B200 counterpart of the reference's AutoGemm sgemm tile kernels, in particular its best one,
+// the hand-tuned 128x128 macro-tile with 8x8 micro-tile
+// (src/library/blas/AutoGemm/UserGemmKernelSources/sgemm_Col_NT_B1_MX128_NX128_KX16_src.cpp),
+// and of the generator they come from (src/library/blas/AutoGemm/KernelOpenCL.py:13-459).
+//
+// CTA = 128 x 128 tile of C, K in slabs of 32.  Warp 8 is the producer (one lane issues two TMA
+// bulk-tensor loads per slab into a STAGES-deep shared-memory ring, full/empty mbarriers, bounded
+// waits); warps 0-7 are consumers, 16 x 16 threads with an 8 x 8 register tile each.  TMA
+// zero-fills beyond M, N, K, so one launch covers ragged shapes; the epilogue is predicated.
+//
+// Shared layouts:
+//  * M/N-contiguous operand (A for transA=N, B for transB=T): box 128 x 32 (k), dense rows of 128
+//    floats; a thread reads two float4 per k (rows 4*tx..+3 and 64+4*tx..+3), a warp reads 256
+//    contiguous bytes: conflict free.
+//  * K-contiguous operand (A for transA=T, B for transB=N): box 32 (k) x 128, 128-byte rows,
+//    SWIZZLE_128B; a thread reads one float4 (4 consecutive k) per row, rows tx + 16*i for A so
+//    that the 8 lanes of a quarter warp hit 8 different swizzle phases: conflict free.  B rows are
+//    shared by the 16 lanes with equal ty (broadcast).
+// The inner loop works on 4 k at a time: 16 LDS.128 for 256 FFMA.
+#include "common.h"
+#include "tma_pipeline.cuh"
+
+namespace cb200 {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 32;
+constexpr int STAGES = 5;
+constexpr int OPERAND_BYTES = BM * BK * 4;          // 16 KB
+constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;
+constexpr int CONSUMER_WARPS = 8;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int GROUP_M = 16;
+
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(THREADS, 1)
+sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                      float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
+                      unsigned tilesM, unsigned tilesN)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+
+    unsigned tm, tn;
+    {
+        const unsigned per_group = GROUP_M * tilesN;
+        const unsigned g = blockIdx.x / per_group;
+        const unsigned first = g * GROUP_M;
+        const unsigned rows = min((unsigned)GROUP_M, tilesM - first);
+        const unsigned r = blockIdx.x - g * per_group;
+        tm = first + r % rows;
+        tn = r / rows;
+    }
+    const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
+    const int nk = (int)((K + BK - 1) / BK);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CONSUMER_WARPS);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == CONSUMER_WARPS) {
+        if (lane == 0) {
+            tma_prefetch_descriptor(&mapA);
+            tma_prefetch_descriptor(&mapB);
+            for (int kt = 0; kt < nk; kt++) {
+                const int s = kt % STAGES;
+                if (kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) break;
+                unsigned char* sa = smem + s * STAGE_BYTES;
+                unsigned char* sb = sa + OPERAND_BYTES;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                const int k0 = kt * BK;
+                if (TA) tma_load_2d(sa, &mapA, k0, (int)m0, &full[s]); else tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
+                if (TB) tma_load_2d(sb, &mapB, (int)n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, (int)n0, &full[s]);
+            }
+        }
+        return;
+    }
+
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+
+    // Row i (0..7) of this thread's register tile is tile row rowA(i); column j is tile column colB(j).
+    auto rowA = [&](int i) { return TA ? tx + 16 * i : tx * 4 + (i & 3) + 64 * (i >> 2); };
+    auto colB = [&](int j) { return ty * 4 + (j & 3) + 64 * (j >> 2); };
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+
+    for (int kt = 0; kt < nk; kt++) {
+        const int s = kt % STAGES;
+        if (!mbar_wait(&full[s], (kt / STAGES) & 1)) break;
+        const unsigned char* sa = smem + s * STAGE_BYTES;
+        const unsigned char* sb = sa + OPERAND_BYTES;
+#pragma unroll
+        for (int kc = 0; kc < BK / 4; kc++) {
+            float a[4][8], b[4][8];
+            if (TA) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float4 v = *reinterpret_cast<const float4*>(sa + (tx + 16 * i) * 128 + ((kc ^ (tx & 7)) << 4));
+                    a[0][i] = v.x; a[1][i] = v.y; a[2][i] = v.z; a[3][i] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float4 v0 = *reinterpret_cast<const float4*>(sa + (kc * 4 + q) * 512 + tx * 16);
+                    const float4 v1 = *reinterpret_cast<const float4*>(sa + (kc * 4 + q) * 512 + 256 + tx * 16);
+                    a[q][0] = v0.x; a[q][1] = v0.y; a[q][2] = v0.z; a[q][3] = v0.w;
+                    a[q][4] = v1.x; a[q][5] = v1.y; a[q][6] = v1.z; a[q][7] = v1.w;
+                }
+            }
+            if (!TB) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int n = ty * 4 + (j & 3) + 64 * (j >> 2);
+                    const float4 v = *reinterpret_cast<const float4*>(sb + n * 128 + ((kc ^ (n & 7)) << 4));
+                    b[0][j] = v.x; b[1][j] = v.y; b[2][j] = v.z; b[3][j] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float4 v0 = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * 512 + ty * 16);
+                    const float4 v1 = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * 512 + 256 + ty * 16);
+                    b[q][0] = v0.x; b[q][1] = v0.y; b[q][2] = v0.z; b[q][3] = v0.w;
+                    b[q][4] = v1.x; b[q][5] = v1.y; b[q][6] = v1.z; b[q][7] = v1.w;
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[q][i], b[q][j], acc[i][j]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+
+    // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
+    const bool useC = (beta != 0.f);
+    const bool vec = !TA && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const size_t col = n0 + colB(j);
+        if (col >= N) continue;
+        float* cc = C + col * ldc;
+        if (vec) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const size_t row = m0 + tx * 4 + 64 * h;
+                if (row + 3 < M) {
+                    float4 r;
+                    r.x = alpha * acc[4 * h + 0][j]; r.y = alpha * acc[4 * h + 1][j];
+                    r.z = alpha * acc[4 * h + 2][j]; r.w = alpha * acc[4 * h + 3][j];
+                    if (useC) {
+                        const float4 o = *reinterpret_cast<const float4*>(cc + row);
+                        r.x = fmaf(beta, o.x, r.x); r.y = fmaf(beta, o.y, r.y);
+                        r.z = fmaf(beta, o.z, r.z); r.w = fmaf(beta, o.w, r.w);
+                    }
+                    *reinterpret_cast<float4*>(cc + row) = r;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        if (row + e < M) {
+                            float r = alpha * acc[4 * h + e][j];
+                            if (useC) r = fmaf(beta, cc[row + e], r);
+                            cc[row + e] = r;
+                        }
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const size_t row = m0 + rowA(i);
+                if (row < M) {
+                    float r = alpha * acc[i][j];
+                    if (useC) r = fmaf(beta, cc[row], r);
+                    cc[row] = r;
+                }
+            }
+        }
+    }
+}
+
+template <bool TA, bool TB>
+cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
+{
+    void* enc = get_tensor_map_encoder();
+    CUtensorMap mapA, mapB;
+    bool ok;
+    if (TA) ok = make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.A, p.K, p.M, p.lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    else    ok = make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.A, p.M, p.K, p.lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!ok) return cudaErrorNotSupported;
+    if (TB) ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.N, p.K, p.ldb, BN, BK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    else    ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.K, p.N, p.ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!ok) return cudaErrorNotSupported;
+
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
+    sgemm_ffma_tma_kernel<TA, TB><<<(unsigned)(tilesM * tilesN), THREADS, SMEM_BYTES, s>>>(
+        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s)
+{
+    if (!aligned16(p.A) || !aligned16(p.B) || (p.lda & 3) || (p.ldb & 3)) return cudaErrorNotSupported;
+    if (p.M >= (1u << 31) || p.N >= (1u << 31) || p.K >= (1u << 31)) return cudaErrorNotSupported;
+    const size_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    if (tiles >= (1u << 31)) return cudaErrorNotSupported;
+    set_last_kernel("sgemm_ffma_tma");
+    if (!p.ta && !p.tb) return launch<false, false>(p, s);
+    if (!p.ta && p.tb) return launch<false, true>(p, s);
+    if (p.ta && !p.tb) return launch<true, false>(p, s);
+    return launch<true, true>(p, s);
+}
+
+unsigned sgemm_tma_fault_flag() { return read_wait_timeout_flag(); }
+
+}  // namespace cb200

@@ -1,0 +1,106 @@
+"""Single-box partitioner: one process per GPU, column-major problems sharded over the ranks.
+
+The reference's only multi-device mechanism is "several command queues per call": its legacy
+solver gives every queue one piece of the problem, split along N in pieces aligned to 128
+(stripeDivision, src/library/blas/generic/solution_seq_make.c:764-866), and relies on all queues
+sharing the OpenCL buffers.  GPUs of one box do not share buffers, so here
+
+* GEMM: rank r owns the column block [b_r, b_{r+1}) of op(B) and of C (boundaries from
+  clblasB200PlanShards); A lives on the root and is broadcast over NCCL in panels -- column
+  blocks of A as stored, which are contiguous in memory.  For transA = N a panel is a K-slab and
+  the panel products accumulate into C (beta only on the first panel, 1 afterwards -- the
+  reference's own split-K accumulation, src/library/blas/specialCases/GemmSpecialCases.cpp:127-191);
+  for transA = T a panel is a block of C's rows.  All broadcasts are issued up front on NCCL's
+  stream; the GEMM on panel p is ordered after broadcast p only, so panel p+1 travels over NVLink
+  while panel p is multiplied.
+* TRSM (side = Left): rank r owns right-hand-side columns [b_r, b_{r+1}); A is broadcast once
+  and every rank solves its block independently (no further exchange).
+
+The GEMM / TRSM calls go through the C ABI (clblas_b200.clblasSgemm, ...).  `gemm_fn` / `trsm_fn`
+exist so that the rank logic (panel plan, ordering, accumulation) can be exercised with CPU
+tensors over gloo in the tests; the package itself has no CPU implementation to put there.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+import clblas_b200 as cb
+
+
+def plan_columns(total: int, parts: int, align: int = 128) -> List[int]:
+    return cb.plan_shards(total, parts, align)
+
+
+def panel_plan(ncols: int, panels: int, align: int = 128) -> List[Tuple[int, int]]:
+    """Column ranges [c0, c1) of the stored A, at most `panels` of them, aligned to `align`."""
+    b = cb.plan_shards(ncols, max(1, panels), align)
+    return [(b[i], b[i + 1]) for i in range(len(b) - 1) if b[i + 1] > b[i]]
+
+
+def _default_gemm(prec: str) -> Callable:
+    return cb.clblasSgemm if prec == "s" else cb.clblasDgemm
+
+
+def _default_trsm(prec: str) -> Callable:
+    return cb.clblasStrsm if prec == "s" else cb.clblasDtrsm
+
+
+def gemm_column_sharded(prec: str, transA: int, transB: int, M: int, n_local: int, K: int, alpha: float,
+                        A: torch.Tensor, lda: int, B_local: torch.Tensor, ldb: int, beta: float,
+                        C_local: torch.Tensor, ldc: int, *, root: int = 0, panels: int = 8,
+                        group: Optional[dist.ProcessGroup] = None, gemm_fn: Optional[Callable] = None) -> int:
+    """Column-major C_local <- alpha*op(A)*op(B)_local + beta*C_local on every rank.
+
+    A is a flat tensor holding the stored A (column-major, leading dimension lda) on the root and a
+    receive buffer of the same size elsewhere; B_local / C_local hold this rank's column block
+    (n_local columns) as flat column-major buffers.  Returns the first non-success clblasStatus.
+    """
+    gemm = gemm_fn or _default_gemm(prec)
+    ta = transA != cb.clblasNoTrans
+    tb = transB != cb.clblasNoTrans
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    a_cols = M if ta else K                     # columns of A as stored
+    plan = panel_plan(a_cols, panels if world > 1 else 1)
+
+    works = []
+    if world > 1:
+        for (c0, c1) in plan:
+            end = min(c1 * lda, A.numel())
+            works.append(dist.broadcast(A[c0 * lda:end], src=root, group=group, async_op=True))
+
+    status = cb.clblasSuccess
+    for idx, (c0, c1) in enumerate(plan):
+        if works:
+            works[idx].wait()                   # orders the compute stream after this panel's broadcast
+        w = c1 - c0
+        if n_local == 0:
+            continue
+        if not ta:
+            # K-slab: C += alpha * A[:, c0:c1] * op(B)[c0:c1, :]
+            offB = c0 * ldb if tb else c0
+            st = gemm(cb.clblasColumnMajor, transA, transB, M, n_local, w, alpha, A, c0 * lda, lda,
+                      B_local, offB, ldb, beta if idx == 0 else 1.0, C_local, 0, ldc)
+        else:
+            # row block of C: C[c0:c1, :] = alpha * A[:, c0:c1]^T * op(B) + beta * C[c0:c1, :]
+            st = gemm(cb.clblasColumnMajor, transA, transB, w, n_local, K, alpha, A, c0 * lda, lda,
+                      B_local, 0, ldb, beta, C_local, c0, ldc)
+        if st != cb.clblasSuccess and status == cb.clblasSuccess:
+            status = st
+    return status
+
+
+def trsm_rhs_sharded(prec: str, uplo: int, transA: int, diag: int, M: int, n_local: int, alpha: float,
+                     A: torch.Tensor, lda: int, B_local: torch.Tensor, ldb: int, *, root: int = 0,
+                     group: Optional[dist.ProcessGroup] = None, trsm_fn: Optional[Callable] = None) -> int:
+    """Column-major, side = Left: op(A) X_local = alpha B_local on every rank; A is broadcast from the
+    root in one piece (M*lda elements), then each rank solves its own right-hand-side columns."""
+    trsm = trsm_fn or _default_trsm(prec)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world > 1:
+        dist.broadcast(A, src=root, group=group)
+    if n_local == 0:
+        return cb.clblasSuccess
+    return trsm(cb.clblasColumnMajor, cb.clblasLeft, uplo, transA, diag, M, n_local, alpha, A, 0, lda, B_local, 0, ldb)

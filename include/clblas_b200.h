@@ -149,6 +149,15 @@ clblasStatus clblasB200PlanShards(size_t total, unsigned parts, size_t align, si
 
 /* Number of CUDA kernels this library has launched in the calling process so far. */
 unsigned long long clblasB200LaunchCount(void);
+/* Synchronises the current device and returns 0 when no kernel of this library ever gave up a
+ * bounded wait on it (every in-kernel wait on an mbarrier has an iteration limit; a kernel whose
+ * wait runs out sets a sticky flag and returns instead of hanging).  Non-zero = results of
+ * earlier calls on this device are not to be trusted. */
+unsigned clblasB200DeviceFault(void);
+/* Issue-rate probe of the current device: kind 0 = FP32 FMA pipe, kind 1 = FP64 tensor-core
+ * (mma.sync m8n8k4) pipe.  Runs register-only FMA/MMA loops for about `seconds` and returns the best
+ * TFLOP/s seen (negative on error).  The benchmark uses it as the live roofline denominator. */
+double clblasB200ProbePeak(int kind, double seconds);
 /* Name of the kernel family the most recent GEMM of the calling thread dispatched to
  * ("dgemm_mma_tma", "sgemm_ffma_tma", "gemm_simt_ldg", ...).  Static storage; never NULL. */
 const char* clblasB200LastGemmKernel(void);

@@ -143,3 +143,51 @@ def test_config3_sgemm_rowmajor_ragged(lib):
     assert (c["lda"], c["ldb"], c["ldc"]) == (4099 + 16, 3001 + 32, 3001 + 8)
     check_real(lib, c)
     assert lib.last_gemm_kernel() == "gemm_simt_ldg"
+
+
+def _aligned_case(prec, order, ta, tb, M, N, K, seed, mode="int", alpha=2.0, beta=3.0):
+    """Leading dimensions rounded up to 16 bytes and zero offsets: what the TMA paths accept."""
+    q = 4 if prec == "s" else 2
+    c = cases.gemm_case(prec, order, ta, tb, M, N, K, alpha=alpha, beta=beta, mode=mode, seed=seed)
+    for k in ("lda", "ldb", "ldc"):
+        c[k] = (c[k] + q - 1) // q * q
+    return c
+
+
+@pytest.mark.parametrize("prec,kernel", [("s", "sgemm_ffma_tma"), ("d", "dgemm_mma_tma")])
+def test_tma_paths_exact(lib, prec, kernel):
+    """TMA-staged kernels, all four transposes and both orders, sizes straddling the 128 tile and the
+    K slab, ragged M, N, K served by TMA's out-of-bounds zero fill: bit-identical to the oracle."""
+    seed = 20000
+    for order in (ColumnMajor, RowMajor):
+        for ta in (NoTrans, Trans):
+            for tb in (NoTrans, Trans):
+                for M, N, K in ((128, 128, 32), (256, 128, 64), (127, 129, 33), (130, 250, 17), (1, 1, 1), (64, 300, 100),
+                                (384, 257, 161), (5, 3, 200)):
+                    seed += 1
+                    check_exact(lib, _aligned_case(prec, order, ta, tb, M, N, K, seed))
+                    assert lib.last_gemm_kernel() == kernel
+                    check_exact(lib, _aligned_case(prec, order, ta, tb, M, N, K, seed, beta=0.0))
+    assert lib.device_fault() == 0
+
+
+@pytest.mark.parametrize("prec", ["s", "d"])
+def test_tma_paths_real_valued(lib, prec):
+    seed = 21000
+    for ta in (NoTrans, Trans):
+        for tb in (NoTrans, Trans):
+            for M, N, K in ((512, 384, 1000), (257, 129, 2049)):
+                seed += 1
+                check_real(lib, _aligned_case(prec, ColumnMajor, ta, tb, M, N, K, seed, mode="uniform", alpha=1.5, beta=0.5))
+                assert lib.last_gemm_kernel().endswith("_tma")
+    assert lib.device_fault() == 0
+
+
+def test_config2_shape_family_dgemm_tn(lib):
+    """DGEMM column-major T/N, normal(0,1), alpha = beta = 1, tight leading dimensions (BASELINE
+    config 2) at 1024^3, where the float64 host check is cheap; the 8192^3 run is checked through
+    sampled rows/columns in test_full_configs_gpu.py."""
+    c = cases.gemm_case("d", ColumnMajor, Trans, NoTrans, 1024, 1024, 1024, alpha=1.0, beta=1.0, mode="normal")
+    r = check_real(lib, c)
+    assert lib.last_gemm_kernel() == "dgemm_mma_tma"
+    assert r <= 1.0
