@@ -1,0 +1,237 @@
+// Native benchmark client for the B200 level-3 path, with the command line and the output lines
+// of the reference's client (src/client/client.cpp:81-111 options, :574-592 timing loop and the
+// two "BLAS kernel execution ..." lines; GFLOP/s formulas src/client/clfunc_xgemm.hpp:95-98 and
+// src/client/clfunc_xtrsm.hpp:70-80; host data from srand(10), clfunc_xgemm.hpp:364-393; TRSM uses
+// a diagonal A, clfunc_xtrsm.hpp:243-279).  Timing uses CUDA events around `apiCallCount`
+// back-to-back enqueued calls, `profile` samples, samples further than 3 sigma from the mean
+// pruned (src/client/statisticalTimer.cpp:267-289).  It also prints one CSV row in the schema of
+// the reference's published sweeps (doc/performance/**.csv header).
+//
+//   clblas_b200_client -f gemm -r d -m 8192 -n 8192 -k 8192 --transposeA 1 -p 10 --apiCallCount 3
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <iostream>
+#include <string>
+#include <vector>
+
+#include "../../include/clblas_b200.h"
+
+#define CUDA_OK(x)                                                                              \
+    do {                                                                                        \
+        cudaError_t e_ = (x);                                                                   \
+        if (e_ != cudaSuccess) {                                                                \
+            std::fprintf(stderr, "CUDA error %s at %s:%d\n", cudaGetErrorString(e_), __FILE__, __LINE__); \
+            std::exit(2);                                                                       \
+        }                                                                                       \
+    } while (0)
+
+struct Options {
+    size_t M = 128, N = 128, K = 128, lda = 0, ldb = 0, ldc = 0, offA = 0, offB = 0, offC = 0;
+    double alpha = 1.0, beta = 1.0;
+    int order = 1, transA = 0, transB = 0, side = 0, uplo = 0, diag = 0, validate = 0, path = 0;
+    unsigned profile = 20, apiCallCount = 10;
+    std::string function = "gemm", precision = "s";
+};
+
+static void usage()
+{
+    std::puts("clblas_b200_client options (same meaning as the clBLAS client):\n"
+              "  -m/--sizem -n/--sizen -k/--sizek  --lda --ldb --ldc  --offA --offBX --offCY\n"
+              "  --alpha --beta  -o/--order (0 row, 1 column)  --transposeA --transposeB (0/1/2)\n"
+              "  -f/--function gemm|trsm  -r/--precision s|d  --side --uplo --diag\n"
+              "  -p/--profile samples (20)  --apiCallCount calls per sample (10)  -v/--validate 0|1");
+}
+
+static bool parse(int argc, char** argv, Options& o)
+{
+    for (int i = 1; i < argc; i++) {
+        std::string a = argv[i];
+        auto val = [&]() -> const char* { return (i + 1 < argc) ? argv[++i] : "0"; };
+        if (a == "-h" || a == "--help") return false;
+        else if (a == "-m" || a == "--sizem") o.M = std::strtoull(val(), nullptr, 10);
+        else if (a == "-n" || a == "--sizen") o.N = std::strtoull(val(), nullptr, 10);
+        else if (a == "-k" || a == "--sizek") o.K = std::strtoull(val(), nullptr, 10);
+        else if (a == "--lda") o.lda = std::strtoull(val(), nullptr, 10);
+        else if (a == "--ldb") o.ldb = std::strtoull(val(), nullptr, 10);
+        else if (a == "--ldc") o.ldc = std::strtoull(val(), nullptr, 10);
+        else if (a == "--offA") o.offA = std::strtoull(val(), nullptr, 10);
+        else if (a == "--offBX") o.offB = std::strtoull(val(), nullptr, 10);
+        else if (a == "--offCY") o.offC = std::strtoull(val(), nullptr, 10);
+        else if (a == "--alpha") o.alpha = std::atof(val());
+        else if (a == "--beta") o.beta = std::atof(val());
+        else if (a == "-o" || a == "--order") o.order = std::atoi(val());
+        else if (a == "--transposeA") o.transA = std::atoi(val());
+        else if (a == "--transposeB") o.transB = std::atoi(val());
+        else if (a == "-f" || a == "--function") o.function = val();
+        else if (a == "-r" || a == "--precision") o.precision = val();
+        else if (a == "--side") o.side = std::atoi(val());
+        else if (a == "--uplo") o.uplo = std::atoi(val());
+        else if (a == "--diag") o.diag = std::atoi(val());
+        else if (a == "-p" || a == "--profile") o.profile = (unsigned)std::atoi(val());
+        else if (a == "--apiCallCount") o.apiCallCount = (unsigned)std::atoi(val());
+        else if (a == "-v" || a == "--validate") o.validate = std::atoi(val());
+        else if (a == "--path") o.path = std::atoi(val());      // clblasB200SetGemmPath (kernel family override)
+        else { std::fprintf(stderr, "unknown option %s\n", a.c_str()); return false; }
+    }
+    return true;
+}
+
+// rows x cols of op(X) as stored: contiguous extent and number of strides
+static void stored(int order, int trans, size_t rows, size_t cols, size_t& inner, size_t& outer)
+{
+    const bool tra = (order == 1 && trans == 0) || (order == 0 && trans != 0);
+    inner = tra ? rows : cols;
+    outer = tra ? cols : rows;
+}
+
+template <typename T>
+static int run(const Options& o)
+{
+    const bool gemm = o.function == "gemm";
+    size_t ai, ao, bi, bo, ci = 0, co = 0;
+    const size_t tri = o.side == 0 ? o.M : o.N;
+    if (gemm) {
+        stored(o.order, o.transA, o.M, o.K, ai, ao);
+        stored(o.order, o.transB, o.K, o.N, bi, bo);
+        stored(o.order, 0, o.M, o.N, ci, co);
+    } else {
+        ai = ao = tri;
+        stored(o.order, 0, o.M, o.N, bi, bo);
+    }
+    const size_t lda = o.lda ? o.lda : ai, ldb = o.ldb ? o.ldb : bi, ldc = o.ldc ? o.ldc : ci;
+    const size_t na = o.offA + (ao - 1) * lda + ai, nb = o.offB + (bo - 1) * ldb + bi;
+    const size_t nc = gemm ? o.offC + (co - 1) * ldc + ci : 0;
+
+    std::vector<T> hA(na), hB(nb), hC(nc ? nc : 1);
+    std::srand(10);
+    auto rnd = [] { return (T)((std::rand() % 20) - 10) / (T)10; };
+    if (gemm) {
+        for (auto& v : hA) v = rnd();
+        for (auto& v : hB) v = rnd();
+        for (auto& v : hC) v = rnd();
+    } else {
+        std::fill(hA.begin(), hA.end(), (T)0);
+        for (size_t i = 0; i < tri; i++) hA[o.offA + i + i * lda] = (T)(1 + (std::rand() % 4));   // diagonal A, as the reference client
+        for (auto& v : hB) v = rnd();
+    }
+
+    T *dA, *dB, *dC = nullptr;
+    CUDA_OK(cudaMalloc(&dA, na * sizeof(T)));
+    CUDA_OK(cudaMalloc(&dB, nb * sizeof(T)));
+    if (gemm) CUDA_OK(cudaMalloc(&dC, nc * sizeof(T)));
+    CUDA_OK(cudaMemcpy(dA, hA.data(), na * sizeof(T), cudaMemcpyHostToDevice));
+    CUDA_OK(cudaMemcpy(dB, hB.data(), nb * sizeof(T), cudaMemcpyHostToDevice));
+    if (gemm) CUDA_OK(cudaMemcpy(dC, hC.data(), nc * sizeof(T), cudaMemcpyHostToDevice));
+
+    cudaStream_t stream;
+    CUDA_OK(cudaStreamCreate(&stream));
+    clblasQueue q = reinterpret_cast<clblasQueue>(stream);
+    if (clblasSetup() != clblasSuccess) { std::fprintf(stderr, "clblasSetup failed\n"); return 2; }
+    clblasB200SetGemmPath(o.path);
+
+    auto call = [&]() -> clblasStatus {
+        if (gemm) {
+            if (sizeof(T) == 4)
+                return clblasSgemm((clblasOrder)o.order, (clblasTranspose)o.transA, (clblasTranspose)o.transB, o.M, o.N, o.K,
+                                   (float)o.alpha, dA, o.offA, lda, dB, o.offB, ldb, (float)o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+            return clblasDgemm((clblasOrder)o.order, (clblasTranspose)o.transA, (clblasTranspose)o.transB, o.M, o.N, o.K,
+                               o.alpha, dA, o.offA, lda, dB, o.offB, ldb, o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+        }
+        if (sizeof(T) == 4)
+            return clblasStrsm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, (clblasTranspose)o.transA, (clblasDiag)o.diag,
+                               o.M, o.N, (float)o.alpha, dA, o.offA, lda, dB, o.offB, ldb, 1, &q, 0, nullptr, nullptr);
+        return clblasDtrsm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, (clblasTranspose)o.transA, (clblasDiag)o.diag,
+                           o.M, o.N, o.alpha, dA, o.offA, lda, dB, o.offB, ldb, 1, &q, 0, nullptr, nullptr);
+    };
+
+    clblasStatus st = call();          // untimed warm-up call (src/client/client.cpp:497)
+    if (st != clblasSuccess) { std::fprintf(stderr, "call failed with status %d\n", (int)st); return 3; }
+    CUDA_OK(cudaStreamSynchronize(stream));
+
+    if (o.validate && gemm) {
+        // spot check of 64 entries against a double-precision host evaluation of the same inputs
+        std::vector<T> out(nc);
+        CUDA_OK(cudaMemcpy(out.data(), dC, nc * sizeof(T), cudaMemcpyDeviceToHost));
+        double worst = 0;
+        for (int t = 0; t < 64; t++) {
+            const size_t i = std::rand() % o.M, j = std::rand() % o.N;
+            double acc = 0, mag = 0;
+            for (size_t k = 0; k < o.K; k++) {
+                const bool traA = (o.order == 1 && o.transA == 0) || (o.order == 0 && o.transA != 0);
+                const bool traB = (o.order == 1 && o.transB == 0) || (o.order == 0 && o.transB != 0);
+                const double a = hA[o.offA + (traA ? i + k * lda : i * lda + k)];
+                const double b = hB[o.offB + (traB ? k + j * ldb : k * ldb + j)];
+                acc += a * b;
+                mag += std::fabs(a * b);
+            }
+            const size_t cidx = o.offC + (o.order == 1 ? i + j * ldc : i * ldc + j);
+            const double want = o.alpha * acc + o.beta * hC[cidx];
+            const double den = std::fabs(o.alpha) * mag + std::fabs(o.beta * hC[cidx]) + 1e-300;
+            worst = std::max(worst, std::fabs((double)out[cidx] - want) / den);
+        }
+        const double u = sizeof(T) == 4 ? std::ldexp(1.0, -24) : std::ldexp(1.0, -53);
+        std::printf("validation: max scaled error %.3e (bound 4*K*u = %.3e) %s\n", worst, 4.0 * o.K * u,
+                    worst <= 4.0 * o.K * u ? "PASS" : "FAIL");
+    }
+
+    cudaEvent_t e0, e1;
+    CUDA_OK(cudaEventCreate(&e0));
+    CUDA_OK(cudaEventCreate(&e1));
+    std::vector<double> ns;
+    for (unsigned s = 0; s < o.profile; s++) {
+        CUDA_OK(cudaEventRecord(e0, stream));
+        for (unsigned c = 0; c < o.apiCallCount; c++) st = call();
+        CUDA_OK(cudaEventRecord(e1, stream));
+        CUDA_OK(cudaEventSynchronize(e1));
+        float ms = 0;
+        CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+        ns.push_back((double)ms * 1e6);
+    }
+    if (st != clblasSuccess) { std::fprintf(stderr, "call failed with status %d\n", (int)st); return 3; }
+
+    auto mean_of = [](const std::vector<double>& v) { double s = 0; for (double x : v) s += x; return s / v.size(); };
+    double mean = mean_of(ns), var = 0;
+    for (double x : ns) var += (x - mean) * (x - mean);
+    const double sd = std::sqrt(var / ns.size());
+    std::vector<double> kept;
+    for (double x : ns) if (std::fabs(x - mean) <= 3.0 * sd || sd == 0) kept.push_back(x);
+    std::clog << "\tStatisticalTimer:: Pruning " << ns.size() - kept.size() << " samples from clfunc" << std::endl;
+    mean = mean_of(kept.empty() ? ns : kept);
+    const double per_call_ns = mean / o.apiCallCount;
+    double flop;
+    std::string formula;
+    if (gemm) { flop = 2.0 * o.M * o.N * o.K; formula = "2.0*M*N*K/time"; }
+    else if (o.side == 0) { flop = (double)o.M * (o.M + 1) * o.N; formula = "M*(M+1)*N/time"; }
+    else { flop = (double)o.M * (o.N + 1) * o.N; formula = "M*(N+1)*N/time"; }
+    const double gflops = flop / per_call_ns;
+    std::printf("BLAS kernel execution time < ns >: %.0f\n", per_call_ns);
+    std::printf("BLAS kernel execution Gflops < %s >: %.2f\n", formula.c_str(), gflops);
+    cudaDeviceProp prop;
+    CUDA_OK(cudaGetDeviceProperties(&prop, 0));
+    std::printf("m,n,k,lda,ldb,ldc,offa,offb,offc,alpha,beta,order,transa,transb,side,uplo,diag,function,device,library,label,GFLOPS\n");
+    std::printf("%zu,%zu,%zu,%zu,%zu,%zu,%zu,%zu,%zu,%g,%g,%s,%s,%s,%s,%s,%s,%s%s,%s,clblas_b200,%s,%.2f\n", o.M, o.N, o.K, lda, ldb, ldc,
+                o.offA, o.offB, o.offC, o.alpha, o.beta, o.order ? "column" : "row", o.transA ? "trans" : "none",
+                o.transB ? "trans" : "none", o.side ? "right" : "left", o.uplo ? "lower" : "upper", o.diag ? "nonunit" : "unit",
+                o.precision.c_str(), o.function.c_str(), prop.name, clblasB200LastGemmKernel(), gflops);
+
+    cudaFree(dA); cudaFree(dB); if (dC) cudaFree(dC);
+    cudaStreamDestroy(stream);
+    clblasTeardown();
+    return 0;
+}
+
+int main(int argc, char** argv)
+{
+    Options o;
+    if (!parse(argc, argv, o)) { usage(); return 1; }
+    if (o.function != "gemm" && o.function != "trsm") { std::fprintf(stderr, "function must be gemm or trsm\n"); return 1; }
+    if (o.precision == "s") return run<float>(o);
+    if (o.precision == "d") return run<double>(o);
+    std::fprintf(stderr, "precision must be s or d\n");
+    return 1;
+}

@@ -25,7 +25,7 @@ struct GemmProblem {
 };
 
 // Kernel families (reported by clblasB200LastGemmKernel).
-enum GemmPath { PATH_AUTO = 0, PATH_SIMT_LDG = 1 };
+enum GemmPath { PATH_AUTO = 0, PATH_SIMT_LDG = 1, PATH_TMA_ONE_CTA = 2, PATH_TMA_TWO_CTAS = 3 };
 
 void count_launch(unsigned n = 1);
 void set_last_kernel(const char* name);

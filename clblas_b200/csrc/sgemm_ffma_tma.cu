@@ -6,10 +6,15 @@
 // (src/library/blas/AutoGemm/UserGemmKernelSources/sgemm_Col_NT_B1_MX128_NX128_KX16_src.cpp),
 // and of the generator they come from (src/library/blas/AutoGemm/KernelOpenCL.py:13-459).
 //
-// CTA = 128 x 128 tile of C, K in slabs of 32.  Warp 8 is the producer (one lane issues two TMA
-// bulk-tensor loads per slab into a STAGES-deep shared-memory ring, full/empty mbarriers, bounded
-// waits); warps 0-7 are consumers, 16 x 16 threads with an 8 x 8 register tile each.  TMA
-// zero-fills beyond M, N, K, so one launch covers ragged shapes; the epilogue is predicated.
+// CTA = 128 x 128 tile of C, K in slabs of 32, 256 threads (16 x 16, an 8 x 8 register tile each).
+// Thread 0 doubles as the producer: part-way through every slab it refills the ring slot that was
+// consumed one slab earlier (two TMA bulk-tensor loads; full/empty mbarriers, bounded waits).
+// Two configurations of the same code:
+//   * 3-stage ring (97 KB), at most 128 registers per thread, TWO CTAs per SM: four warps per SM
+//     sub-partition hide each other's shared-memory latency and barrier waits;
+//   * 5-stage ring (161 KB), up to 255 registers, one CTA per SM: for the transpose case whose
+//     fragments need the registers (both operands K-contiguous).
+// TMA zero-fills beyond M, N, K, so one launch covers ragged shapes; the epilogue is predicated.
 //
 // Shared layouts:
 //  * M/N-contiguous operand (A for transA=N, B for transB=T): box 128 x 32 (k), dense rows of 128
@@ -19,7 +24,7 @@
 //    SWIZZLE_128B; a thread reads one float4 (4 consecutive k) per row, rows tx + 16*i for A so
 //    that the 8 lanes of a quarter warp hit 8 different swizzle phases: conflict free.  B rows are
 //    shared by the 16 lanes with equal ty (broadcast).
-// The inner loop works on 4 k at a time: 16 LDS.128 for 256 FFMA.
+// Per k: 4 LDS.128 for 64 FFMA (K-contiguous operands are fetched 4 k at a time).
 #include "common.h"
 #include "tma_pipeline.cuh"
 
@@ -28,16 +33,15 @@ namespace cb200 {
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int STAGES = 5;
 constexpr int OPERAND_BYTES = BM * BK * 4;          // 16 KB
 constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;
-constexpr int CONSUMER_WARPS = 8;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int THREADS = 256;
 constexpr int GROUP_M = 16;
 
-template <bool TA, bool TB>
-__global__ void __launch_bounds__(THREADS, 1)
+constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 + 256; }
+
+template <bool TA, bool TB, int STAGES, int MIN_CTAS>
+__global__ void __launch_bounds__(THREADS, MIN_CTAS)
 sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
                       unsigned tilesM, unsigned tilesN)
@@ -59,33 +63,30 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     }
     const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
     const int nk = (int)((K + BK - 1) / BK);
-    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], CONSUMER_WARPS);
+            mbar_init(&empty[s], THREADS / 32);
         }
         mbar_fence_init();
     }
     __syncthreads();
 
-    if (warp == CONSUMER_WARPS) {
-        if (lane == 0) {
-            tma_prefetch_descriptor(&mapA);
-            tma_prefetch_descriptor(&mapB);
-            for (int kt = 0; kt < nk; kt++) {
-                const int s = kt % STAGES;
-                if (kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) break;
-                unsigned char* sa = smem + s * STAGE_BYTES;
-                unsigned char* sb = sa + OPERAND_BYTES;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                const int k0 = kt * BK;
-                if (TA) tma_load_2d(sa, &mapA, k0, (int)m0, &full[s]); else tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
-                if (TB) tma_load_2d(sb, &mapB, (int)n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, (int)n0, &full[s]);
-            }
-        }
-        return;
+    auto issue = [&](int kt) {
+        const int s = kt % STAGES;
+        unsigned char* sa = smem + s * STAGE_BYTES;
+        unsigned char* sb = sa + OPERAND_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        const int k0 = kt * BK;
+        if (TA) tma_load_2d(sa, &mapA, k0, (int)m0, &full[s]); else tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
+        if (TB) tma_load_2d(sb, &mapB, (int)n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, (int)n0, &full[s]);
+    };
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&mapA);
+        tma_prefetch_descriptor(&mapB);
+        for (int kt = 0; kt < STAGES - 1 && kt < nk; kt++) issue(kt);
     }
 
     const int tid = threadIdx.x;
@@ -101,6 +102,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
 
+    bool alive = true;
     for (int kt = 0; kt < nk; kt++) {
         const int s = kt % STAGES;
         if (!mbar_wait(&full[s], (kt / STAGES) & 1)) break;
@@ -108,20 +110,19 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         const unsigned char* sb = sa + OPERAND_BYTES;
 #pragma unroll
         for (int kc = 0; kc < BK / 4; kc++) {
-            float a[4][8], b[4][8];
+            // Refill the slot consumed during the previous slab with the slab STAGES-1 ahead.  Done a
+            // quarter of the way into this slab: by then the other warps have released that slot,
+            // so the producer thread rarely waits.
+            if (kc == 2 && threadIdx.x == 0 && kt + STAGES - 1 < nk) {
+                if (kt >= 1) alive = mbar_wait(&empty[(kt - 1) % STAGES], ((kt - 1) / STAGES) & 1);
+                if (alive) issue(kt + STAGES - 1);
+            }
+            float a4[4][8], b4[4][8];
             if (TA) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const float4 v = *reinterpret_cast<const float4*>(sa + (tx + 16 * i) * 128 + ((kc ^ (tx & 7)) << 4));
-                    a[0][i] = v.x; a[1][i] = v.y; a[2][i] = v.z; a[3][i] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const float4 v0 = *reinterpret_cast<const float4*>(sa + (kc * 4 + q) * 512 + tx * 16);
-                    const float4 v1 = *reinterpret_cast<const float4*>(sa + (kc * 4 + q) * 512 + 256 + tx * 16);
-                    a[q][0] = v0.x; a[q][1] = v0.y; a[q][2] = v0.z; a[q][3] = v0.w;
-                    a[q][4] = v1.x; a[q][5] = v1.y; a[q][6] = v1.z; a[q][7] = v1.w;
+                    a4[0][i] = v.x; a4[1][i] = v.y; a4[2][i] = v.z; a4[3][i] = v.w;
                 }
             }
             if (!TB) {
@@ -129,23 +130,35 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
                 for (int j = 0; j < 8; j++) {
                     const int n = ty * 4 + (j & 3) + 64 * (j >> 2);
                     const float4 v = *reinterpret_cast<const float4*>(sb + n * 128 + ((kc ^ (n & 7)) << 4));
-                    b[0][j] = v.x; b[1][j] = v.y; b[2][j] = v.z; b[3][j] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const float4 v0 = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * 512 + ty * 16);
-                    const float4 v1 = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * 512 + 256 + ty * 16);
-                    b[q][0] = v0.x; b[q][1] = v0.y; b[q][2] = v0.z; b[q][3] = v0.w;
-                    b[q][4] = v1.x; b[q][5] = v1.y; b[q][6] = v1.z; b[q][7] = v1.w;
+                    b4[0][j] = v.x; b4[1][j] = v.y; b4[2][j] = v.z; b4[3][j] = v.w;
                 }
             }
 #pragma unroll
-            for (int q = 0; q < 4; q++)
+            for (int q = 0; q < 4; q++) {
+                float a[8], b[8];
+                if (TA) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) a[i] = a4[q][i];
+                } else {
+                    const float4 v0 = *reinterpret_cast<const float4*>(sa + (kc * 4 + q) * 512 + tx * 16);
+                    const float4 v1 = *reinterpret_cast<const float4*>(sa + (kc * 4 + q) * 512 + 256 + tx * 16);
+                    a[0] = v0.x; a[1] = v0.y; a[2] = v0.z; a[3] = v0.w;
+                    a[4] = v1.x; a[5] = v1.y; a[6] = v1.z; a[7] = v1.w;
+                }
+                if (!TB) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) b[j] = b4[q][j];
+                } else {
+                    const float4 v0 = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * 512 + ty * 16);
+                    const float4 v1 = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * 512 + 256 + ty * 16);
+                    b[0] = v0.x; b[1] = v0.y; b[2] = v0.z; b[3] = v0.w;
+                    b[4] = v1.x; b[5] = v1.y; b[6] = v1.z; b[7] = v1.w;
+                }
 #pragma unroll
                 for (int i = 0; i < 8; i++)
 #pragma unroll
-                    for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[q][i], b[q][j], acc[i][j]);
+                    for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
@@ -198,7 +211,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     }
 }
 
-template <bool TA, bool TB>
+template <bool TA, bool TB, int STAGES, int MIN_CTAS>
 cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
 {
     void* enc = get_tensor_map_encoder();
@@ -211,19 +224,30 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
     else    ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.K, p.N, p.ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorNotSupported;
 
+    constexpr int SMEM = smem_bytes(STAGES);
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB, STAGES, MIN_CTAS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
-    sgemm_ffma_tma_kernel<TA, TB><<<(unsigned)(tilesM * tilesN), THREADS, SMEM_BYTES, s>>>(
+    sgemm_ffma_tma_kernel<TA, TB, STAGES, MIN_CTAS><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN);
     count_launch();
     return cudaGetLastError();
+}
+
+template <int STAGES, int MIN_CTAS>
+cudaError_t launch_any(const GemmProblem<float>& p, cudaStream_t s)
+{
+    if (!p.ta && !p.tb) return launch<false, false, STAGES, MIN_CTAS>(p, s);
+    if (!p.ta && p.tb) return launch<false, true, STAGES, MIN_CTAS>(p, s);
+    if (p.ta && !p.tb) return launch<true, false, STAGES, MIN_CTAS>(p, s);
+    return launch<true, true, STAGES, MIN_CTAS>(p, s);
 }
 
 }  // namespace
@@ -235,10 +259,14 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s)
     const size_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     if (tiles >= (1u << 31)) return cudaErrorNotSupported;
     set_last_kernel("sgemm_ffma_tma");
-    if (!p.ta && !p.tb) return launch<false, false>(p, s);
-    if (!p.ta && p.tb) return launch<false, true>(p, s);
-    if (p.ta && !p.tb) return launch<true, false>(p, s);
-    return launch<true, true>(p, s);
+    const int forced = forced_gemm_path();
+    if (forced == PATH_TMA_ONE_CTA) return launch_any<5, 1>(p, s);
+    if (forced == PATH_TMA_TWO_CTAS) return launch_any<3, 2>(p, s);
+    // A K-contiguous operand is fetched 4 k at a time (32 fragment registers on top of the 64
+    // accumulators), which only the one-CTA configuration holds without spilling; measured at
+    // 8192^3: N/T 52.6 (two CTAs) vs 47.6 TFLOP/s (one), N/N 37.5 vs 41.6, T/N 24.8 vs 37.1, T/T 43.6 vs 46.5.
+    if (!p.ta && p.tb) return launch_any<3, 2>(p, s);
+    return launch_any<5, 1>(p, s);
 }
 
 unsigned sgemm_tma_fault_flag() { return read_wait_timeout_flag(); }

@@ -65,30 +65,31 @@ trtri_diag_kernel(const T* __restrict__ A, size_t lda, size_t n, bool lower, boo
         for (int jj = 0; jj < 4; jj++) x[ii][jj] = (tr + 16 * ii == tc + 32 * jj) ? T(1) : T(0);
     __syncthreads();
 
-    for (int k = 0; k < NB; k++) {
-        T* rb = rowbuf + (k & 1) * NB;
-        if (tr == (k & 15)) {
-            const T d = Ls[k * NB + k];
+    // k = 16*kb + kk: row k belongs to the threads with tr == kk, register row kb (kept a
+    // compile-time index so that x stays in registers).
 #pragma unroll
-            for (int ii = 0; ii < 8; ii++) {
-                if (ii == (k >> 4)) {
+    for (int kb = 0; kb < NB / 16; kb++) {
+#pragma unroll 1
+        for (int kk = 0; kk < 16; kk++) {
+            const int k = kb * 16 + kk;
+            T* rb = rowbuf + (k & 1) * NB;
+            if (tr == kk) {
+                const T rd = T(1) / Ls[k * NB + k];
 #pragma unroll
-                    for (int jj = 0; jj < 4; jj++) {
-                        x[ii][jj] = x[ii][jj] / d;
-                        rb[tc + 32 * jj] = x[ii][jj];
-                    }
+                for (int jj = 0; jj < 4; jj++) {
+                    x[kb][jj] = x[kb][jj] * rd;
+                    rb[tc + 32 * jj] = x[kb][jj];
                 }
             }
-        }
-        __syncthreads();
-        T xr[4];
+            __syncthreads();
+            T xr[4];
 #pragma unroll
-        for (int jj = 0; jj < 4; jj++) xr[jj] = rb[tc + 32 * jj];
+            for (int jj = 0; jj < 4; jj++) xr[jj] = rb[tc + 32 * jj];
 #pragma unroll
-        for (int ii = 0; ii < 8; ii++) {
-            const int i = tr + 16 * ii;
-            if (i > k) {
-                const T l = Ls[k * NB + i];
+            for (int ii = 0; ii < 8; ii++) {
+                if (ii < kb) continue;                       // rows above the current block row are final
+                if (ii == kb && tr <= kk) continue;          // rows up to k inside the block row are final
+                const T l = Ls[k * NB + tr + 16 * ii];
 #pragma unroll
                 for (int jj = 0; jj < 4; jj++) x[ii][jj] = fma(-l, xr[jj], x[ii][jj]);
             }

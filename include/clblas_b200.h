@@ -162,7 +162,8 @@ double clblasB200ProbePeak(int kind, double seconds);
  * ("dgemm_mma_tma", "sgemm_ffma_tma", "gemm_simt_ldg", ...).  Static storage; never NULL. */
 const char* clblasB200LastGemmKernel(void);
 /* Forces a kernel family for GEMM calls of the whole process: 0 = automatic dispatch,
- * 1 = always the alignment-free LDG path.  Returns the previous value. */
+ * 1 = always the alignment-free LDG path, 2 / 3 = SGEMM TMA path with one / two CTAs per SM
+ * (tuning aid; operands the TMA path cannot address still take the LDG path).  Returns the previous value. */
 int clblasB200SetGemmPath(int path);
 
 #ifdef __cplusplus
