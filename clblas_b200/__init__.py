@@ -67,7 +67,8 @@ def _load() -> ctypes.CDLL:
         f = getattr(lib, name)
         f.argtypes = [i, i, i, sz, sz, sz, ft, vp, sz, sz, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
-    for name, ft in (("clblasStrsm", ctypes.c_float), ("clblasDtrsm", ctypes.c_double)):
+    for name, ft in (("clblasStrsm", ctypes.c_float), ("clblasDtrsm", ctypes.c_double),
+                     ("clblasB200DtrsmNoAlloc", ctypes.c_double)):
         f = getattr(lib, name)
         f.argtypes = [i, i, i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
@@ -96,7 +97,7 @@ lib = _load()
 
 EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "clblasDgemm", "clblasStrsm",
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
-           "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak"]
+           "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -187,6 +188,19 @@ def clblasStrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, o
 def clblasDtrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
                 queues=None, wait=None, events=None) -> int:
     return _trsm(lib.clblasDtrsm, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                 queues, wait, events)
+
+
+NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = 4096, 8192
+
+
+def clblasB200DtrsmNoAlloc(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                           queues=None, wait=None, events=None) -> int:
+    """clblasDtrsm for callers that may not allocate device memory while running (a process whose
+    GPU memory all belongs to its own pool, a fixed-budget loop): the solve's workspace is a 12 MiB
+    array resident in the library, so no allocation happens.  Order of A <= 4096, other dimension of
+    B <= 8192, else clblasOutOfResources.  Calls that can overlap on the GPU share that array and race."""
+    return _trsm(lib.clblasB200DtrsmNoAlloc, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
                  queues, wait, events)
 
 

@@ -289,6 +289,40 @@ clblasStatus clblasDtrsm(clblasOrder order, clblasSide side, clblasUplo uplo, cl
                               nq, queues, nev, wait, events);
 }
 
+clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,
+                                    clblasDiag diag, size_t M, size_t N, double alpha, const clblasMem A, size_t offA,
+                                    size_t lda, clblasMem B, size_t offB, size_t ldb, unsigned nq, clblasQueue* queues,
+                                    unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    // Same checks, in the same order, as clblasDtrsm; then the size limit of the fixed scratch array.
+    clblasStatus st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u || (unsigned)transA > 2u || (unsigned)diag > 1u) return clblasInvalidValue;
+    const size_t msize = (side == clblasLeft) ? M : N;
+    if ((st = check_matrix_sizes(sizeof(double), order, transA, msize, msize, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(sizeof(double), order, clblasNoTrans, M, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    const size_t other = (side == clblasLeft) ? N : M;
+    if (msize > CLBLAS_B200_NOALLOC_MAX_ORDER || other > CLBLAS_B200_NOALLOC_MAX_OTHER) return clblasOutOfResources;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = dtrsm_colmajor_noalloc(right, lower, transA != clblasNoTrans, diag == clblasUnit, M, N, alpha,
+                                           static_cast<const double*>(A) + offA, lda, static_cast<double*>(B) + offB, ldb, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 clblasStatus clblasB200PlanShards(size_t total, unsigned parts, size_t align, size_t* bounds)
 {
     if (parts == 0 || bounds == nullptr) return clblasInvalidValue;

@@ -54,6 +54,11 @@ cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t 
                           const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
 void trsm_release_workspaces();
 
+// DTRSM on the fixed device-resident scratch array (no allocation); cudaErrorMemoryAllocation
+// when the problem exceeds the array.
+cudaError_t dtrsm_colmajor_noalloc(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, double alpha,
+                                   const double* A, size_t lda, double* B, size_t ldb, cudaStream_t s);
+
 // Sticky per-translation-unit flags set when a bounded mbarrier wait inside a kernel ran out.
 unsigned dgemm_tma_fault_flag();
 unsigned sgemm_tma_fault_flag();

@@ -14,6 +14,7 @@
 #include "common.h"
 
 #include <algorithm>
+#include <mutex>
 
 namespace cb200 {
 
@@ -238,6 +239,77 @@ void trsm_release_workspaces()
     cudaMemPool_t pool;
     if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) cudaMemPoolTrimTo(pool, 0);
     cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// DTRSM without any allocation: the workspace of the blocked solve (inverted diagonal blocks and
+// the staging panel) lives in a file-scope device array instead of coming from cudaMallocAsync.
+//
+// It is for callers that must not allocate device memory once they are running: a service that
+// hands the whole GPU to its own memory pool at start-up, or a control loop with a fixed memory
+// budget in which an allocation that synchronises the device or fails is not acceptable.
+//
+// The array has a fixed, modest size (12 MiB, held by every GPU that loads this library until the
+// process exits), which bounds the problem: order of A <= CLBLAS_B200_NOALLOC_MAX_ORDER and the other
+// dimension of B <= CLBLAS_B200_NOALLOC_MAX_OTHER.  All calls on a device share the one array: two
+// calls whose kernels can overlap on the GPU (different streams without an ordering between them)
+// race on it.  Nothing in it has to start from zero -- the inversion kernel writes every entry of
+// every inverted block and each leaf product fully overwrites the part of the panel that is read
+// back -- so contents left by an earlier call are harmless.
+constexpr size_t NOALLOC_MAX_ORDER = CLBLAS_B200_NOALLOC_MAX_ORDER;
+constexpr size_t NOALLOC_MAX_OTHER = CLBLAS_B200_NOALLOC_MAX_OTHER;
+constexpr size_t NOALLOC_INV_ELEMS = NOALLOC_MAX_ORDER * NB;           // NB*NB per diagonal block
+constexpr size_t NOALLOC_TMP_ELEMS = (size_t)NB * NOALLOC_MAX_OTHER;
+static __device__ __align__(256) double g_dtrsm_noalloc_scratch[NOALLOC_INV_ELEMS + NOALLOC_TMP_ELEMS];
+
+// In host code the array's name is only a handle; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static cudaError_t noalloc_scratch_address(double** out)
+{
+    static std::mutex mu;
+    static double* addr[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+        double* p = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_dtrsm_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(trtri_diag_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)((size_t)(NB * NB + 2 * NB) * sizeof(double)));
+        if (e != cudaSuccess) return e;
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return cudaSuccess;
+}
+
+cudaError_t dtrsm_colmajor_noalloc(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, double alpha,
+                                   const double* A, size_t lda, double* B, size_t ldb, cudaStream_t s)
+{
+    if (M == 0 || N == 0) return cudaSuccess;
+    const size_t n = right ? N : M, other = right ? M : N;
+    if (n > NOALLOC_MAX_ORDER || other > NOALLOC_MAX_OTHER) return cudaErrorMemoryAllocation;
+    if (alpha == 0.0) return launch_scale<double>(M, N, 0.0, B, ldb, s);
+
+    double* ws = nullptr;
+    cudaError_t e = noalloc_scratch_address(&ws);
+    if (e != cudaSuccess) return e;
+
+    TrsmCtx<double> c;
+    c.right = right; c.lower = lower; c.trans = trans; c.eff_lower = (lower != trans);
+    c.M = M; c.N = N; c.n = n; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.s = s;
+    c.inv = ws;
+    c.tmp = ws + NOALLOC_INV_ELEMS;
+    const size_t nblk = (n + NB - 1) / NB;
+    const size_t smem = (size_t)(NB * NB + 2 * NB) * sizeof(double);
+    trtri_diag_kernel<double><<<(unsigned)nblk, TRTRI_THREADS, smem, s>>>(A, lda, n, lower, unit, c.inv);
+    count_launch();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return solve_range<double>(c, 0, nblk, alpha);
 }
 
 template cudaError_t trsm_colmajor<float>(bool, bool, bool, bool, size_t, size_t, float, const float*, size_t,

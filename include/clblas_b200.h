@@ -136,6 +136,33 @@ clblasStatus clblasDtrsm(
     unsigned numCommandQueues, clblasQueue* commandQueues,
     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
 
+/* ---- DTRSM that allocates nothing (no counterpart in the reference, whose DTRSM creates and
+ *      releases two OpenCL buffers inside every call, src/library/blas/xtrsm.cc:1183-1207).
+ *      Same arguments, checks and result as clblasDtrsm, but the blocked solve's workspace is a
+ *      fixed 12 MiB array that lives in device memory for as long as the library is loaded, so the
+ *      call makes no cudaMalloc / cudaMallocAsync / cudaFree of any kind.  It is meant for callers
+ *      that must not allocate while running: a server that gave all device memory to its own pool
+ *      at start-up, or a loop with a fixed memory budget where an allocation that stalls or fails
+ *      is not acceptable.
+ *      Limits: order of A (M for Left, N for Right) <= CLBLAS_B200_NOALLOC_MAX_ORDER and the other
+ *      dimension of B <= CLBLAS_B200_NOALLOC_MAX_OTHER; larger problems return
+ *      clblasOutOfResources and touch nothing.
+ *      The first call on each device looks up the array's device address and sets a kernel
+ *      attribute; make that first call before starting any stream capture.
+ *      Every call on a device uses the same array: calls that may overlap on the GPU (streams with
+ *      no ordering between them) race and give wrong results -- order them on one stream or with
+ *      events.  What an earlier call left in the array never influences a later one. */
+#define CLBLAS_B200_NOALLOC_MAX_ORDER 4096
+#define CLBLAS_B200_NOALLOC_MAX_OTHER 8192
+clblasStatus clblasB200DtrsmNoAlloc(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    double alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- partition planning: replaces the per-queue problem split of
  *      src/library/blas/generic/solution_seq_make.c:764-866 (stripeDivision over the N
  *      dimension, pieces aligned to DIVISION_ALIGNMENT = 128).
