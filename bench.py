@@ -125,7 +125,7 @@ class GemmWorkload(Workload):
         from clblas_b200 import partition
         assert self.order == cb.clblasColumnMajor and self.offs == (0, 0, 0)
         return partition.gemm_column_sharded(self.prec, self.transA, self.transB, self.M, nl, self.K, self.alpha,
-                                             A, self.lda, B, self.ldb, self.beta, C, self.ldc, root=0, panels=8)
+                                             A, self.lda, B, self.ldb, self.beta, C, self.ldc, root=0)
 
     def config(self, world):
         return {"workload": f"{self.name}: {self.desc}", "M": self.M, "N": self.N * (world if self.scaling == "weak" else 1),

@@ -41,8 +41,20 @@ cudaError_t launch_gemm_simt(const GemmProblem<T>& p, cudaStream_t s);
 
 // TMA-staged paths (need 16-byte aligned bases and leading dimensions); return
 // cudaErrorNotSupported when the problem does not meet their requirements.
-cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s);
+// min_bn: 0 = choose the tile width from the shape; 128 = never use the narrow-tile variants.
+cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s, int min_bn = 0);
 cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s);
+
+// Copies (or transposes) a rows x cols column-major operand into an aligned workspace.
+template <typename T>
+cudaError_t launch_repack(T* dst, size_t ldd, const T* src, size_t lds, size_t rows, size_t cols, bool transpose,
+                          cudaStream_t s);
+
+// While one of these is alive on a thread, gemm_colmajor never allocates (no operand repacking).
+struct ScopedNoAlloc {
+    ScopedNoAlloc();
+    ~ScopedNoAlloc();
+};
 
 // Dispatcher keyed on precision, transposes, shape and alignment.
 template <typename T>
@@ -53,6 +65,11 @@ template <typename T>
 cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
                           const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
 void trsm_release_workspaces();
+
+// Stream-ordered workspace from the library's own per-device pool (workspace.cu).
+cudaError_t ws_alloc(void** ptr, size_t bytes, cudaStream_t s);
+cudaError_t ws_free(void* ptr, cudaStream_t s);
+void ws_release_all();
 
 // DTRSM on the fixed device-resident scratch array (no allocation); cudaErrorMemoryAllocation
 // when the problem exceeds the array.

@@ -5,10 +5,11 @@
 // src/library/blas/AutoGemm/KernelOpenCL.py:13-459; hand-tuned 48x48 kernel
 // src/library/blas/AutoGemm/UserGemmKernelSources/dgemm_Col_TN_B1_MX048_NX048_KX08_src.cpp).
 //
-// CTA = 128 x 128 tile of C, K in slabs of 16.  Warp 8 is the producer: one lane issues two TMA
+// CTA = 128 x BN tile of C (BN = 128; 64 or 32 for problems too narrow to fill the SMs with 128-wide
+// tiles, e.g. the panel products of TRSM), K in slabs of 16.  Warp 8 is the producer: one lane issues two TMA
 // bulk-tensor loads per slab (A and B) into a STAGES-deep ring in shared memory; full/empty
 // mbarriers carry the hand-over, all waits are bounded.  Warps 0-7 are consumers (2 x 4 grid,
-// 64 x 32 of C each, 128 accumulator registers per thread) issuing mma.sync.m8n8k4.f64.
+// 64 x BN/4 of C each, up to 128 accumulator registers per thread) issuing mma.sync.m8n8k4.f64.
 // TMA zero-fills whatever lies beyond M, N or K, so ragged shapes need no separate edge launches
 // (the reference runs tile + row + column + corner kernels, src/library/blas/xgemm.cc:603-658);
 // only the epilogue is predicated.
@@ -18,9 +19,9 @@
 //    16 (k) x 128 rows, 128-byte rows, SWIZZLE_128B.  Within every group of 8 rows the fragment row
 //    g reads tile row 2*(g%4) + g/4, which spreads a half-warp over all 32 banks; the epilogue
 //    applies the same permutation to the C coordinates.
-//  * operand whose M/N index is contiguous (A for transA=N, B for transB=T): box 132 x 16 (k),
-//    i.e. rows of 132 doubles of which 128 are used: the 4 extra elements make the row pitch
-//    1056 bytes = 32 (mod 128), which is what separates the four k rows of a fragment.
+//  * operand whose M/N index is contiguous (A for transA=N, B for transB=T): box (tile + 4) x 16 (k),
+//    i.e. rows of 132 (68, 36) doubles of which 128 (64, 32) are used: the 4 extra elements make the
+//    row pitch = 32 (mod 128) bytes, which is what separates the four k rows of a fragment.
 #include "common.h"
 #include "tma_pipeline.cuh"
 
@@ -28,15 +29,18 @@ namespace cb200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int BM = 128, BK = 16;
 constexpr int STAGES = 5;
-constexpr int MC_PITCH = 132;                       // doubles per k row, M/N-contiguous layout
-constexpr int OPERAND_BYTES = 17 * 1024;            // >= max(128*16*8, 16*132*8), multiple of 1024
-constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;
+constexpr int MC_PITCH = BM + 4;                    // doubles per k row of A, M-contiguous layout
+constexpr int A_BYTES = 17 * 1024;                  // >= max(128*16*8, 16*132*8), multiple of 1024
 constexpr int CONSUMER_WARPS = 8;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int GROUP_M = 16;                         // tile rows per rasterisation group
+
+// B operand buffer: max(BN rows of 128 bytes, 16 rows of (BN+4)*8 bytes), rounded up to 1 KB
+constexpr int b_bytes(int bn) { return ((16 * (bn + 4) * 8 + 1023) / 1024) * 1024; }
+constexpr int stage_bytes(int bn) { return A_BYTES + b_bytes(bn); }
+constexpr int smem_bytes(int bn) { return STAGES * stage_bytes(bn) + 1024 /*alignment slack*/ + 256 /*barriers*/; }
 
 __device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b)
 {
@@ -47,7 +51,7 @@ __device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b)
 __device__ __forceinline__ int perm8(int g) { return 2 * (g & 3) + (g >> 2); }
 
 // TA: A is stored K x M (K contiguous).  TB: B is stored N x K (N contiguous).
-template <bool TA, bool TB>
+template <bool TA, bool TB, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      double* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, double alpha, double beta,
@@ -55,6 +59,9 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
 {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int STAGE_BYTES = stage_bytes(BN);
+    constexpr int PITCH_B = BN + 4;                 // doubles per k row of B, N-contiguous layout
+    constexpr int WN = BN / 4, NI = WN / 8;         // warp tile width, 8-wide sub-tiles per warp
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
 
@@ -91,8 +98,8 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
                 const int s = kt % STAGES;
                 if (kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) break;
                 unsigned char* sa = smem + s * STAGE_BYTES;
-                unsigned char* sb = sa + OPERAND_BYTES;
-                const uint32_t bytes = (TA ? BK * BM : MC_PITCH * BK) * 8 + (TB ? MC_PITCH * BK : BK * BN) * 8;
+                unsigned char* sb = sa + A_BYTES;
+                const uint32_t bytes = (TA ? BK * BM : MC_PITCH * BK) * 8 + (TB ? PITCH_B * BK : BK * BN) * 8;
                 mbar_expect_tx(&full[s], bytes);
                 const int k0 = kt * BK;
                 if (TA) tma_load_2d(sa, &mapA, k0, (int)m0, &full[s]); else tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
@@ -103,7 +110,7 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
 
     // --------------------------------- consumers ---------------------------------
-    const int wm = warp % 2, wn = warp / 2;          // 2 x 4 warps, 64 x 32 each
+    const int wm = warp % 2, wn = warp / 2;          // 2 x 4 warps, 64 x WN each
     const int g = lane / 4, kk = lane % 4;
     const int pg = perm8(g);
 
@@ -112,24 +119,24 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     int offA, offB;
     if (TA) offA = (wm * 64 + pg) * 128 + ((((kk >> 1) ^ (pg & 1))) << 4) + (kk & 1) * 8;
     else    offA = kk * (MC_PITCH * 8) + (wm * 64 + g) * 8;
-    if (!TB) offB = (wn * 32 + pg) * 128 + ((((kk >> 1) ^ (pg & 1))) << 4) + (kk & 1) * 8;
-    else     offB = kk * (MC_PITCH * 8) + (wn * 32 + g) * 8;
+    if (!TB) offB = (wn * WN + pg) * 128 + ((((kk >> 1) ^ (pg & 1))) << 4) + (kk & 1) * 8;
+    else     offB = kk * (PITCH_B * 8) + (wn * WN + g) * 8;
     const int xr = (pg & 6) << 4;                    // swizzle XOR applied to the 32-byte chunk of a k-step
 
-    double acc[8][4][2];
+    double acc[8][NI][2];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j][0] = acc[i][j][1] = 0.0;
+        for (int j = 0; j < NI; j++) acc[i][j][0] = acc[i][j][1] = 0.0;
 
     for (int kt = 0; kt < nk; kt++) {
         const int s = kt % STAGES;
         if (!mbar_wait(&full[s], (kt / STAGES) & 1)) break;
         const unsigned char* sa = smem + s * STAGE_BYTES;
-        const unsigned char* sb = sa + OPERAND_BYTES;
+        const unsigned char* sb = sa + A_BYTES;
 #pragma unroll
         for (int ks = 0; ks < BK / 4; ks++) {
-            double a[8], b[4];
+            double a[8], b[NI];
 #pragma unroll
             for (int mi = 0; mi < 8; mi++) {
                 const int o = TA ? offA + mi * 1024 + (((ks * 32) ^ xr))
@@ -137,15 +144,15 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
                 a[mi] = *reinterpret_cast<const double*>(sa + o);
             }
 #pragma unroll
-            for (int ni = 0; ni < 4; ni++) {
+            for (int ni = 0; ni < NI; ni++) {
                 const int o = !TB ? offB + ni * 1024 + (((ks * 32) ^ xr))
-                                  : offB + ks * 4 * (MC_PITCH * 8) + ni * 64;
+                                  : offB + ks * 4 * (PITCH_B * 8) + ni * 64;
                 b[ni] = *reinterpret_cast<const double*>(sb + o);
             }
 #pragma unroll
             for (int mi = 0; mi < 8; mi++)
 #pragma unroll
-                for (int ni = 0; ni < 4; ni++) dmma(acc[mi][ni][0], acc[mi][ni][1], a[mi], b[ni]);
+                for (int ni = 0; ni < NI; ni++) dmma(acc[mi][ni][0], acc[mi][ni][1], a[mi], b[ni]);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
@@ -154,11 +161,11 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
     const bool useC = (beta != 0.0);
 #pragma unroll
-    for (int ni = 0; ni < 4; ni++)
+    for (int ni = 0; ni < NI; ni++)
 #pragma unroll
         for (int e = 0; e < 2; e++) {
             const int j = 2 * kk + e;
-            const size_t col = n0 + wn * 32 + ni * 8 + (!TB ? perm8(j) : j);
+            const size_t col = n0 + wn * WN + ni * 8 + (!TB ? perm8(j) : j);
             if (col >= N) continue;
             double* cc = C + col * ldc;
 #pragma unroll
@@ -172,7 +179,7 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         }
 }
 
-template <bool TA, bool TB>
+template <bool TA, bool TB, int BN>
 cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
 {
     void* enc = get_tensor_map_encoder();
@@ -181,7 +188,7 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
     if (TA) ok = make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.A, p.K, p.M, p.lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
     else    ok = make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.A, p.M, p.K, p.lda, MC_PITCH, BK, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) return cudaErrorNotSupported;
-    if (TB) ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.B, p.N, p.K, p.ldb, MC_PITCH, BK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (TB) ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.B, p.N, p.K, p.ldb, BN + 4, BK, CU_TENSOR_MAP_SWIZZLE_NONE);
     else    ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.B, p.K, p.N, p.ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorNotSupported;
 
@@ -189,31 +196,41 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(dgemm_mma_tma_kernel<TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(dgemm_mma_tma_kernel<TA, TB, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN));
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
-    dgemm_mma_tma_kernel<TA, TB><<<(unsigned)(tilesM * tilesN), THREADS, SMEM_BYTES, s>>>(
+    dgemm_mma_tma_kernel<TA, TB, BN><<<(unsigned)(tilesM * tilesN), THREADS, smem_bytes(BN), s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN);
     count_launch();
     return cudaGetLastError();
 }
 
+template <int BN>
+cudaError_t launch_t(const GemmProblem<double>& p, cudaStream_t s)
+{
+    if (!p.ta && !p.tb) return launch<false, false, BN>(p, s);
+    if (!p.ta && p.tb) return launch<false, true, BN>(p, s);
+    if (p.ta && !p.tb) return launch<true, false, BN>(p, s);
+    return launch<true, true, BN>(p, s);
+}
+
 }  // namespace
 
-cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s)
+cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s, int min_bn)
 {
     // TMA needs 16-byte aligned global addresses and strides; coordinates are 32-bit.
     if (!aligned16(p.A) || !aligned16(p.B) || (p.lda & 1) || (p.ldb & 1)) return cudaErrorNotSupported;
     if (p.M >= (1u << 31) || p.N >= (1u << 31) || p.K >= (1u << 31)) return cudaErrorNotSupported;
-    const size_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-    if (tiles >= (1u << 31)) return cudaErrorNotSupported;
+    const size_t tilesM = (p.M + BM - 1) / BM;
+    if (tilesM * ((p.N + 31) / 32) >= (1u << 31)) return cudaErrorNotSupported;
     set_last_kernel("dgemm_mma_tma");
-    if (!p.ta && !p.tb) return launch<false, false>(p, s);
-    if (!p.ta && p.tb) return launch<false, true>(p, s);
-    if (p.ta && !p.tb) return launch<true, false>(p, s);
-    return launch<true, true>(p, s);
+    // Widest tile that still gives the 148 SMs about one CTA each; narrower tiles only for
+    // problems that 128-wide tiles would leave most SMs idle on.
+    if (min_bn >= 128 || tilesM * ((p.N + 127) / 128) >= 120) return launch_t<128>(p, s);
+    if (tilesM * ((p.N + 63) / 64) >= 120) return launch_t<64>(p, s);
+    return launch_t<32>(p, s);
 }
 
 unsigned dgemm_tma_fault_flag() { return read_wait_timeout_flag(); }

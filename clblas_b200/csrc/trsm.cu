@@ -128,6 +128,15 @@ cudaError_t gemm_call(bool ta, bool tb, size_t M, size_t N, size_t K, T alpha, c
     return gemm_colmajor<T>(p, s);
 }
 
+// TMA-staged product whose output aliases one of its inputs (see solve_leaf); NotSupported when the
+// operands are not TMA-addressable.  For the FP64 kernel the tile must span all 128 columns when the
+// aliased operand is A (Right side), so the narrow-tile variants are excluded there.
+inline cudaError_t launch_tma_inplace(const GemmProblem<float>& p, cudaStream_t s) { return launch_sgemm_ffma_tma(p, s); }
+inline cudaError_t launch_tma_inplace(const GemmProblem<double>& p, cudaStream_t s)
+{
+    return launch_dgemm_mma_tma(p, s, p.C == p.A ? 128 : 0);
+}
+
 // X_b = alpha * op(inv_b) * B_b (Left) or alpha * B_b * op(inv_b) (Right) for diagonal block b.
 template <typename T>
 cudaError_t solve_leaf(const TrsmCtx<T>& c, size_t b, T alpha)
@@ -135,6 +144,18 @@ cudaError_t solve_leaf(const TrsmCtx<T>& c, size_t b, T alpha)
     const size_t r = b * NB, nv = std::min<size_t>(NB, c.n - r);
     const T* invb = c.inv + b * (size_t)(NB * NB);
     cudaError_t e;
+    // In place when the TMA kernels can take the panel: their CTA tile is 128 rows (Left) or 128
+    // columns (Right) = the whole block, so each CTA reads exactly the part of B it later overwrites,
+    // and reads all of it (every K slab) before its epilogue stores; beta = 0 never reads C.
+    {
+        T* Bb = c.right ? c.B + r * c.ldb : c.B + r;
+        GemmProblem<T> p;
+        p.alpha = alpha; p.beta = T(0); p.C = Bb; p.ldc = c.ldb; p.K = nv;
+        if (!c.right) { p.ta = c.trans; p.tb = false; p.M = nv; p.N = c.N; p.A = invb; p.lda = NB; p.B = Bb; p.ldb = c.ldb; }
+        else          { p.ta = false; p.tb = c.trans; p.M = c.M; p.N = nv; p.A = Bb; p.lda = c.ldb; p.B = invb; p.ldb = NB; }
+        e = launch_tma_inplace(p, c.s);
+        if (e != cudaErrorNotSupported) return e;
+    }
     if (!c.right) {
         T* Bb = c.B + r;
         e = gemm_call<T>(c.trans, false, nv, c.N, nv, alpha, invb, NB, Bb, c.ldb, T(0), c.tmp, nv, c.s);
@@ -208,7 +229,7 @@ cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t 
     const size_t tmp_elems = (size_t)NB * (right ? M : N);
 
     T* ws = nullptr;
-    cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&ws), (inv_elems + tmp_elems) * sizeof(T), s);
+    cudaError_t e = ws_alloc(reinterpret_cast<void**>(&ws), (inv_elems + tmp_elems) * sizeof(T), s);
     if (e != cudaSuccess) return e;
     c.inv = ws;
     c.tmp = ws + inv_elems;
@@ -221,25 +242,18 @@ cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t 
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[ti][dev]) {
         e = cudaFuncSetAttribute(trtri_diag_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { cudaFreeAsync(ws, s); return e; }
+        if (e != cudaSuccess) { ws_free(ws, s); return e; }
         if (dev >= 0 && dev < 64) attr_done[ti][dev] = true;
     }
     trtri_diag_kernel<T><<<(unsigned)nblk, TRTRI_THREADS, smem, s>>>(A, lda, c.n, lower, unit, c.inv);
     count_launch();
     e = cudaGetLastError();
     if (e == cudaSuccess) e = solve_range<T>(c, 0, nblk, alpha);
-    cudaError_t e2 = cudaFreeAsync(ws, s);
+    cudaError_t e2 = ws_free(ws, s);
     return e != cudaSuccess ? e : e2;
 }
 
-void trsm_release_workspaces()
-{
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return; }
-    cudaMemPool_t pool;
-    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) cudaMemPoolTrimTo(pool, 0);
-    cudaGetLastError();
-}
+void trsm_release_workspaces() { ws_release_all(); }
 
 // ---------------------------------------------------------------------------------------------
 // DTRSM without any allocation: the workspace of the blocked solve (inverted diagonal blocks and
@@ -297,6 +311,7 @@ cudaError_t dtrsm_colmajor_noalloc(bool right, bool lower, bool trans, bool unit
     double* ws = nullptr;
     cudaError_t e = noalloc_scratch_address(&ws);
     if (e != cudaSuccess) return e;
+    ScopedNoAlloc no_alloc;          // the GEMM dispatcher must not repack operands into a workspace here
 
     TrsmCtx<double> c;
     c.right = right; c.lower = lower; c.trans = trans; c.eff_lower = (lower != trans);

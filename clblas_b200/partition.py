@@ -50,7 +50,7 @@ def _default_trsm(prec: str) -> Callable:
 
 def gemm_column_sharded(prec: str, transA: int, transB: int, M: int, n_local: int, K: int, alpha: float,
                         A: torch.Tensor, lda: int, B_local: torch.Tensor, ldb: int, beta: float,
-                        C_local: torch.Tensor, ldc: int, *, root: int = 0, panels: int = 8,
+                        C_local: torch.Tensor, ldc: int, *, root: int = 0, panels: Optional[int] = None,
                         group: Optional[dist.ProcessGroup] = None, gemm_fn: Optional[Callable] = None) -> int:
     """Column-major C_local <- alpha*op(A)*op(B)_local + beta*C_local on every rank.
 
@@ -63,6 +63,10 @@ def gemm_column_sharded(prec: str, transA: int, transB: int, M: int, n_local: in
     tb = transB != cb.clblasNoTrans
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     a_cols = M if ta else K                     # columns of A as stored
+    if panels is None:
+        # K-slabs keep every tile of C in each launch, so many thin slabs cost nothing; row blocks of C
+        # shrink the grid of each launch, so they stay large enough for several full waves of CTAs.
+        panels = 8 if not ta else max(1, min(4, (M * max(n_local, 1)) // (128 * 128 * 148 * 6)))
     plan = panel_plan(a_cols, panels if world > 1 else 1)
 
     works = []

@@ -141,8 +141,25 @@ def test_config3_sgemm_rowmajor_ragged(lib):
     c = cases.gemm_case("s", RowMajor, Trans, NoTrans, 4099, 3001, 1537, alpha=-2.0, beta=0.25,
                         pad=(16, 32, 8), off=(7, 13, 5))
     assert (c["lda"], c["ldb"], c["ldc"]) == (4099 + 16, 3001 + 32, 3001 + 8)
+    # automatic dispatch: operands are copied once into an aligned workspace, then the TMA kernel runs
     check_real(lib, c)
-    assert lib.last_gemm_kernel() == "gemm_simt_ldg"
+    assert lib.last_gemm_kernel() == "sgemm_ffma_tma"
+    # the alignment-free kernel on the same problem, in place
+    old = lib.set_gemm_path(1)
+    try:
+        check_real(lib, c)
+        assert lib.last_gemm_kernel() == "gemm_simt_ldg"
+        ci = cases.gemm_case("s", RowMajor, Trans, NoTrans, 4099, 3001, 1537, alpha=-2.0, beta=3.0,
+                             pad=(16, 32, 8), off=(7, 13, 5), mode="int")
+        bufs = cases.gemm_buffers(ci)
+        st, got_simt = run_gemm_gpu(lib, ci, bufs)
+        assert st == lib.clblasSuccess
+    finally:
+        lib.set_gemm_path(old)
+    # integer-valued inputs: both routes give the same bits, padding and offsets untouched
+    st, got_auto = run_gemm_gpu(lib, ci, bufs)
+    assert st == lib.clblasSuccess and same_bits(got_auto, got_simt)
+    assert outside_untouched(bufs[2], got_auto, ci)
 
 
 def _aligned_case(prec, order, ta, tb, M, N, K, seed, mode="int", alpha=2.0, beta=3.0):
@@ -191,3 +208,28 @@ def test_config2_shape_family_dgemm_tn(lib):
     r = check_real(lib, c)
     assert lib.last_gemm_kernel() == "dgemm_mma_tma"
     assert r <= 1.0
+
+
+@pytest.mark.parametrize("prec", ["s", "d"])
+def test_repacked_operands_exact(lib, prec):
+    """Large products whose operands TMA cannot address (odd leading dimensions, offset bases) or, for
+    SGEMM, whose operands are K-contiguous: the dispatcher copies / transposes them into an aligned
+    workspace first.  Integer-valued inputs, compared bit for bit with the exact float64 product."""
+    dt = cases.DT[prec]
+    seed = 30000
+    for order in (ColumnMajor, RowMajor):
+        for ta in (NoTrans, Trans):
+            for tb in (NoTrans, Trans):
+                seed += 1
+                M, N, K = 2049, 2111, 2053
+                c = cases.gemm_case(prec, order, ta, tb, M, N, K, alpha=2.0, beta=-1.0, pad=(3, 5, 1), off=(1, 2, 3),
+                                    mode="int", seed=seed)
+                opA, opB, C = cases.gemm_logical(c)
+                bufs = cases.gemm_buffers(c, (opA, opB, C))
+                st, got = run_gemm_gpu(lib, c, bufs)
+                assert st == lib.clblasSuccess
+                assert lib.last_gemm_kernel().endswith("_tma"), lib.last_gemm_kernel()
+                want = (2.0 * (opA.astype(np.float64) @ opB.astype(np.float64)) - C.astype(np.float64)).astype(dt)
+                assert np.array_equal(oracle.view(got, order, NoTrans, M, N, c["ldc"], c["offC"]), want), c
+                assert outside_untouched(bufs[2], got, c)
+    assert lib.device_fault() == 0
