@@ -25,7 +25,11 @@ struct GemmProblem {
 };
 
 // Kernel families (reported by clblasB200LastGemmKernel).
-enum GemmPath { PATH_AUTO = 0, PATH_SIMT_LDG = 1, PATH_TMA_ONE_CTA = 2, PATH_TMA_TWO_CTAS = 3 };
+enum GemmPath { PATH_AUTO = 0, PATH_SIMT_LDG = 1, PATH_TMA_ONE_CTA = 2, PATH_TMA_TWO_CTAS = 3, PATH_3XTF32 = 4 };
+
+// Optional SGEMM on tcgen05 tensor cores with the 3xTF32 operand split (opt-in, PATH_3XTF32).
+cudaError_t launch_sgemm_3xtf32(const GemmProblem<float>& p, cudaStream_t s);
+unsigned sgemm_3xtf32_fault_flag();
 
 void count_launch(unsigned n = 1);
 void set_last_kernel(const char* name);

@@ -47,6 +47,9 @@ bool tma_addressable(const T* ptr, size_t ld)
     return aligned16(ptr) && (ld * sizeof(T)) % 16 == 0;
 }
 
+inline cudaError_t try_3xtf32(const GemmProblem<float>& p, cudaStream_t s) { return launch_sgemm_3xtf32(p, s); }
+inline cudaError_t try_3xtf32(const GemmProblem<double>&, cudaStream_t) { return cudaErrorNotSupported; }
+
 // What to do with one operand before the product.
 enum Fix { KEEP, COPY, TRANSPOSE };
 
@@ -57,6 +60,10 @@ cudaError_t gemm_any(const GemmProblem<T>& p, cudaStream_t s)
     cudaError_t e = degenerate(p, s, &handled);
     if (handled) return e;
     if (forced_gemm_path() == PATH_SIMT_LDG) return launch_gemm_simt<T>(p, s);
+    if (forced_gemm_path() == PATH_3XTF32 && t_forbid_alloc == 0) {
+        e = try_3xtf32(p, s);
+        if (e != cudaErrorNotSupported) return e;
+    }
 
     constexpr bool kFloat = sizeof(T) == 4;
     // stored extents: rows are the contiguous direction
