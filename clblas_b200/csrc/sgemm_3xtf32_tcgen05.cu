@@ -7,15 +7,18 @@
 // The reference has no counterpart (its sgemm kernels are scalar mad() code,
 // src/library/blas/AutoGemm/KernelOpenCL.py:171-181).
 //
-// CTA = 128 x 256 tile of C, K in slabs of 32 (one 128-byte swizzle row), 6 warps:
-//   warp 0    producer: TMA loads of the A and B slabs (both K-contiguous, SWIZZLE_128B), ring of 2;
+// CTA = 128 x 256 tile of C, K in slabs of 16 (64-byte swizzled rows), ring of 4 slabs, 10 warps:
+//   warp 0    producer: TMA loads of the A and B slabs (both K-contiguous, SWIZZLE_64B), issued
+//             three slabs ahead of the tensor core;
 //   warp 1    owns tensor memory (tcgen05.alloc / dealloc, 256 columns) and issues the MMAs: per 8-wide
 //             k step three tcgen05.mma.kind::tf32 (M=128, N=256, K=8) reading shared-memory descriptors;
 //             tcgen05.commit releases the ring slot and, at the end, publishes the accumulator;
-//   warps 2-5 splitters: rewrite each raw slab in place as `hi` and write `lo` next to it (same
-//             swizzled layout, so the split is element-wise), then fence.proxy.async and hand the slot
-//             to warp 1; after the last slab they are the epilogue: tcgen05.ld of their quarter of the
-//             128 accumulator lanes, alpha/beta, coalesced stores.
+//   warps 2-9 splitters: rewrite each raw slab in place as `hi` and write `lo` next to it (same
+//             swizzled layout, so the split is element-wise; rounding is done with integer adds and
+//             masks, the conversion instruction is a quarter-rate pipe), then fence.proxy.async and
+//             hand the slot to warp 1; after the last slab they are the epilogue: tcgen05.ld of their
+//             quarter of the 128 accumulator lanes (two warps share a quarter, half the columns each),
+//             alpha/beta, coalesced stores.
 // Every wait is bounded; all roles meet at one barrier before tensor memory is freed.
 // Operands that are not K-contiguous (A for transA=N, B for transB=T) or not 16-byte aligned are
 // transposed / copied into a workspace first (repack.cu).
@@ -26,12 +29,14 @@ namespace cb200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 32;
-constexpr int STAGES = 2;
-constexpr int A_BYTES = BM * BK * 4;                 // 16 KB
-constexpr int B_BYTES = BN * BK * 4;                 // 32 KB
-constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES); // raw/hi + lo for both operands
-constexpr int THREADS = 192;
+constexpr int BM = 128, BN = 256, BK = 16;
+constexpr int STAGES = 4;
+constexpr int ROW_BYTES = BK * 4;                    // 64-byte rows: SWIZZLE_64B
+constexpr int A_BYTES = BM * ROW_BYTES;              // 8 KB
+constexpr int B_BYTES = BN * ROW_BYTES;              // 16 KB
+constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES); // raw/hi + lo for both operands: 48 KB
+constexpr int SPLIT_WARPS = 8;
+constexpr int THREADS = (2 + SPLIT_WARPS) * 32;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int TMEM_COLS = BN;                        // one FP32 column per accumulator column
 constexpr int GROUP_M = 16;
@@ -39,15 +44,15 @@ constexpr int GROUP_M = 16;
 // tcgen05 instruction descriptor, kind::tf32: D = F32, A = B = TF32, both K-major, N = 256, M = 128
 constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
-// Shared-memory matrix descriptor: K-major tile of 128-byte rows, SWIZZLE_128B, 8-row groups 1024 bytes apart.
+// Shared-memory matrix descriptor: K-major tile of 64-byte rows, SWIZZLE_64B, 8-row groups 512 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr)
 {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3fff);          // start address / 16
     d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset / 16
+    d |= (uint64_t)((8 * ROW_BYTES) >> 4) << 32;     // stride byte offset / 16
     d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    d |= (uint64_t)4 << 61;                          // SWIZZLE_64B
     return d;
 }
 
@@ -68,24 +73,49 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Round to nearest TF32 (10 explicit mantissa bits), ties away from zero -- what cvt.rna.tf32.f32
+// computes -- with an integer add and a mask: adding half an ulp to the magnitude carries into the
+// exponent exactly when rounding must.
 __device__ __forceinline__ float rn_tf32(float x)
 {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
 
-// Splits 16-byte chunks [first, first + count) of a slab in place: raw -> hi, lo written at +lo_off.
-__device__ __forceinline__ void split_chunks(unsigned char* raw, int lo_off, int chunks, int tid, int nthreads)
+// kRewriteHi = true: hi = rn_tf32(x) is written back over the raw slab.  false: the raw FP32 slab is
+// left as it is and the tensor core's own reading of an FP32 word as TF32 (it ignores the 13 low
+// mantissa bits, i.e. truncates) plays the role of hi; lo is then the exact remainder of that truncation.
+constexpr bool kRewriteHi = false;
+
+__device__ __forceinline__ float trunc_tf32(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+
+__device__ __forceinline__ void split4(const float4& v, float4& h, float4& l)
 {
-    for (int c = tid; c < chunks; c += nthreads) {
-        float4* p = reinterpret_cast<float4*>(raw + (size_t)c * 16);
-        const float4 v = *p;
-        float4 h, l;
-        h.x = rn_tf32(v.x); h.y = rn_tf32(v.y); h.z = rn_tf32(v.z); h.w = rn_tf32(v.w);
-        l.x = rn_tf32(v.x - h.x); l.y = rn_tf32(v.y - h.y); l.z = rn_tf32(v.z - h.z); l.w = rn_tf32(v.w - h.w);
-        *p = h;
-        *reinterpret_cast<float4*>(raw + lo_off + (size_t)c * 16) = l;
+    if (!kRewriteHi) {
+        l.x = rn_tf32(v.x - trunc_tf32(v.x)); l.y = rn_tf32(v.y - trunc_tf32(v.y));
+        l.z = rn_tf32(v.z - trunc_tf32(v.z)); l.w = rn_tf32(v.w - trunc_tf32(v.w));
+        h = v;
+        return;
+    }
+    h.x = rn_tf32(v.x); h.y = rn_tf32(v.y); h.z = rn_tf32(v.z); h.w = rn_tf32(v.w);
+    l.x = rn_tf32(v.x - h.x); l.y = rn_tf32(v.y - h.y); l.z = rn_tf32(v.z - h.z); l.w = rn_tf32(v.w - h.w);
+}
+
+// Splits the CHUNKS 16-byte chunks of a slab in place: raw -> hi, lo written lo_off bytes further.
+// Four chunks per thread are in flight at a time.
+template <int CHUNKS, int NTHREADS>
+__device__ __forceinline__ void split_chunks(unsigned char* raw, int lo_off, int tid)
+{
+    static_assert(CHUNKS % NTHREADS == 0, "chunks per thread");
+    constexpr int PER = CHUNKS / NTHREADS;
+    float4 v[PER], h[PER], l[PER];
+#pragma unroll
+    for (int i = 0; i < PER; i++) v[i] = *reinterpret_cast<const float4*>(raw + (size_t)(tid + i * NTHREADS) * 16);
+#pragma unroll
+    for (int i = 0; i < PER; i++) split4(v[i], h[i], l[i]);
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        if (kRewriteHi) *reinterpret_cast<float4*>(raw + (size_t)(tid + i * NTHREADS) * 16) = h[i];
+        *reinterpret_cast<float4*>(raw + lo_off + (size_t)(tid + i * NTHREADS) * 16) = l[i];
     }
 }
 
@@ -119,7 +149,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&raw_full[s], 1);
-            mbar_init(&split_done[s], 4);
+            mbar_init(&split_done[s], SPLIT_WARPS);
             mbar_init(&mma_done[s], 1);
         }
         mbar_init(accum_full, 1);
@@ -175,7 +205,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         }
     } else {
         // ------------------------------- splitters, then epilogue -------------------
-        const int tid = threadIdx.x - 64;           // 0..127
+        const int tid = threadIdx.x - 64;           // 0 .. 32*SPLIT_WARPS-1
         bool ok = true;
         for (int kt = 0; kt < nk && ok; kt++) {
             const int s = kt % STAGES;
@@ -183,8 +213,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             if (!ok) break;
             unsigned char* sa = smem + s * STAGE_BYTES;
             unsigned char* sb = sa + 2 * A_BYTES;
-            split_chunks(sa, A_BYTES, A_BYTES / 16, tid, 128);
-            split_chunks(sb, B_BYTES, B_BYTES / 16, tid, 128);
+            split_chunks<A_BYTES / 16, SPLIT_WARPS * 32>(sa, A_BYTES, tid);
+            split_chunks<B_BYTES / 16, SPLIT_WARPS * 32>(sb, B_BYTES, tid);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's async reads
             __syncwarp();
             if (lane == 0) mbar_arrive(&split_done[s]);
@@ -193,10 +223,11 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const int q = warp & 3;                 // this warp may read accumulator lanes 32q .. 32q+31
+            const int half = (warp - 2) / 4;        // the two warps of a quarter take half the columns each
             const size_t row = m0 + 32 * q + lane;
             const bool useC = (beta != 0.f);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
+            for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); c++) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(c * 32);
                 asm volatile(
@@ -266,8 +297,8 @@ cudaError_t launch_sgemm_3xtf32(const GemmProblem<float>& p, cudaStream_t s)
     if (e == cudaSuccess) {
         void* enc = get_tensor_map_encoder();
         CUtensorMap mapA, mapB;
-        bool ok = make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, A, p.K, p.M, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B) &&
-                  make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, p.K, p.N, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+        bool ok = make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, A, p.K, p.M, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_64B) &&
+                  make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, p.K, p.N, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_64B);
         if (!ok) e = cudaErrorNotSupported;
         if (e == cudaSuccess) {
             static bool attr_done[64] = {};
