@@ -400,6 +400,8 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "sgemm8192"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gemm-path", type=int, default=0, choices=[0, 1, 4],
+                    help="clblasB200SetGemmPath: 0 automatic, 1 alignment-free kernels, 4 SGEMM 3xTF32 on tcgen05")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -422,6 +424,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     cb.check(cb.clblasSetup(), "clblasSetup")
+    cb.set_gemm_path(args.gemm_path)
 
     def barrier():
         if world > 1:
@@ -544,6 +547,19 @@ def main():
                      "achieved_hbm_gbs": min_bytes / (kernel_ms * 1e-3) / 1e9, "hbm_peak_gbs": hbm_peak},
         "device_fault_flag": fault,
     }
+    if args.gemm_path == 4 and wl.prec == "s":
+        # Optional 3xTF32 variant: three TF32 tensor-core MMAs per product.  TF32 runs at half the BF16
+        # rate, so the ceiling is the measured BF16 burst figure / 2 / 3.
+        try:
+            bf16 = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+            src = "MEASURED_PEAKS.json bf16_tflops / 2 (TF32 rate) / 3 (MMAs per product); of measured"
+        except Exception:
+            bf16, src = 1590.0, "fallback 1.59 PFLOP/s bf16 / 2 / 3; of fallback"
+        r = line["roofline"]
+        r.update(bound="tensor", peak=bf16 / 6.0, frac=achieved / (bf16 / 6.0), peak_source=src,
+                 fp32_ffma_peak=peak, frac_of_fp32_ffma_peak=achieved / peak if peak > 0 else None)
+        line["metric"] = "SGEMM (3xTF32 on tcgen05) TFLOP/s"
+        line["config"]["gemm_path"] = "3xTF32 tcgen05 (opt-in)"
     if world == 1 and not args.no_cpu_baseline:
         v, cores, kind, text = cpu_reference_sample(wl)
         line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": text}

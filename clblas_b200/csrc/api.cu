@@ -4,6 +4,7 @@
 #include "common.h"
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 namespace cb200 {
@@ -243,6 +244,13 @@ clblasStatus clblasSetup(void)
 {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { cudaGetLastError(); return clblasInvalidDevice; }
+    // Implementation switch by environment variable, in the manner of the reference's
+    // AMD_CLBLAS_GEMM_IMPLEMENTATION (src/library/blas/impl.c:81-129):
+    // CLBLAS_B200_GEMM_PATH = 0 (automatic), 1 (alignment-free kernels), 4 (SGEMM: 3xTF32 on tcgen05).
+    if (const char* env = std::getenv("CLBLAS_B200_GEMM_PATH")) {
+        const int v = std::atoi(env);
+        if (v >= 0 && v <= 4) g_forced_path.store(v);
+    }
     g_initialized.store(1);
     return clblasSuccess;
 }

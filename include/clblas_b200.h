@@ -190,7 +190,13 @@ double clblasB200ProbePeak(int kind, double seconds);
 const char* clblasB200LastGemmKernel(void);
 /* Forces a kernel family for GEMM calls of the whole process: 0 = automatic dispatch,
  * 1 = always the alignment-free LDG path, 2 / 3 = SGEMM TMA path with one / two CTAs per SM
- * (tuning aid; operands the TMA path cannot address still take the LDG path).  Returns the previous value. */
+ * (tuning aid; operands the TMA path cannot address still take the LDG path),
+ * 4 = SGEMM through the optional 3xTF32 tensor-core kernel (tcgen05): each FP32 operand is split into
+ * two TF32 numbers and three tensor-core products are accumulated in FP32; the result meets the
+ * library's SGEMM tolerance (4*K*2^-24 relative to |alpha||A||B| + |beta||C|) but is not bit-identical to
+ * the default FFMA kernel, hence opt-in.  The environment variable CLBLAS_B200_GEMM_PATH, read by
+ * clblasSetup(), sets the same switch (the reference's counterpart: AMD_CLBLAS_GEMM_IMPLEMENTATION,
+ * src/library/blas/impl.c:81-129).  Returns the previous value. */
 int clblasB200SetGemmPath(int path);
 
 #ifdef __cplusplus
