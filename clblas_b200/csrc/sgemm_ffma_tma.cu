@@ -40,6 +40,24 @@ constexpr int GROUP_M = 16;
 
 constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 + 256; }
 
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// d = a * b + c on both halves (packed FP32x2 FMA of sm_100)
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c)
+{
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 template <bool TA, bool TB, int STAGES, int MIN_CTAS>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
@@ -96,11 +114,18 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     auto rowA = [&](int i) { return TA ? tx + 16 * i : tx * 4 + (i & 3) + 64 * (i >> 2); };
     auto colB = [&](int j) { return ty * 4 + (j & 3) + 64 * (j >> 2); };
 
+    // Accumulators.  When A is M-contiguous a 16-byte fragment load delivers rows in adjacent pairs, so
+    // the products are issued as packed FP32x2 FMAs (fma.rn.f32x2: two IEEE FMAs per instruction, the
+    // same results as scalar FFMA at half the issue slots): acc2[p][j] = rows (2p, 2p+1) of column j.
     float acc[8][8];
+    unsigned long long acc2[4][8];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+        for (int j = 0; j < 8; j++) {
+            if (TA) acc[i][j] = 0.f;
+            else if (i < 4) acc2[i][j] = 0ull;
+        }
 
     bool alive = true;
     for (int kt = 0; kt < nk; kt++) {
@@ -154,14 +179,32 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
                     b[0] = v0.x; b[1] = v0.y; b[2] = v0.z; b[3] = v0.w;
                     b[4] = v1.x; b[5] = v1.y; b[6] = v1.z; b[7] = v1.w;
                 }
+                if (TA) {
 #pragma unroll
-                for (int i = 0; i < 8; i++)
+                    for (int i = 0; i < 8; i++)
 #pragma unroll
-                    for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                } else {
+                    unsigned long long a2[4], bd[8];
+#pragma unroll
+                    for (int pr = 0; pr < 4; pr++) a2[pr] = pack2(a[2 * pr], a[2 * pr + 1]);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) bd[j] = pack2(b[j], b[j]);
+#pragma unroll
+                    for (int pr = 0; pr < 4; pr++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) acc2[pr][j] = ffma2(a2[pr], bd[j], acc2[pr][j]);
+                }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    if (!TA) {
+#pragma unroll
+        for (int pr = 0; pr < 4; pr++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) unpack2(acc2[pr][j], acc[2 * pr][j], acc[2 * pr + 1][j]);
     }
 
     // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
