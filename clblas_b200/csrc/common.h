@@ -47,7 +47,7 @@ cudaError_t launch_gemm_simt(const GemmProblem<T>& p, cudaStream_t s);
 // cudaErrorNotSupported when the problem does not meet their requirements.
 // min_bn: 0 = choose the tile width from the shape; 128 = never use the narrow-tile variants.
 cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s, int min_bn = 0);
-cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s);
+cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, int min_bn = 0);
 
 // Copies (or transposes) a rows x cols column-major operand into an aligned workspace.
 template <typename T>

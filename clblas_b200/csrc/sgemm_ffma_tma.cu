@@ -6,25 +6,28 @@
 // (src/library/blas/AutoGemm/UserGemmKernelSources/sgemm_Col_NT_B1_MX128_NX128_KX16_src.cpp),
 // and of the generator they come from (src/library/blas/AutoGemm/KernelOpenCL.py:13-459).
 //
-// CTA = 128 x 128 tile of C, K in slabs of 32, 256 threads (16 x 16, an 8 x 8 register tile each).
+// CTA = 128 x BN tile of C (BN = 128, or 64 for problems too small to give every SM a 128-wide
+// tile), K in slabs of 32, 256 threads (16 x 16, an 8 x BN/16 register tile each).
 // Thread 0 doubles as the producer: part-way through every slab it refills the ring slot that was
 // consumed one slab earlier (two TMA bulk-tensor loads; full/empty mbarriers, bounded waits).
-// Two configurations of the same code:
-//   * 3-stage ring (97 KB), at most 128 registers per thread, TWO CTAs per SM: four warps per SM
+// Configurations of the same code:
+//   * 3-stage ring, at most 128 registers per thread, TWO CTAs per SM: four warps per SM
 //     sub-partition hide each other's shared-memory latency and barrier waits;
-//   * 5-stage ring (161 KB), up to 255 registers, one CTA per SM: for the transpose case whose
-//     fragments need the registers (both operands K-contiguous).
+//   * 5-stage ring, up to 255 registers, one CTA per SM: for the transpose cases whose 4-k
+//     fragments need the registers (K-contiguous operands).
 // TMA zero-fills beyond M, N, K, so one launch covers ragged shapes; the epilogue is predicated.
 //
 // Shared layouts:
-//  * M/N-contiguous operand (A for transA=N, B for transB=T): box 128 x 32 (k), dense rows of 128
-//    floats; a thread reads two float4 per k (rows 4*tx..+3 and 64+4*tx..+3), a warp reads 256
-//    contiguous bytes: conflict free.
-//  * K-contiguous operand (A for transA=T, B for transB=N): box 32 (k) x 128, 128-byte rows,
+//  * M/N-contiguous operand (A for transA=N, B for transB=T): box tile x 32 (k), dense rows;
+//    a thread reads float4 per k (rows 4*tx..+3 and 64+4*tx..+3), a warp reads 256 contiguous
+//    bytes: conflict free.
+//  * K-contiguous operand (A for transA=T, B for transB=N): box 32 (k) x tile, 128-byte rows,
 //    SWIZZLE_128B; a thread reads one float4 (4 consecutive k) per row, rows tx + 16*i for A so
 //    that the 8 lanes of a quarter warp hit 8 different swizzle phases: conflict free.  B rows are
 //    shared by the 16 lanes with equal ty (broadcast).
-// Per k: 4 LDS.128 for 64 FFMA (K-contiguous operands are fetched 4 k at a time).
+// When A is M-contiguous the products are issued as packed FP32x2 FMAs (fma.rn.f32x2: two IEEE
+// FMAs per instruction, bit-identical to scalar FFMA, half the issue slots): per k, 32 packed FMAs,
+// 4 LDS.128 and 8 register moves that duplicate the B values.
 #include "common.h"
 #include "tma_pipeline.cuh"
 
@@ -32,13 +35,13 @@ namespace cb200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int OPERAND_BYTES = BM * BK * 4;          // 16 KB
-constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;
+constexpr int BM = 128, BK = 32;
+constexpr int A_BYTES = BM * BK * 4;                // 16 KB
 constexpr int THREADS = 256;
 constexpr int GROUP_M = 16;
 
-constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 + 256; }
+constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 4; }
+constexpr int smem_bytes(int stages, int bn) { return stages * stage_bytes(bn) + 1024 + 256; }
 
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi)
 {
@@ -58,12 +61,17 @@ __device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsign
     return d;
 }
 
-template <bool TA, bool TB, int STAGES, int MIN_CTAS>
+template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
                       unsigned tilesM, unsigned tilesN)
 {
+    constexpr int STAGE_BYTES = stage_bytes(BN);
+    constexpr int NJ = BN / 16;                     // columns per thread: 8 or 4
+    constexpr int NH = NJ / 4;                      // 4-column groups per thread (64 columns apart)
+    constexpr int B_ROW = BN * 4;                   // bytes per k row of an N-contiguous B slab
+
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -95,7 +103,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     auto issue = [&](int kt) {
         const int s = kt % STAGES;
         unsigned char* sa = smem + s * STAGE_BYTES;
-        unsigned char* sb = sa + OPERAND_BYTES;
+        unsigned char* sb = sa + A_BYTES;
         mbar_expect_tx(&full[s], STAGE_BYTES);
         const int k0 = kt * BK;
         if (TA) tma_load_2d(sa, &mapA, k0, (int)m0, &full[s]); else tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
@@ -115,14 +123,13 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     auto colB = [&](int j) { return ty * 4 + (j & 3) + 64 * (j >> 2); };
 
     // Accumulators.  When A is M-contiguous a 16-byte fragment load delivers rows in adjacent pairs, so
-    // the products are issued as packed FP32x2 FMAs (fma.rn.f32x2: two IEEE FMAs per instruction, the
-    // same results as scalar FFMA at half the issue slots): acc2[p][j] = rows (2p, 2p+1) of column j.
-    float acc[8][8];
-    unsigned long long acc2[4][8];
+    // the products are packed: acc2[p][j] = rows (2p, 2p+1) of column j.
+    float acc[8][NJ];
+    unsigned long long acc2[4][NJ];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
+        for (int j = 0; j < NJ; j++) {
             if (TA) acc[i][j] = 0.f;
             else if (i < 4) acc2[i][j] = 0ull;
         }
@@ -132,7 +139,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         const int s = kt % STAGES;
         if (!mbar_wait(&full[s], (kt / STAGES) & 1)) break;
         const unsigned char* sa = smem + s * STAGE_BYTES;
-        const unsigned char* sb = sa + OPERAND_BYTES;
+        const unsigned char* sb = sa + A_BYTES;
 #pragma unroll
         for (int kc = 0; kc < BK / 4; kc++) {
             // Refill the slot consumed during the previous slab with the slab STAGES-1 ahead.  Done a
@@ -142,7 +149,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
                 if (kt >= 1) alive = mbar_wait(&empty[(kt - 1) % STAGES], ((kt - 1) / STAGES) & 1);
                 if (alive) issue(kt + STAGES - 1);
             }
-            float a4[4][8], b4[4][8];
+            float a4[4][8], b4[4][NJ];
             if (TA) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
@@ -152,7 +159,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
             }
             if (!TB) {
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
+                for (int j = 0; j < NJ; j++) {
                     const int n = ty * 4 + (j & 3) + 64 * (j >> 2);
                     const float4 v = *reinterpret_cast<const float4*>(sb + n * 128 + ((kc ^ (n & 7)) << 4));
                     b4[0][j] = v.x; b4[1][j] = v.y; b4[2][j] = v.z; b4[3][j] = v.w;
@@ -160,7 +167,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
             }
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                float a[8], b[8];
+                float a[8], b[NJ];
                 if (TA) {
 #pragma unroll
                     for (int i = 0; i < 8; i++) a[i] = a4[q][i];
@@ -172,28 +179,29 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
                 }
                 if (!TB) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) b[j] = b4[q][j];
+                    for (int j = 0; j < NJ; j++) b[j] = b4[q][j];
                 } else {
-                    const float4 v0 = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * 512 + ty * 16);
-                    const float4 v1 = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * 512 + 256 + ty * 16);
-                    b[0] = v0.x; b[1] = v0.y; b[2] = v0.z; b[3] = v0.w;
-                    b[4] = v1.x; b[5] = v1.y; b[6] = v1.z; b[7] = v1.w;
+#pragma unroll
+                    for (int h = 0; h < NH; h++) {
+                        const float4 v = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * B_ROW + h * 256 + ty * 16);
+                        b[4 * h + 0] = v.x; b[4 * h + 1] = v.y; b[4 * h + 2] = v.z; b[4 * h + 3] = v.w;
+                    }
                 }
                 if (TA) {
 #pragma unroll
                     for (int i = 0; i < 8; i++)
 #pragma unroll
-                        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                        for (int j = 0; j < NJ; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
                 } else {
-                    unsigned long long a2[4], bd[8];
+                    unsigned long long a2[4], bd[NJ];
 #pragma unroll
                     for (int pr = 0; pr < 4; pr++) a2[pr] = pack2(a[2 * pr], a[2 * pr + 1]);
 #pragma unroll
-                    for (int j = 0; j < 8; j++) bd[j] = pack2(b[j], b[j]);
+                    for (int j = 0; j < NJ; j++) bd[j] = pack2(b[j], b[j]);
 #pragma unroll
                     for (int pr = 0; pr < 4; pr++)
 #pragma unroll
-                        for (int j = 0; j < 8; j++) acc2[pr][j] = ffma2(a2[pr], bd[j], acc2[pr][j]);
+                        for (int j = 0; j < NJ; j++) acc2[pr][j] = ffma2(a2[pr], bd[j], acc2[pr][j]);
                 }
             }
         }
@@ -204,14 +212,14 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 #pragma unroll
         for (int pr = 0; pr < 4; pr++)
 #pragma unroll
-            for (int j = 0; j < 8; j++) unpack2(acc2[pr][j], acc[2 * pr][j], acc[2 * pr + 1][j]);
+            for (int j = 0; j < NJ; j++) unpack2(acc2[pr][j], acc[2 * pr][j], acc[2 * pr + 1][j]);
     }
 
     // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
     const bool useC = (beta != 0.f);
     const bool vec = !TA && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
+    for (int j = 0; j < NJ; j++) {
         const size_t col = n0 + colB(j);
         if (col >= N) continue;
         float* cc = C + col * ldc;
@@ -254,7 +262,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     }
 }
 
-template <bool TA, bool TB, int STAGES, int MIN_CTAS>
+template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS>
 cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
 {
     void* enc = get_tensor_map_encoder();
@@ -267,49 +275,56 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
     else    ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.K, p.N, p.ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorNotSupported;
 
-    constexpr int SMEM = smem_bytes(STAGES);
+    constexpr int SMEM = smem_bytes(STAGES, BN);
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB, STAGES, MIN_CTAS>,
+        cudaError_t e = cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
-    sgemm_ffma_tma_kernel<TA, TB, STAGES, MIN_CTAS><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
+    sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN);
     count_launch();
     return cudaGetLastError();
 }
 
-template <int STAGES, int MIN_CTAS>
+template <int BN, int STAGES, int MIN_CTAS>
 cudaError_t launch_any(const GemmProblem<float>& p, cudaStream_t s)
 {
-    if (!p.ta && !p.tb) return launch<false, false, STAGES, MIN_CTAS>(p, s);
-    if (!p.ta && p.tb) return launch<false, true, STAGES, MIN_CTAS>(p, s);
-    if (p.ta && !p.tb) return launch<true, false, STAGES, MIN_CTAS>(p, s);
-    return launch<true, true, STAGES, MIN_CTAS>(p, s);
+    if (!p.ta && !p.tb) return launch<false, false, BN, STAGES, MIN_CTAS>(p, s);
+    if (!p.ta && p.tb) return launch<false, true, BN, STAGES, MIN_CTAS>(p, s);
+    if (p.ta && !p.tb) return launch<true, false, BN, STAGES, MIN_CTAS>(p, s);
+    return launch<true, true, BN, STAGES, MIN_CTAS>(p, s);
 }
 
 }  // namespace
 
-cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s)
+cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, int min_bn)
 {
     if (!aligned16(p.A) || !aligned16(p.B) || (p.lda & 3) || (p.ldb & 3)) return cudaErrorNotSupported;
     if (p.M >= (1u << 31) || p.N >= (1u << 31) || p.K >= (1u << 31)) return cudaErrorNotSupported;
-    const size_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-    if (tiles >= (1u << 31)) return cudaErrorNotSupported;
+    const size_t tilesM = (p.M + BM - 1) / BM;
+    const size_t tiles128 = tilesM * ((p.N + 127) / 128);
+    if (tilesM * ((p.N + 63) / 64) >= (1u << 31)) return cudaErrorNotSupported;
     set_last_kernel("sgemm_ffma_tma");
     const int forced = forced_gemm_path();
-    if (forced == PATH_TMA_ONE_CTA) return launch_any<5, 1>(p, s);
-    if (forced == PATH_TMA_TWO_CTAS) return launch_any<3, 2>(p, s);
-    // A K-contiguous operand is fetched 4 k at a time (32 fragment registers on top of the 64
-    // accumulators), which only the one-CTA configuration holds without spilling; measured at
-    // 8192^3: N/T 52.6 (two CTAs) vs 47.6 TFLOP/s (one), N/N 37.5 vs 41.6, T/N 24.8 vs 37.1, T/T 43.6 vs 46.5.
-    if (!p.ta && p.tb) return launch_any<3, 2>(p, s);
-    return launch_any<5, 1>(p, s);
+    if (forced == PATH_TMA_ONE_CTA) return launch_any<128, 5, 1>(p, s);
+    if (forced == PATH_TMA_TWO_CTAS) return launch_any<128, 3, 2>(p, s);
+    // Fewer 128-wide tiles than SMs: halve the tile width so that twice as many CTAs share the work
+    // (three of them fit an SM).  With A K-contiguous the 4-k fragments need the one-CTA register budget.
+    if (min_bn < 128 && tiles128 < 120) {
+        if (p.ta) return launch_any<64, 5, 1>(p, s);
+        return launch_any<64, 3, 2>(p, s);
+    }
+    // A K-contiguous operand is fetched 4 k at a time (32 fragment registers on top of the
+    // accumulators), which the two-CTA budget of 128 registers holds only for B; measured at 8192^3
+    // with packed FMAs: N/T 60.2 (two CTAs) vs 53.6 TFLOP/s (one), N/N 48.6 vs 47.2.
+    if (!p.ta) return launch_any<128, 3, 2>(p, s);
+    return launch_any<128, 5, 1>(p, s);
 }
 
 unsigned sgemm_tma_fault_flag() { return read_wait_timeout_flag(); }

@@ -131,7 +131,10 @@ cudaError_t gemm_call(bool ta, bool tb, size_t M, size_t N, size_t K, T alpha, c
 // TMA-staged product whose output aliases one of its inputs (see solve_leaf); NotSupported when the
 // operands are not TMA-addressable.  For the FP64 kernel the tile must span all 128 columns when the
 // aliased operand is A (Right side), so the narrow-tile variants are excluded there.
-inline cudaError_t launch_tma_inplace(const GemmProblem<float>& p, cudaStream_t s) { return launch_sgemm_ffma_tma(p, s); }
+inline cudaError_t launch_tma_inplace(const GemmProblem<float>& p, cudaStream_t s)
+{
+    return launch_sgemm_ffma_tma(p, s, p.C == p.A ? 128 : 0);
+}
 inline cudaError_t launch_tma_inplace(const GemmProblem<double>& p, cudaStream_t s)
 {
     return launch_dgemm_mma_tma(p, s, p.C == p.A ? 128 : 0);
