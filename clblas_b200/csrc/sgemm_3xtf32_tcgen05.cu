@@ -7,16 +7,19 @@
 // The reference has no counterpart (its sgemm kernels are scalar mad() code,
 // src/library/blas/AutoGemm/KernelOpenCL.py:171-181).
 //
-// CTA = 128 x 256 tile of C, K in slabs of 16 (64-byte swizzled rows), ring of 4 slabs, 10 warps:
+// CTA = 128 x 256 tile of C, K in slabs of 16 (64-byte swizzled rows), ring of 5 slabs, 10 warps:
 //   warp 0    producer: TMA loads of the A and B slabs (both K-contiguous, SWIZZLE_64B), issued
-//             three slabs ahead of the tensor core;
-//   warp 1    owns tensor memory (tcgen05.alloc / dealloc, 256 columns) and issues the MMAs: per 8-wide
-//             k step three tcgen05.mma.kind::tf32 (M=128, N=256, K=8) reading shared-memory descriptors;
+//             four slabs ahead of the tensor core;
+//   warp 1    owns tensor memory (tcgen05.alloc / dealloc: 256 accumulator columns + a ring of A
+//             operands) and issues the MMAs: per 8-wide k step three tcgen05.mma.kind::tf32
+//             (M=128, N=256, K=8), B through shared-memory descriptors, A from tensor memory;
 //             tcgen05.commit releases the ring slot and, at the end, publishes the accumulator;
-//   warps 2-9 splitters: rewrite each raw slab in place as `hi` and write `lo` next to it (same
-//             swizzled layout, so the split is element-wise; rounding is done with integer adds and
-//             masks, the conversion instruction is a quarter-rate pipe), then fence.proxy.async and
-//             hand the slot to warp 1; after the last slab they are the epilogue: tcgen05.ld of their
+//   warps 2-9 splitters: hi is the raw FP32 word itself (the tensor core truncates it); lo is computed
+//             with integer adds and masks (the conversion instruction is a quarter-rate pipe).  B lo
+//             is written next to the raw slab in the same swizzled layout (element-wise, layout
+//             agnostic); A hi and lo go to tensor memory with tcgen05.st (warps 2-5, one row per
+//             thread).  fence.proxy.async + tcgen05 fences hand the slot to warp 1.  After the last
+//             slab the same warps are the epilogue: tcgen05.ld of their
 //             quarter of the 128 accumulator lanes (two warps share a quarter, half the columns each),
 //             alpha/beta, coalesced stores.
 // Every wait is bounded; all roles meet at one barrier before tensor memory is freed.
@@ -30,15 +33,22 @@ namespace cb200 {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 16;
-constexpr int STAGES = 4;
+// kATmem: the A operand of the MMAs (hi and lo) is kept in tensor memory, written there by the
+// splitter warps with tcgen05.st, instead of in shared memory.  Shared-memory bandwidth is what
+// bounds this kernel (TMA writes, splitter reads and writes, and the operand reads of three MMAs per
+// k step all go through it); taking A out of the MMA's shared-memory reads removes a third of them.
+constexpr bool kATmem = true;
+constexpr int STAGES = kATmem ? 5 : 4;
 constexpr int ROW_BYTES = BK * 4;                    // 64-byte rows: SWIZZLE_64B
 constexpr int A_BYTES = BM * ROW_BYTES;              // 8 KB
 constexpr int B_BYTES = BN * ROW_BYTES;              // 16 KB
-constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES); // raw/hi + lo for both operands: 48 KB
+constexpr int B_OFF = kATmem ? A_BYTES : 2 * A_BYTES;                 // raw A (+ A lo) come first in a slot
+constexpr int STAGE_BYTES = B_OFF + 2 * B_BYTES;     // + raw/hi B + B lo: 40 KB (48 KB with A lo in shared)
 constexpr int SPLIT_WARPS = 8;
 constexpr int THREADS = (2 + SPLIT_WARPS) * 32;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int TMEM_COLS = BN;                        // one FP32 column per accumulator column
+constexpr int TMEM_A_COL = BN;                       // A ring: slot s = columns [BN + 32 s, BN + 32 s + 32): hi 16, lo 16
+constexpr int TMEM_COLS = kATmem ? 512 : BN;         // accumulator: one FP32 column per column of the tile
 constexpr int GROUP_M = 16;
 
 // tcgen05 instruction descriptor, kind::tf32: D = F32, A = B = TF32, both K-major, N = 256, M = 128
@@ -65,6 +75,30 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t a_desc, uint
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
         "}\n"
         ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate)
+        : "memory");
+}
+
+// Same MMA with the A operand (128 rows = lanes, 8 k = 8 columns) read from tensor memory.
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
+        "}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(IDESC), "r"(accumulate)
+        : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
 
@@ -173,7 +207,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 const int s = kt % STAGES;
                 if (kt >= STAGES && !mbar_wait(&mma_done[s], ((kt / STAGES) - 1) & 1)) break;
                 unsigned char* sa = smem + s * STAGE_BYTES;
-                unsigned char* sb = sa + 2 * A_BYTES;
+                unsigned char* sb = sa + B_OFF;
                 mbar_expect_tx(&raw_full[s], A_BYTES + B_BYTES);
                 tma_load_2d(sa, &mapA, kt * BK, (int)m0, &raw_full[s]);
                 tma_load_2d(sb, &mapB, kt * BK, (int)n0, &raw_full[s]);
@@ -189,15 +223,23 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-                const uint32_t sb = sa + 2 * A_BYTES;
+                const uint32_t sb = sa + B_OFF;
                 const uint64_t a_hi = smem_desc(sa), a_lo = smem_desc(sa + A_BYTES);
                 const uint64_t b_hi = smem_desc(sb), b_lo = smem_desc(sb + B_BYTES);
+                const uint32_t ta = tmem_base + TMEM_A_COL + s * 32;      // A hi at +0, A lo at +16
 #pragma unroll
                 for (int ks = 0; ks < BK / 8; ks++) {
                     const uint64_t adv = (uint64_t)((ks * 32) >> 4);      // 8 TF32 = 32 bytes along K
-                    umma_tf32(tmem_base, a_lo + adv, b_hi + adv, (kt > 0 || ks > 0) ? 1u : 0u);
-                    umma_tf32(tmem_base, a_hi + adv, b_lo + adv, 1u);
-                    umma_tf32(tmem_base, a_hi + adv, b_hi + adv, 1u);
+                    const uint32_t first = (kt > 0 || ks > 0) ? 1u : 0u;
+                    if (kATmem) {
+                        umma_tf32_ts(tmem_base, ta + 16 + ks * 8, b_hi + adv, first);
+                        umma_tf32_ts(tmem_base, ta + ks * 8, b_lo + adv, 1u);
+                        umma_tf32_ts(tmem_base, ta + ks * 8, b_hi + adv, 1u);
+                    } else {
+                        umma_tf32(tmem_base, a_lo + adv, b_hi + adv, first);
+                        umma_tf32(tmem_base, a_hi + adv, b_lo + adv, 1u);
+                        umma_tf32(tmem_base, a_hi + adv, b_hi + adv, 1u);
+                    }
                 }
                 umma_commit(&mma_done[s]);          // slot reusable once these MMAs have read it
             }
@@ -212,10 +254,34 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             ok = mbar_wait(&raw_full[s], (kt / STAGES) & 1);
             if (!ok) break;
             unsigned char* sa = smem + s * STAGE_BYTES;
-            unsigned char* sb = sa + 2 * A_BYTES;
-            split_chunks<A_BYTES / 16, SPLIT_WARPS * 32>(sa, A_BYTES, tid);
+            unsigned char* sb = sa + B_OFF;
+            if (kATmem) {
+                if (warp < 6) {
+                    // Warps 2-5 own the four lane quarters of tensor memory: thread = row 32q + lane of the A
+                    // slab.  Its 16 k values are four 16-byte chunks; SWIZZLE_64B stored chunk j at j ^ ((row/2)&3).
+                    const int row = 32 * (warp & 3) + lane;
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float4 v = *reinterpret_cast<const float4*>(sa + row * ROW_BYTES + ((j ^ ((row >> 1) & 3)) << 4));
+                        float4 h, l;
+                        split4(v, h, l);
+                        hi[4 * j + 0] = __float_as_uint(v.x); hi[4 * j + 1] = __float_as_uint(v.y);
+                        hi[4 * j + 2] = __float_as_uint(v.z); hi[4 * j + 3] = __float_as_uint(v.w);
+                        lo[4 * j + 0] = __float_as_uint(l.x); lo[4 * j + 1] = __float_as_uint(l.y);
+                        lo[4 * j + 2] = __float_as_uint(l.z); lo[4 * j + 3] = __float_as_uint(l.w);
+                    }
+                    const uint32_t taddr = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + TMEM_A_COL + s * 32;
+                    tmem_st16(taddr, hi);
+                    tmem_st16(taddr + 16, lo);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            } else {
+                split_chunks<A_BYTES / 16, SPLIT_WARPS * 32>(sa, A_BYTES, tid);
+            }
             split_chunks<B_BYTES / 16, SPLIT_WARPS * 32>(sb, B_BYTES, tid);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's async reads
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&split_done[s]);
         }
