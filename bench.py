@@ -30,9 +30,18 @@ sys.path.insert(0, ROOT)
 
 NOMINAL = {"fp32": 148 * 128 * 2 * 1.965e9 / 1e12, "fp64": 148 * 64 * 2 * 1.965e9 / 1e12}
 
-# DRAM bytes per launch of the dominant kernel from the committed ncu captures under profiles/
-# (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"cfg1": None, "cfg2": None, "cfg3": None, "cfg4": None, "cfg5": None}
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum), captured
+# with ncu at the workload's full size (these two metrics take one pass; profiles/dram_traffic_full_size.md).
+# None where no capture of that workload exists (cfg4 is 127 launches of different shapes; cfg5 runs 1.2 s).
+NCU_TRAFFIC_BYTES = {
+    "cfg1": int(12.63e6),                          # sgemm_ffma_tma N/N 1024^3 (operands L2 resident, C not written back yet)
+    "cfg2": int(6.34e9 + 528.82e6),                # dgemm_mma_tma T/N 8192^3
+    "cfg3": int(94.89e6 + 18.84e6),                # sgemm_ffma_tma on the repacked operands of config 3
+    "cfg4": None,
+    "cfg5": None,
+    "sgemm8192": int(3.06e9 + 269.16e6),           # sgemm_ffma_tma N/T 8192^3
+}
+NCU_TRAFFIC_BYTES_3XTF32 = {"sgemm8192": int(2.70e9 + 256.35e6)}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -557,7 +566,8 @@ def main():
             bf16, src = 1590.0, "fallback 1.59 PFLOP/s bf16 / 2 / 3; of fallback"
         r = line["roofline"]
         r.update(bound="tensor", peak=bf16 / 6.0, frac=achieved / (bf16 / 6.0), peak_source=src,
-                 fp32_ffma_peak=peak, frac_of_fp32_ffma_peak=achieved / peak if peak > 0 else None)
+                 fp32_ffma_peak=peak, frac_of_fp32_ffma_peak=achieved / peak if peak > 0 else None,
+                 traffic=NCU_TRAFFIC_BYTES_3XTF32.get(wl.name))
         line["metric"] = "SGEMM (3xTF32 on tcgen05) TFLOP/s"
         line["config"]["gemm_path"] = "3xTF32 tcgen05 (opt-in)"
     if world == 1 and not args.no_cpu_baseline:

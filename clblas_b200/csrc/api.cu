@@ -214,6 +214,19 @@ void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxe
 void set_last_kernel(const char* name) { t_last_kernel = name; }
 int forced_gemm_path() { return g_forced_path.load(std::memory_order_relaxed); }
 
+int sm_count()
+{
+    static std::atomic<int> cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int v = cached[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+
 void* get_tensor_map_encoder()
 {
     static void* fn = [] {

@@ -87,6 +87,9 @@ unsigned sgemm_tma_fault_flag();
 // cuTensorMapEncodeTiled obtained through the runtime's driver entry point query (no libcuda link).
 void* get_tensor_map_encoder();
 
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace cb200

@@ -55,7 +55,7 @@ template <bool TA, bool TB, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      double* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, double alpha, double beta,
-                     unsigned tilesM, unsigned tilesN)
+                     unsigned tilesM, unsigned tilesN, unsigned wave)
 {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -78,6 +78,9 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
     const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
     const int nk = (int)((K + BK - 1) / BK);
+    // Every other wave of CTAs walks K backwards: it starts on the K range the wave before it
+    // finished on, which is what L2 still holds, instead of re-streaming those panels from DRAM.
+    const bool reverse_k = wave != 0 && ((blockIdx.x / wave) & 1);
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
@@ -101,7 +104,7 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
                 unsigned char* sb = sa + A_BYTES;
                 const uint32_t bytes = (TA ? BK * BM : MC_PITCH * BK) * 8 + (TB ? PITCH_B * BK : BK * BN) * 8;
                 mbar_expect_tx(&full[s], bytes);
-                const int k0 = kt * BK;
+                const int k0 = (reverse_k ? nk - 1 - kt : kt) * BK;
                 if (TA) tma_load_2d(sa, &mapA, k0, (int)m0, &full[s]); else tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
                 if (TB) tma_load_2d(sb, &mapB, (int)n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, (int)n0, &full[s]);
             }
@@ -202,7 +205,7 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
     dgemm_mma_tma_kernel<TA, TB, BN><<<(unsigned)(tilesM * tilesN), THREADS, smem_bytes(BN), s>>>(
-        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN);
+        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 1));
     count_launch();
     return cudaGetLastError();
 }

@@ -65,7 +65,7 @@ template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                      unsigned tilesM, unsigned tilesN)
+                      unsigned tilesM, unsigned tilesN, unsigned wave)
 {
     constexpr int STAGE_BYTES = stage_bytes(BN);
     constexpr int NJ = BN / 16;                     // columns per thread: 8 or 4
@@ -89,6 +89,9 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     }
     const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
     const int nk = (int)((K + BK - 1) / BK);
+    // Every other wave of CTAs walks K backwards: it starts on the K range the wave before it
+    // finished on, which is what L2 still holds, instead of re-streaming those panels from DRAM.
+    const bool reverse_k = wave != 0 && ((blockIdx.x / wave) & 1);
     const int lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
@@ -105,7 +108,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         unsigned char* sa = smem + s * STAGE_BYTES;
         unsigned char* sb = sa + A_BYTES;
         mbar_expect_tx(&full[s], STAGE_BYTES);
-        const int k0 = kt * BK;
+        const int k0 = (reverse_k ? nk - 1 - kt : kt) * BK;
         if (TA) tma_load_2d(sa, &mapA, k0, (int)m0, &full[s]); else tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
         if (TB) tma_load_2d(sb, &mapB, (int)n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, (int)n0, &full[s]);
     };
@@ -287,7 +290,7 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
     sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
-        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN);
+        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * MIN_CTAS));
     count_launch();
     return cudaGetLastError();
 }
