@@ -68,7 +68,8 @@ def _load() -> ctypes.CDLL:
         f.argtypes = [i, i, i, sz, sz, sz, ft, vp, sz, sz, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
     for name, ft in (("clblasStrsm", ctypes.c_float), ("clblasDtrsm", ctypes.c_double),
-                     ("clblasB200DtrsmNoAlloc", ctypes.c_double)):
+                     ("clblasB200DtrsmNoAlloc", ctypes.c_double), ("clblasStrmm", ctypes.c_float),
+                     ("clblasDtrmm", ctypes.c_double)):
         f = getattr(lib, name)
         f.argtypes = [i, i, i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
@@ -97,7 +98,8 @@ lib = _load()
 
 EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "clblasDgemm", "clblasStrsm",
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
-           "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc"]
+           "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
+           "clblasStrmm", "clblasDtrmm"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -188,6 +190,19 @@ def clblasStrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, o
 def clblasDtrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
                 queues=None, wait=None, events=None) -> int:
     return _trsm(lib.clblasDtrsm, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                 queues, wait, events)
+
+
+def clblasStrmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                queues=None, wait=None, events=None) -> int:
+    """B <- alpha*op(A)*B (Left) / alpha*B*op(A) (Right), A triangular (src/clBLAS.h:7697-7717)."""
+    return _trsm(lib.clblasStrmm, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                 queues, wait, events)
+
+
+def clblasDtrmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                queues=None, wait=None, events=None) -> int:
+    return _trsm(lib.clblasDtrmm, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
                  queues, wait, events)
 
 

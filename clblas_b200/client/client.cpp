@@ -43,7 +43,7 @@ static void usage()
     std::puts("clblas_b200_client options (same meaning as the clBLAS client):\n"
               "  -m/--sizem -n/--sizen -k/--sizek  --lda --ldb --ldc  --offA --offBX --offCY\n"
               "  --alpha --beta  -o/--order (0 row, 1 column)  --transposeA --transposeB (0/1/2)\n"
-              "  -f/--function gemm|trsm  -r/--precision s|d  --side --uplo --diag\n"
+              "  -f/--function gemm|trsm|trmm  -r/--precision s|d  --side --uplo --diag\n"
               "  -p/--profile samples (20)  --apiCallCount calls per sample (10)  -v/--validate 0|1");
 }
 
@@ -142,6 +142,13 @@ static int run(const Options& o)
             return clblasDgemm((clblasOrder)o.order, (clblasTranspose)o.transA, (clblasTranspose)o.transB, o.M, o.N, o.K,
                                o.alpha, dA, o.offA, lda, dB, o.offB, ldb, o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
         }
+        if (o.function == "trmm") {
+            if (sizeof(T) == 4)
+                return clblasStrmm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, (clblasTranspose)o.transA, (clblasDiag)o.diag,
+                                   o.M, o.N, (float)o.alpha, dA, o.offA, lda, dB, o.offB, ldb, 1, &q, 0, nullptr, nullptr);
+            return clblasDtrmm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, (clblasTranspose)o.transA, (clblasDiag)o.diag,
+                               o.M, o.N, o.alpha, dA, o.offA, lda, dB, o.offB, ldb, 1, &q, 0, nullptr, nullptr);
+        }
         if (sizeof(T) == 4)
             return clblasStrsm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, (clblasTranspose)o.transA, (clblasDiag)o.diag,
                                o.M, o.N, (float)o.alpha, dA, o.offA, lda, dB, o.offB, ldb, 1, &q, 0, nullptr, nullptr);
@@ -229,7 +236,7 @@ int main(int argc, char** argv)
 {
     Options o;
     if (!parse(argc, argv, o)) { usage(); return 1; }
-    if (o.function != "gemm" && o.function != "trsm") { std::fprintf(stderr, "function must be gemm or trsm\n"); return 1; }
+    if (o.function != "gemm" && o.function != "trsm" && o.function != "trmm") { std::fprintf(stderr, "function must be gemm, trsm or trmm\n"); return 1; }
     if (o.precision == "s") return run<float>(o);
     if (o.precision == "d") return run<double>(o);
     std::fprintf(stderr, "precision must be s or d\n");

@@ -208,6 +208,40 @@ clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clb
     return record_out(s, events);
 }
 
+// clblasStrmm / clblasDtrmm: checks of the reference's doTrmm (src/library/blas/xtrmm.c:52-70):
+// initialised, memory objects, A (order x order), B; then the same row-major flip as TRSM.
+template <typename T>
+clblasStatus trmm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                        size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda,
+                        void* B, size_t offB, size_t ldb,
+                        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u || (unsigned)transA > 2u || (unsigned)diag > 1u) return clblasInvalidValue;
+    const size_t msize = (side == clblasLeft) ? M : N;
+    if ((st = check_matrix_sizes(sizeof(T), order, transA, msize, msize, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, M, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = trmm_colmajor<T>(right, lower, transA != clblasNoTrans, diag == clblasUnit, M, N, alpha,
+                                     static_cast<const T*>(A) + offA, lda, static_cast<T*>(B) + offB, ldb, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 }  // namespace
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -307,6 +341,24 @@ clblasStatus clblasDtrsm(clblasOrder order, clblasSide side, clblasUplo uplo, cl
                          unsigned nev, const clblasEvent* wait, clblasEvent* events)
 {
     return trsm_entry<double>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                              nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasStrmm(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, float alpha, const clblasMem A, size_t offA, size_t lda,
+                         clblasMem B, size_t offB, size_t ldb, unsigned nq, clblasQueue* queues,
+                         unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return trmm_entry<float>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                             nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasDtrmm(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, double alpha, const clblasMem A, size_t offA, size_t lda,
+                         clblasMem B, size_t offB, size_t ldb, unsigned nq, clblasQueue* queues,
+                         unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return trmm_entry<double>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
                               nq, queues, nev, wait, events);
 }
 

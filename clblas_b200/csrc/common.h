@@ -70,6 +70,11 @@ cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t 
                           const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
 void trsm_release_workspaces();
 
+// Triangular matrix multiply on a column-major problem (B overwritten by alpha*op(A)*B or alpha*B*op(A)).
+template <typename T>
+cudaError_t trmm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
+                          const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
+
 // Stream-ordered workspace from the library's own per-device pool (workspace.cu).
 cudaError_t ws_alloc(void** ptr, size_t bytes, cudaStream_t s);
 cudaError_t ws_free(void* ptr, cudaStream_t s);

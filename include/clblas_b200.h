@@ -136,6 +136,29 @@ clblasStatus clblasDtrsm(
     unsigned numCommandQueues, clblasQueue* commandQueues,
     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
 
+/* ---- TRMM: replaces clblasStrmm (src/clBLAS.h:7697-7717) and clblasDtrmm (:7772-7792), implemented by
+ *      src/library/blas/xtrmm.c:30-180 in the reference.  B <- alpha*op(A)*B (Left) or alpha*B*op(A) (Right),
+ *      A triangular; only the referenced triangle is read and a unit diagonal is not read.  Checks in the
+ *      order of the reference's doTrmm (xtrmm.c:52-70): NotInitialized, NULL A/B, A sizes, B sizes.
+ *      Needs clblasSetup(); takes its workspace from the library's stream-ordered pool. */
+clblasStatus clblasStrmm(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    float alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasDtrmm(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    double alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- DTRSM that allocates nothing (no counterpart in the reference, whose DTRSM creates and
  *      releases two OpenCL buffers inside every call, src/library/blas/xtrsm.cc:1183-1207).
  *      Same arguments, checks and result as clblasDtrsm, but the blocked solve's workspace is a

@@ -46,6 +46,9 @@ def build(force: bool = False) -> None:
     ref = os.path.join(_HERE, "_ref", "libnaive_ref.so")
     stale = (not os.path.exists(port)) or os.path.getmtime(port) < os.path.getmtime(src)
     ref_possible = os.path.exists("/root/reference/src/library/tools/ktest/naive/naive_blas.cpp")
+    shim = os.path.join(_HERE, "ref_shim.cpp")
+    if ref_possible and os.path.exists(ref) and os.path.getmtime(ref) < os.path.getmtime(shim):
+        force = True
     if force or stale or (ref_possible and not os.path.exists(ref)):
         subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True,
                        stdout=subprocess.DEVNULL)
@@ -73,6 +76,8 @@ def _lib(impl: str) -> ctypes.CDLL:
         getattr(lib, f"{prefix}{p}gemm").restype = None
         getattr(lib, f"{prefix}{p}trsm").argtypes = [i, i, i, i, i, sz, sz, ct, ptr, sz, ptr, sz]
         getattr(lib, f"{prefix}{p}trsm").restype = None
+        getattr(lib, f"{prefix}{p}trmm").argtypes = [i, i, i, i, i, sz, sz, ct, ptr, sz, ptr, sz]
+        getattr(lib, f"{prefix}{p}trmm").restype = None
     lib._prefix = prefix
     _libs[impl] = lib
     return lib
@@ -102,6 +107,15 @@ def trsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ld
     lib = _lib(impl)
     p = "s" if B.dtype == np.float32 else "d"
     fn = getattr(lib, f"{lib._prefix}{p}trsm")
+    fn(order, side, uplo, transA, diag, M, N, alpha, _p(A, offA), lda, _p(B, offB), ldb)
+
+
+def trmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+         impl: str = "port") -> None:
+    """B <- alpha op(A) B (Left) / alpha B op(A) (Right) in place on the flat buffer B."""
+    lib = _lib(impl)
+    p = "s" if B.dtype == np.float32 else "d"
+    fn = getattr(lib, f"{lib._prefix}{p}trmm")
     fn(order, side, uplo, transA, diag, M, N, alpha, _p(A, offA), lda, _p(B, offB), ldb)
 
 

@@ -116,3 +116,42 @@ void NAME(int order, int side, int uplo, int transA, int diag, size_t M, size_t 
 
 DEFINE_TRSM(oracle_strsm, float)
 DEFINE_TRSM(oracle_dtrsm, double)
+
+/* NaiveBlas::trmm (naive_blas.cpp:580-630): B <- alpha*op(A)*B (Left) / alpha*B*op(A) (Right), in place.
+ * Rows of the (possibly flipped) system are produced in the order that only consumes values of B
+ * not yet overwritten; the columns of a row are independent. */
+#define DEFINE_TRMM(NAME, T)                                                                   \
+void NAME(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, T alpha,    \
+          const T* A, size_t lda, T* B, size_t ldb)                                            \
+{                                                                                              \
+    size_t rowsA = (side == OLeft) ? M : N;                                                    \
+    size_t colsB = (side == OLeft) ? N : M;                                                    \
+    acc_t ma = make_acc(order, transA, lda);                                                   \
+    acc_t mb = make_acc(order, ONoTrans, ldb);                                                 \
+    int revPass = (uplo == OLower) ^ (transA != ONoTrans);                                     \
+    size_t i;                                                                                  \
+    if (side == ORight) {                                                                      \
+        ma.tra = !ma.tra;                                                                      \
+        mb.tra = !mb.tra;                                                                      \
+        revPass = !revPass;                                                                    \
+    }                                                                                          \
+    for (i = 0; i < rowsA; i++) {                                                              \
+        size_t row = revPass ? (rowsA - i - 1) : i;                                            \
+        size_t boundK = revPass ? row : (rowsA - row - 1);                                     \
+        long long j;                                                                           \
+        _Pragma("omp parallel for schedule(static)")                                           \
+        for (j = 0; j < (long long)colsB; j++) {                                               \
+            T tmp = (T)0.0;                                                                    \
+            size_t k;                                                                          \
+            for (k = 0; k <= boundK; k++) {                                                    \
+                size_t col = revPass ? k : (rowsA - k - 1);                                    \
+                T a = ((k == boundK) && (diag == OUnit)) ? (T)1.0 : A[at(ma, row, col)];       \
+                tmp = tmp + a * B[at(mb, col, (size_t)j)];                                     \
+            }                                                                                  \
+            B[at(mb, row, (size_t)j)] = tmp * alpha;                                           \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_TRMM(oracle_strmm, float)
+DEFINE_TRMM(oracle_dtrmm, double)

@@ -55,4 +55,20 @@ void ref_dtrsm(int order, int side, int uplo, int transA, int diag, size_t M, si
                             (NaiveBlas::clblasDiag)diag, M, N, alpha, A, lda, B, ldb);
 }
 
+void ref_strmm(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, float alpha,
+               const float* A, size_t lda, float* B, size_t ldb)
+{
+    NaiveBlas::trmm<float>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasSide)side,
+                           (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)transA,
+                           (NaiveBlas::clblasDiag)diag, M, N, alpha, A, lda, B, ldb);
+}
+
+void ref_dtrmm(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, double alpha,
+               const double* A, size_t lda, double* B, size_t ldb)
+{
+    NaiveBlas::trmm<double>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasSide)side,
+                            (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)transA,
+                            (NaiveBlas::clblasDiag)diag, M, N, alpha, A, lda, B, ldb);
+}
+
 }  // extern "C"

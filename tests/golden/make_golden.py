@@ -17,7 +17,7 @@ import numpy as np
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "..", ".."))
 import oracle  # noqa: E402
-from tests import cases  # noqa: E402
+from tests import cases, cases_trmm  # noqa: E402
 
 
 def main():
@@ -32,6 +32,11 @@ def main():
     for name, c in cases.golden_trsm_cases().items():
         A, B = cases.trsm_buffers(c)
         oracle.trsm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A,
+                    c["offA"], c["lda"], B, c["offB"], c["ldb"], impl="ref")
+        out[name] = B
+    for name, c in cases_trmm.golden_trmm_cases().items():
+        A, B = cases_trmm.trmm_buffers(c)
+        oracle.trmm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A,
                     c["offA"], c["lda"], B, c["offB"], c["ldb"], impl="ref")
         out[name] = B
     path = os.path.join(os.path.dirname(__file__), "level3_golden.npz")
