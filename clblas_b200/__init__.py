@@ -73,6 +73,10 @@ def _load() -> ctypes.CDLL:
         f = getattr(lib, name)
         f.argtypes = [i, i, i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
+    for name, ft in (("clblasSsyrk", ctypes.c_float), ("clblasDsyrk", ctypes.c_double)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, sz, sz, ft, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
+        f.restype = i
     lib.clblasSetup.argtypes = []
     lib.clblasSetup.restype = i
     lib.clblasTeardown.argtypes = []
@@ -99,7 +103,7 @@ lib = _load()
 EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "clblasDgemm", "clblasStrsm",
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
-           "clblasStrmm", "clblasDtrmm"]
+           "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -204,6 +208,20 @@ def clblasDtrmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, o
                 queues=None, wait=None, events=None) -> int:
     return _trsm(lib.clblasDtrmm, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
                  queues, wait, events)
+
+
+def _syrk(fn, order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, queues, wait, events):
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return fn(order, uplo, transA, N, K, alpha, _ptr(A), offA, lda, beta, _ptr(C), offC, ldc, nq, q, nw, w, e)
+
+
+def clblasSsyrk(order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, queues=None, wait=None, events=None) -> int:
+    """C <- alpha*op(A)*op(A)^T + beta*C on one triangle of C (src/clBLAS.h:8279-8296)."""
+    return _syrk(lib.clblasSsyrk, order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, queues, wait, events)
+
+
+def clblasDsyrk(order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, queues=None, wait=None, events=None) -> int:
+    return _syrk(lib.clblasDsyrk, order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, queues, wait, events)
 
 
 NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = 4096, 8192

@@ -43,7 +43,7 @@ static void usage()
     std::puts("clblas_b200_client options (same meaning as the clBLAS client):\n"
               "  -m/--sizem -n/--sizen -k/--sizek  --lda --ldb --ldc  --offA --offBX --offCY\n"
               "  --alpha --beta  -o/--order (0 row, 1 column)  --transposeA --transposeB (0/1/2)\n"
-              "  -f/--function gemm|trsm|trmm  -r/--precision s|d  --side --uplo --diag\n"
+              "  -f/--function gemm|trsm|trmm|syrk  -r/--precision s|d  --side --uplo --diag\n"
               "  -p/--profile samples (20)  --apiCallCount calls per sample (10)  -v/--validate 0|1");
 }
 
@@ -92,13 +92,17 @@ static void stored(int order, int trans, size_t rows, size_t cols, size_t& inner
 template <typename T>
 static int run(const Options& o)
 {
-    const bool gemm = o.function == "gemm";
+    const bool gemm = o.function == "gemm", syrk = o.function == "syrk";
     size_t ai, ao, bi, bo, ci = 0, co = 0;
     const size_t tri = o.side == 0 ? o.M : o.N;
     if (gemm) {
         stored(o.order, o.transA, o.M, o.K, ai, ao);
         stored(o.order, o.transB, o.K, o.N, bi, bo);
         stored(o.order, 0, o.M, o.N, ci, co);
+    } else if (syrk) {
+        // A is N x K (K x N when transposed); the "B" buffer holds the N x N matrix C
+        stored(o.order, o.transA, o.N, o.K, ai, ao);
+        stored(o.order, 0, o.N, o.N, bi, bo);
     } else {
         ai = ao = tri;
         stored(o.order, 0, o.M, o.N, bi, bo);
@@ -110,7 +114,7 @@ static int run(const Options& o)
     std::vector<T> hA(na), hB(nb), hC(nc ? nc : 1);
     std::srand(10);
     auto rnd = [] { return (T)((std::rand() % 20) - 10) / (T)10; };
-    if (gemm) {
+    if (gemm || syrk) {
         for (auto& v : hA) v = rnd();
         for (auto& v : hB) v = rnd();
         for (auto& v : hC) v = rnd();
@@ -141,6 +145,13 @@ static int run(const Options& o)
                                    (float)o.alpha, dA, o.offA, lda, dB, o.offB, ldb, (float)o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
             return clblasDgemm((clblasOrder)o.order, (clblasTranspose)o.transA, (clblasTranspose)o.transB, o.M, o.N, o.K,
                                o.alpha, dA, o.offA, lda, dB, o.offB, ldb, o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+        }
+        if (syrk) {
+            if (sizeof(T) == 4)
+                return clblasSsyrk((clblasOrder)o.order, (clblasUplo)o.uplo, (clblasTranspose)o.transA, o.N, o.K, (float)o.alpha,
+                                   dA, o.offA, lda, (float)o.beta, dB, o.offB, ldb, 1, &q, 0, nullptr, nullptr);
+            return clblasDsyrk((clblasOrder)o.order, (clblasUplo)o.uplo, (clblasTranspose)o.transA, o.N, o.K, o.alpha,
+                               dA, o.offA, lda, o.beta, dB, o.offB, ldb, 1, &q, 0, nullptr, nullptr);
         }
         if (o.function == "trmm") {
             if (sizeof(T) == 4)
@@ -213,6 +224,7 @@ static int run(const Options& o)
     double flop;
     std::string formula;
     if (gemm) { flop = 2.0 * o.M * o.N * o.K; formula = "2.0*M*N*K/time"; }
+    else if (syrk) { flop = (double)o.N * (o.N + 1) * o.K; formula = "N*(N+1)*K/time"; }
     else if (o.side == 0) { flop = (double)o.M * (o.M + 1) * o.N; formula = "M*(M+1)*N/time"; }
     else { flop = (double)o.M * (o.N + 1) * o.N; formula = "M*(N+1)*N/time"; }
     const double gflops = flop / per_call_ns;
@@ -236,7 +248,7 @@ int main(int argc, char** argv)
 {
     Options o;
     if (!parse(argc, argv, o)) { usage(); return 1; }
-    if (o.function != "gemm" && o.function != "trsm" && o.function != "trmm") { std::fprintf(stderr, "function must be gemm, trsm or trmm\n"); return 1; }
+    if (o.function != "gemm" && o.function != "trsm" && o.function != "trmm" && o.function != "syrk") { std::fprintf(stderr, "function must be gemm, trsm, trmm or syrk\n"); return 1; }
     if (o.precision == "s") return run<float>(o);
     if (o.precision == "d") return run<double>(o);
     std::fprintf(stderr, "precision must be s or d\n");

@@ -242,6 +242,38 @@ clblasStatus trmm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clb
     return record_out(s, events);
 }
 
+// clblasSsyrk / clblasDsyrk: checks of the reference's doSyrk (src/library/blas/xsyrk.c:48-70): initialised,
+// queues (InvalidValue there), memory objects A and C, A sizes (N x K as op(A)), C sizes (N x N).
+template <typename T>
+clblasStatus syrk_entry(clblasOrder order, clblasUplo uplo, clblasTranspose transA, size_t N, size_t K, T alpha,
+                        const void* A, size_t offA, size_t lda, T beta, void* C, size_t offC, size_t ldc,
+                        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (nq == 0 || queues == nullptr) return clblasInvalidValue;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)uplo > 1u || (unsigned)transA > 2u) return clblasInvalidValue;
+    if ((st = check_matrix_sizes(sizeof(T), order, transA, N, K, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, N, N, C, offC, ldc, SET_C)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool lower = (uplo == clblasLower), trans = (transA != clblasNoTrans);
+    if (order == clblasRowMajor) {
+        // a row-major matrix is its transpose in column-major: the other triangle of C, and A^T stored
+        lower = !lower;
+        trans = !trans;
+    }
+    cudaError_t e = syrk_colmajor<T>(lower, trans, N, K, alpha, static_cast<const T*>(A) + offA, lda, beta,
+                                     static_cast<T*>(C) + offC, ldc, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 }  // namespace
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -360,6 +392,20 @@ clblasStatus clblasDtrmm(clblasOrder order, clblasSide side, clblasUplo uplo, cl
 {
     return trmm_entry<double>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
                               nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasSsyrk(clblasOrder order, clblasUplo uplo, clblasTranspose transA, size_t N, size_t K, float alpha,
+                         const clblasMem A, size_t offA, size_t lda, float beta, clblasMem C, size_t offC, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return syrk_entry<float>(order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasDsyrk(clblasOrder order, clblasUplo uplo, clblasTranspose transA, size_t N, size_t K, double alpha,
+                         const clblasMem A, size_t offA, size_t lda, double beta, clblasMem C, size_t offC, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return syrk_entry<double>(order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, nq, queues, nev, wait, events);
 }
 
 clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,

@@ -22,7 +22,27 @@ struct GemmProblem {
     const T* B; size_t ldb;
     T beta;
     T* C; size_t ldc;
+    // 0: all of C; TRI_LOWER / TRI_UPPER: only entries with row >= col / row <= col are computed and
+    // stored (SYRK); tiles entirely outside the triangle exit at once, the others mask their stores.
+    int tri = 0;
 };
+
+enum { TRI_FULL = 0, TRI_LOWER = 1, TRI_UPPER = 2 };
+
+// true when no entry of the bm x bn tile at (m0, n0) lies in the triangle
+__host__ __device__ inline bool tri_tile_outside(int tri, size_t m0, size_t bm, size_t n0, size_t bn)
+{
+    return tri == TRI_LOWER ? m0 + bm - 1 < n0 : tri == TRI_UPPER ? n0 + bn - 1 < m0 : false;
+}
+// true when every entry of the tile lies in the triangle (no masking needed)
+__host__ __device__ inline bool tri_tile_inside(int tri, size_t m0, size_t bm, size_t n0, size_t bn)
+{
+    return tri == TRI_LOWER ? m0 >= n0 + bn - 1 : tri == TRI_UPPER ? n0 >= m0 + bm - 1 : true;
+}
+__host__ __device__ inline bool tri_masked(int tri, size_t row, size_t col)
+{
+    return tri == TRI_LOWER ? row < col : tri == TRI_UPPER ? row > col : false;
+}
 
 // Kernel families (reported by clblasB200LastGemmKernel).
 enum GemmPath { PATH_AUTO = 0, PATH_SIMT_LDG = 1, PATH_TMA_ONE_CTA = 2, PATH_TMA_TWO_CTAS = 3, PATH_3XTF32 = 4 };
@@ -74,6 +94,12 @@ void trsm_release_workspaces();
 template <typename T>
 cudaError_t trmm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
                           const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
+
+// Symmetric rank-k update of one triangle of C (column-major): C <- alpha*op(A)*op(A)^T + beta*C,
+// op(A) = A (N x K) or A^T (A stored K x N).
+template <typename T>
+cudaError_t syrk_colmajor(bool lower, bool trans, size_t N, size_t K, T alpha, const T* A, size_t lda, T beta,
+                          T* C, size_t ldc, cudaStream_t s);
 
 // Stream-ordered workspace from the library's own per-device pool (workspace.cu).
 cudaError_t ws_alloc(void** ptr, size_t bytes, cudaStream_t s);

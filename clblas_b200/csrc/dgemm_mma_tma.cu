@@ -55,7 +55,7 @@ template <bool TA, bool TB, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      double* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, double alpha, double beta,
-                     unsigned tilesM, unsigned tilesN, unsigned wave)
+                     unsigned tilesM, unsigned tilesN, unsigned wave, int tri)
 {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -77,6 +77,8 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         tn = r / rows;
     }
     const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
+    if (tri_tile_outside(tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
+    if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
     const int nk = (int)((K + BK - 1) / BK);
     // Every other wave of CTAs walks K backwards: it starts on the K range the wave before it
     // finished on, which is what L2 still holds, instead of re-streaming those panels from DRAM.
@@ -174,7 +176,7 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
 #pragma unroll
             for (int mi = 0; mi < 8; mi++) {
                 const size_t row = m0 + wm * 64 + mi * 8 + (TA ? pg : g);
-                if (row >= M) continue;
+                if (row >= M || tri_masked(tri, row, col)) continue;
                 double r = alpha * acc[mi][ni][e];
                 if (useC) r = fma(beta, cc[row], r);
                 cc[row] = r;
@@ -205,7 +207,7 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
     dgemm_mma_tma_kernel<TA, TB, BN><<<(unsigned)(tilesM * tilesN), THREADS, smem_bytes(BN), s>>>(
-        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 1));
+        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 1), p.tri);
     count_launch();
     return cudaGetLastError();
 }

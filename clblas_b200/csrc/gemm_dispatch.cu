@@ -60,7 +60,7 @@ cudaError_t gemm_any(const GemmProblem<T>& p, cudaStream_t s)
     cudaError_t e = degenerate(p, s, &handled);
     if (handled) return e;
     if (forced_gemm_path() == PATH_SIMT_LDG) return launch_gemm_simt<T>(p, s);
-    if (forced_gemm_path() == PATH_3XTF32 && t_forbid_alloc == 0) {
+    if (forced_gemm_path() == PATH_3XTF32 && t_forbid_alloc == 0 && p.tri == TRI_FULL) {
         e = try_3xtf32(p, s);
         if (e != cudaErrorNotSupported) return e;
     }
@@ -98,7 +98,9 @@ cudaError_t gemm_any(const GemmProblem<T>& p, cudaStream_t s)
     const size_t a_ld = fa == TRANSPOSE ? round_up(a_cols, Q) : round_up(a_rows, Q);
     const size_t a_n = fa == KEEP ? 0 : a_ld * (fa == TRANSPOSE ? a_rows : a_cols);
     const size_t b_ld = fb == TRANSPOSE ? round_up(b_cols, Q) : round_up(b_rows, Q);
-    const size_t b_n = fb == KEEP ? 0 : b_ld * (fb == TRANSPOSE ? b_rows : b_cols);
+    // A * A^T (rank-k update): both operands are one stored matrix, repacked once
+    const bool same = fa != KEEP && fa == fb && p.A == p.B && p.lda == p.ldb && a_rows == b_rows && a_cols == b_cols;
+    const size_t b_n = fb == KEEP || same ? 0 : b_ld * (fb == TRANSPOSE ? b_rows : b_cols);
     T* ws = nullptr;
     e = ws_alloc(reinterpret_cast<void**>(&ws), (round_up(a_n, 64) + b_n) * sizeof(T) + 256, s);
     if (e != cudaSuccess) {
@@ -115,7 +117,10 @@ cudaError_t gemm_any(const GemmProblem<T>& p, cudaStream_t s)
         q.A = ws; q.lda = a_ld;
         if (fa == TRANSPOSE) q.ta = !p.ta;
     }
-    if (e == cudaSuccess && fb != KEEP) {
+    if (same) {
+        q.B = ws; q.ldb = a_ld;
+        if (fb == TRANSPOSE) q.tb = !p.tb;
+    } else if (e == cudaSuccess && fb != KEEP) {
         T* wb = ws + round_up(a_n, 64);
         e = launch_repack<T>(wb, b_ld, p.B, p.ldb, b_rows, b_cols, fb == TRANSPOSE, s);
         q.B = wb; q.ldb = b_ld;

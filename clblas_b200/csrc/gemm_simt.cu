@@ -51,6 +51,7 @@ gemm_simt_kernel(const GemmProblem<T> p, const unsigned tilesM)
     const size_t m0 = (size_t)(blockIdx.x % tilesM) * BM;
     const size_t n0 = (size_t)(blockIdx.x / tilesM) * BN;
     const size_t M = p.M, N = p.N, K = p.K;
+    if (tri_tile_outside(p.tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
 
     // ---- loader mapping: f = index along the memory-contiguous direction, s = the strided one
     constexpr int FA = TA ? BK : BM;           // extent of f for A
@@ -144,7 +145,7 @@ gemm_simt_kernel(const GemmProblem<T> p, const unsigned tilesM)
 #pragma unroll
                 for (int jm = 0; jm < V; jm++) {
                     const size_t m = m0 + cm * (BM / CM) + tx * V + jm;
-                    if (m >= M) continue;
+                    if (m >= M || tri_masked(p.tri, m, n)) continue;
                     T* c = p.C + m + n * p.ldc;
                     T r = alpha * acc[cm * V + jm][cn * V + jn];
                     if (useC) r = fma(beta, *c, r);

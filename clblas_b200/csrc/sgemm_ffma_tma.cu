@@ -65,7 +65,7 @@ template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                      unsigned tilesM, unsigned tilesN, unsigned wave)
+                      unsigned tilesM, unsigned tilesN, unsigned wave, int tri)
 {
     constexpr int STAGE_BYTES = stage_bytes(BN);
     constexpr int NJ = BN / 16;                     // columns per thread: 8 or 4
@@ -88,6 +88,8 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         tn = r / rows;
     }
     const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
+    if (tri_tile_outside(tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
+    if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
     const int nk = (int)((K + BK - 1) / BK);
     // Every other wave of CTAs walks K backwards: it starts on the K range the wave before it
     // finished on, which is what L2 still holds, instead of re-streaming those panels from DRAM.
@@ -220,7 +222,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 
     // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
     const bool useC = (beta != 0.f);
-    const bool vec = !TA && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
+    const bool vec = !TA && tri == TRI_FULL && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const size_t col = n0 + colB(j);
@@ -243,7 +245,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
                 } else {
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        if (row + e < M) {
+                        if (row + e < M && !tri_masked(tri, row + e, col)) {
                             float r = alpha * acc[4 * h + e][j];
                             if (useC) r = fmaf(beta, cc[row + e], r);
                             cc[row + e] = r;
@@ -255,7 +257,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const size_t row = m0 + rowA(i);
-                if (row < M) {
+                if (row < M && !tri_masked(tri, row, col)) {
                     float r = alpha * acc[i][j];
                     if (useC) r = fmaf(beta, cc[row], r);
                     cc[row] = r;
@@ -290,7 +292,7 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
     sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
-        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * MIN_CTAS));
+        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * MIN_CTAS), p.tri);
     count_launch();
     return cudaGetLastError();
 }

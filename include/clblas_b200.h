@@ -159,6 +159,30 @@ clblasStatus clblasDtrmm(
     unsigned numCommandQueues, clblasQueue* commandQueues,
     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
 
+/* ---- SYRK: replaces clblasSsyrk (src/clBLAS.h:8279-8296) and clblasDsyrk (:8351-8368), implemented by
+ *      src/library/blas/xsyrk.c in the reference.  C <- alpha*op(A)*op(A)^T + beta*C on the `uplo` triangle of
+ *      the N x N matrix C, op(A) N x K; the other triangle of C is neither read nor written.  Checks in the
+ *      reference's order (xsyrk.c:48-70): NotInitialized, queues (InvalidValue), NULL A/C, A sizes, C sizes. */
+clblasStatus clblasSsyrk(
+    clblasOrder order, clblasUplo uplo, clblasTranspose transA,
+    size_t N, size_t K,
+    float alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    float beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasDsyrk(
+    clblasOrder order, clblasUplo uplo, clblasTranspose transA,
+    size_t N, size_t K,
+    double alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    double beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- DTRSM that allocates nothing (no counterpart in the reference, whose DTRSM creates and
  *      releases two OpenCL buffers inside every call, src/library/blas/xtrsm.cc:1183-1207).
  *      Same arguments, checks and result as clblasDtrsm, but the blocked solve's workspace is a

@@ -78,6 +78,8 @@ def _lib(impl: str) -> ctypes.CDLL:
         getattr(lib, f"{prefix}{p}trsm").restype = None
         getattr(lib, f"{prefix}{p}trmm").argtypes = [i, i, i, i, i, sz, sz, ct, ptr, sz, ptr, sz]
         getattr(lib, f"{prefix}{p}trmm").restype = None
+        getattr(lib, f"{prefix}{p}syrk").argtypes = [i, i, i, sz, sz, ct, ptr, sz, ct, ptr, sz]
+        getattr(lib, f"{prefix}{p}syrk").restype = None
     lib._prefix = prefix
     _libs[impl] = lib
     return lib
@@ -117,6 +119,14 @@ def trmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ld
     p = "s" if B.dtype == np.float32 else "d"
     fn = getattr(lib, f"{lib._prefix}{p}trmm")
     fn(order, side, uplo, transA, diag, M, N, alpha, _p(A, offA), lda, _p(B, offB), ldb)
+
+
+def syrk(order, uplo, trans, N, K, alpha, A, offA, lda, beta, C, offC, ldc, impl: str = "port") -> None:
+    """C <- alpha op(A) op(A)^T + beta C on the uplo triangle, in place on the flat buffer C."""
+    lib = _lib(impl)
+    p = "s" if C.dtype == np.float32 else "d"
+    fn = getattr(lib, f"{lib._prefix}{p}syrk")
+    fn(order, uplo, trans, N, K, alpha, _p(A, offA), lda, beta, _p(C, offC), ldc)
 
 
 # --------------------------------------------------------------------------------------------

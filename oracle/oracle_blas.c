@@ -155,3 +155,29 @@ void NAME(int order, int side, int uplo, int transA, int diag, size_t M, size_t 
 
 DEFINE_TRMM(oracle_strmm, float)
 DEFINE_TRMM(oracle_dtrmm, double)
+
+/* NaiveBlas::syrk (naive_blas.cpp:692-727): C <- alpha*op(A)*op(A)^T + beta*C on the uplo triangle of C;
+ * op(A) is N x K (ConjTrans counts as Trans).  Entries outside the triangle are not touched. */
+#define DEFINE_SYRK(NAME, T)                                                                   \
+void NAME(int order, int uplo, int trans, size_t N, size_t K, T alpha, const T* A, size_t lda, \
+          T beta, T* C, size_t ldc)                                                            \
+{                                                                                              \
+    acc_t ma = make_acc(order, trans == ONoTrans ? ONoTrans : OTrans, lda);                    \
+    acc_t mc = make_acc(order, ONoTrans, ldc);                                                 \
+    long long i;                                                                               \
+    _Pragma("omp parallel for schedule(dynamic, 8)")                                           \
+    for (i = 0; i < (long long)N; i++) {                                                       \
+        size_t j, k;                                                                           \
+        for (j = 0; j < N; j++) {                                                              \
+            T tmp = (T)0.0;                                                                    \
+            if ((uplo == OLower && j > (size_t)i) || (uplo == OUpper && (size_t)i > j)) continue; \
+            for (k = 0; k < K; k++) {                                                          \
+                tmp = tmp + A[at(ma, (size_t)i, k)] * A[at(ma, j, k)];                         \
+            }                                                                                  \
+            C[at(mc, (size_t)i, j)] = C[at(mc, (size_t)i, j)] * beta + tmp * alpha;            \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_SYRK(oracle_ssyrk, float)
+DEFINE_SYRK(oracle_dsyrk, double)

@@ -71,4 +71,18 @@ void ref_dtrmm(int order, int side, int uplo, int transA, int diag, size_t M, si
                             (NaiveBlas::clblasDiag)diag, M, N, alpha, A, lda, B, ldb);
 }
 
+void ref_ssyrk(int order, int uplo, int trans, size_t N, size_t K, float alpha, const float* A, size_t lda,
+               float beta, float* C, size_t ldc)
+{
+    NaiveBlas::syrk<float>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)trans,
+                           N, K, alpha, A, lda, beta, C, ldc);
+}
+
+void ref_dsyrk(int order, int uplo, int trans, size_t N, size_t K, double alpha, const double* A, size_t lda,
+               double beta, double* C, size_t ldc)
+{
+    NaiveBlas::syrk<double>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)trans,
+                            N, K, alpha, A, lda, beta, C, ldc);
+}
+
 }  // extern "C"

@@ -17,7 +17,7 @@ import numpy as np
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "..", ".."))
 import oracle  # noqa: E402
-from tests import cases, cases_trmm  # noqa: E402
+from tests import cases, cases_syrk, cases_trmm  # noqa: E402
 
 
 def main():
@@ -39,6 +39,11 @@ def main():
         oracle.trmm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A,
                     c["offA"], c["lda"], B, c["offB"], c["ldb"], impl="ref")
         out[name] = B
+    for name, c in cases_syrk.golden_syrk_cases().items():
+        A, C = cases_syrk.syrk_buffers(c)
+        oracle.syrk(c["order"], c["uplo"], c["trans"], c["N"], c["K"], c["alpha"], A, c["offA"], c["lda"], c["beta"], C,
+                    c["offC"], c["ldc"], impl="ref")
+        out[name] = C
     path = os.path.join(os.path.dirname(__file__), "level3_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} cases, {os.path.getsize(path)} bytes")
