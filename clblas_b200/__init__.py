@@ -77,6 +77,14 @@ def _load() -> ctypes.CDLL:
         f = getattr(lib, name)
         f.argtypes = [i, i, i, sz, sz, ft, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
+    for name, ft in (("clblasSsyr2k", ctypes.c_float), ("clblasDsyr2k", ctypes.c_double)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
+        f.restype = i
+    for name, ft in (("clblasSsymm", ctypes.c_float), ("clblasDsymm", ctypes.c_double)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
+        f.restype = i
     lib.clblasSetup.argtypes = []
     lib.clblasSetup.restype = i
     lib.clblasTeardown.argtypes = []
@@ -103,7 +111,8 @@ lib = _load()
 EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "clblasDgemm", "clblasStrsm",
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
-           "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk"]
+           "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
+           "clblasSsymm", "clblasDsymm"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -222,6 +231,37 @@ def clblasSsyrk(order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, l
 
 def clblasDsyrk(order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, queues=None, wait=None, events=None) -> int:
     return _syrk(lib.clblasDsyrk, order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, queues, wait, events)
+
+
+def _abc(fn, e0, e1, e2, d0, d1, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, queues, wait, events):
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return fn(e0, e1, e2, d0, d1, alpha, _ptr(A), offA, lda, _ptr(B), offB, ldb, beta, _ptr(C), offC, ldc, nq, q, nw, w, e)
+
+
+def clblasSsyr2k(order, uplo, transAB, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                 queues=None, wait=None, events=None) -> int:
+    """C <- alpha*op(A)*op(B)^T + alpha*op(B)*op(A)^T + beta*C on one triangle of C (src/clBLAS.h:8568-8589)."""
+    return _abc(lib.clblasSsyr2k, order, uplo, transAB, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues, wait, events)
+
+
+def clblasDsyr2k(order, uplo, transAB, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                 queues=None, wait=None, events=None) -> int:
+    return _abc(lib.clblasDsyr2k, order, uplo, transAB, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues, wait, events)
+
+
+def clblasSsymm(order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues=None, wait=None, events=None) -> int:
+    """C <- alpha*A*B + beta*C (Left) / alpha*B*A + beta*C (Right), A symmetric (src/clBLAS.h:8898-8919)."""
+    return _abc(lib.clblasSsymm, order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues, wait, events)
+
+
+def clblasDsymm(order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues=None, wait=None, events=None) -> int:
+    return _abc(lib.clblasDsymm, order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues, wait, events)
 
 
 NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = 4096, 8192

@@ -43,7 +43,7 @@ static void usage()
     std::puts("clblas_b200_client options (same meaning as the clBLAS client):\n"
               "  -m/--sizem -n/--sizen -k/--sizek  --lda --ldb --ldc  --offA --offBX --offCY\n"
               "  --alpha --beta  -o/--order (0 row, 1 column)  --transposeA --transposeB (0/1/2)\n"
-              "  -f/--function gemm|trsm|trmm|syrk  -r/--precision s|d  --side --uplo --diag\n"
+              "  -f/--function gemm|trsm|trmm|syrk|syr2k|symm  -r/--precision s|d  --side --uplo --diag\n"
               "  -p/--profile samples (20)  --apiCallCount calls per sample (10)  -v/--validate 0|1");
 }
 
@@ -92,10 +92,20 @@ static void stored(int order, int trans, size_t rows, size_t cols, size_t& inner
 template <typename T>
 static int run(const Options& o)
 {
-    const bool gemm = o.function == "gemm", syrk = o.function == "syrk";
+    const bool syr2k = o.function == "syr2k", symm = o.function == "symm";
+    const bool gemm = o.function == "gemm" || syr2k || symm, syrk = o.function == "syrk";
     size_t ai, ao, bi, bo, ci = 0, co = 0;
     const size_t tri = o.side == 0 ? o.M : o.N;
-    if (gemm) {
+    if (syr2k) {
+        // A and B are N x K (K x N when transposed), C is N x N
+        stored(o.order, o.transA, o.N, o.K, ai, ao);
+        stored(o.order, o.transA, o.N, o.K, bi, bo);
+        stored(o.order, 0, o.N, o.N, ci, co);
+    } else if (symm) {
+        ai = ao = tri;
+        stored(o.order, 0, o.M, o.N, bi, bo);
+        stored(o.order, 0, o.M, o.N, ci, co);
+    } else if (gemm) {
         stored(o.order, o.transA, o.M, o.K, ai, ao);
         stored(o.order, o.transB, o.K, o.N, bi, bo);
         stored(o.order, 0, o.M, o.N, ci, co);
@@ -139,6 +149,20 @@ static int run(const Options& o)
     clblasB200SetGemmPath(o.path);
 
     auto call = [&]() -> clblasStatus {
+        if (syr2k) {
+            if (sizeof(T) == 4)
+                return clblasSsyr2k((clblasOrder)o.order, (clblasUplo)o.uplo, (clblasTranspose)o.transA, o.N, o.K, (float)o.alpha,
+                                    dA, o.offA, lda, dB, o.offB, ldb, (float)o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+            return clblasDsyr2k((clblasOrder)o.order, (clblasUplo)o.uplo, (clblasTranspose)o.transA, o.N, o.K, o.alpha,
+                                dA, o.offA, lda, dB, o.offB, ldb, o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+        }
+        if (symm) {
+            if (sizeof(T) == 4)
+                return clblasSsymm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, o.M, o.N, (float)o.alpha,
+                                   dA, o.offA, lda, dB, o.offB, ldb, (float)o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+            return clblasDsymm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, o.M, o.N, o.alpha,
+                               dA, o.offA, lda, dB, o.offB, ldb, o.beta, dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+        }
         if (gemm) {
             if (sizeof(T) == 4)
                 return clblasSgemm((clblasOrder)o.order, (clblasTranspose)o.transA, (clblasTranspose)o.transB, o.M, o.N, o.K,
@@ -171,7 +195,7 @@ static int run(const Options& o)
     if (st != clblasSuccess) { std::fprintf(stderr, "call failed with status %d\n", (int)st); return 3; }
     CUDA_OK(cudaStreamSynchronize(stream));
 
-    if (o.validate && gemm) {
+    if (o.validate && gemm && !syr2k && !symm) {
         // spot check of 64 entries against a double-precision host evaluation of the same inputs
         std::vector<T> out(nc);
         CUDA_OK(cudaMemcpy(out.data(), dC, nc * sizeof(T), cudaMemcpyDeviceToHost));
@@ -223,7 +247,9 @@ static int run(const Options& o)
     const double per_call_ns = mean / o.apiCallCount;
     double flop;
     std::string formula;
-    if (gemm) { flop = 2.0 * o.M * o.N * o.K; formula = "2.0*M*N*K/time"; }
+    if (syr2k) { flop = 2.0 * o.N * (o.N + 1) * o.K; formula = "2*N*(N+1)*K/time"; }
+    else if (symm) { flop = 2.0 * o.M * o.N * (o.side == 0 ? o.M : o.N); formula = o.side == 0 ? "2*M*M*N/time" : "2*M*N*N/time"; }
+    else if (gemm) { flop = 2.0 * o.M * o.N * o.K; formula = "2.0*M*N*K/time"; }
     else if (syrk) { flop = (double)o.N * (o.N + 1) * o.K; formula = "N*(N+1)*K/time"; }
     else if (o.side == 0) { flop = (double)o.M * (o.M + 1) * o.N; formula = "M*(M+1)*N/time"; }
     else { flop = (double)o.M * (o.N + 1) * o.N; formula = "M*(N+1)*N/time"; }
@@ -248,7 +274,10 @@ int main(int argc, char** argv)
 {
     Options o;
     if (!parse(argc, argv, o)) { usage(); return 1; }
-    if (o.function != "gemm" && o.function != "trsm" && o.function != "trmm" && o.function != "syrk") { std::fprintf(stderr, "function must be gemm, trsm, trmm or syrk\n"); return 1; }
+    if (o.function != "gemm" && o.function != "trsm" && o.function != "trmm" && o.function != "syrk" && o.function != "syr2k" && o.function != "symm") {
+        std::fprintf(stderr, "function must be gemm, trsm, trmm, syrk, syr2k or symm\n");
+        return 1;
+    }
     if (o.precision == "s") return run<float>(o);
     if (o.precision == "d") return run<double>(o);
     std::fprintf(stderr, "precision must be s or d\n");

@@ -274,6 +274,76 @@ clblasStatus syrk_entry(clblasOrder order, clblasUplo uplo, clblasTranspose tran
     return record_out(s, events);
 }
 
+// SYR2K front end.  Check order of the reference's doSyr2k (src/library/blas/xsyr2k.c:52-78).
+template <typename T>
+clblasStatus syr2k_entry(clblasOrder order, clblasUplo uplo, clblasTranspose transAB, size_t N, size_t K, T alpha,
+                         const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb, T beta,
+                         void* C, size_t offC, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (nq == 0 || queues == nullptr) return clblasInvalidValue;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)uplo > 1u || (unsigned)transAB > 2u) return clblasInvalidValue;
+    if ((st = check_matrix_sizes(sizeof(T), order, transAB, N, K, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(sizeof(T), order, transAB, N, K, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, N, N, C, offC, ldc, SET_C)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool lower = (uplo == clblasLower), trans = (transAB != clblasNoTrans);
+    if (order == clblasRowMajor) {
+        lower = !lower;
+        trans = !trans;
+    }
+    cudaError_t e = syr2k_colmajor<T>(lower, trans, N, K, alpha, static_cast<const T*>(A) + offA, lda,
+                                      static_cast<const T*>(B) + offB, ldb, beta, static_cast<T*>(C) + offC, ldc, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
+// SYMM front end.  Check order of the reference's doSymm (src/library/blas/xsymm.c): memory objects and
+// sizes first, then the queues and the wait list; a row-major call is the column-major call on the
+// transposed problem (other side, other triangle, M and N exchanged), as there.
+template <typename T>
+clblasStatus symm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, size_t M, size_t N, T alpha,
+                        const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb, T beta,
+                        void* C, size_t offC, size_t ldc,
+                        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u) return clblasInvalidValue;
+    const size_t n = (side == clblasLeft) ? M : N;
+    if ((st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, n, n, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, M, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, M, N, C, offC, ldc, SET_C)) != clblasSuccess) return st;
+    if (nq == 0 || queues == nullptr) return clblasInvalidValue;
+    if (nev != 0 && wait == nullptr) return clblasInvalidEventWaitList;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = symm_colmajor<T>(right, lower, M, N, alpha, static_cast<const T*>(A) + offA, lda,
+                                     static_cast<const T*>(B) + offB, ldb, beta, static_cast<T*>(C) + offC, ldc, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 }  // namespace
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -406,6 +476,38 @@ clblasStatus clblasDsyrk(clblasOrder order, clblasUplo uplo, clblasTranspose tra
                          unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
 {
     return syrk_entry<double>(order, uplo, transA, N, K, alpha, A, offA, lda, beta, C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasSsyr2k(clblasOrder order, clblasUplo uplo, clblasTranspose transAB, size_t N, size_t K, float alpha,
+                          const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb, float beta,
+                          clblasMem C, size_t offC, size_t ldc,
+                          unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return syr2k_entry<float>(order, uplo, transAB, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasDsyr2k(clblasOrder order, clblasUplo uplo, clblasTranspose transAB, size_t N, size_t K, double alpha,
+                          const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb, double beta,
+                          clblasMem C, size_t offC, size_t ldc,
+                          unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return syr2k_entry<double>(order, uplo, transAB, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasSsymm(clblasOrder order, clblasSide side, clblasUplo uplo, size_t M, size_t N, float alpha,
+                         const clblasMem A, size_t offa, size_t lda, const clblasMem B, size_t offb, size_t ldb, float beta,
+                         clblasMem C, size_t offc, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return symm_entry<float>(order, side, uplo, M, N, alpha, A, offa, lda, B, offb, ldb, beta, C, offc, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasDsymm(clblasOrder order, clblasSide side, clblasUplo uplo, size_t M, size_t N, double alpha,
+                         const clblasMem A, size_t offa, size_t lda, const clblasMem B, size_t offb, size_t ldb, double beta,
+                         clblasMem C, size_t offc, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return symm_entry<double>(order, side, uplo, M, N, alpha, A, offa, lda, B, offb, ldb, beta, C, offc, ldc, nq, queues, nev, wait, events);
 }
 
 clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,

@@ -101,6 +101,17 @@ template <typename T>
 cudaError_t syrk_colmajor(bool lower, bool trans, size_t N, size_t K, T alpha, const T* A, size_t lda, T beta,
                           T* C, size_t ldc, cudaStream_t s);
 
+// Symmetric rank-2k update of one triangle of C: C <- alpha*op(A)*op(B)^T + alpha*op(B)*op(A)^T + beta*C.
+template <typename T>
+cudaError_t syr2k_colmajor(bool lower, bool trans, size_t N, size_t K, T alpha, const T* A, size_t lda, const T* B,
+                           size_t ldb, T beta, T* C, size_t ldc, cudaStream_t s);
+
+// C <- alpha*A*B + beta*C (A symmetric M x M) or alpha*B*A + beta*C (right; A symmetric N x N); only the
+// `lower` / upper triangle of A is read.
+template <typename T>
+cudaError_t symm_colmajor(bool right, bool lower, size_t M, size_t N, T alpha, const T* A, size_t lda, const T* B, size_t ldb,
+                          T beta, T* C, size_t ldc, cudaStream_t s);
+
 // Stream-ordered workspace from the library's own per-device pool (workspace.cu).
 cudaError_t ws_alloc(void** ptr, size_t bytes, cudaStream_t s);
 cudaError_t ws_free(void* ptr, cudaStream_t s);

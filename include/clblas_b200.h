@@ -183,6 +183,59 @@ clblasStatus clblasDsyrk(
     unsigned numCommandQueues, clblasQueue* commandQueues,
     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
 
+/* ---- SYR2K: replaces clblasSsyr2k (src/clBLAS.h:8568-8589) and clblasDsyr2k (:8648-8669), implemented by
+ *      src/library/blas/xsyr2k.c in the reference.  C <- alpha*op(A)*op(B)^T + alpha*op(B)*op(A)^T + beta*C on the
+ *      `uplo` triangle of the N x N matrix C; op(A), op(B) are N x K.  Checks in the reference's order
+ *      (xsyr2k.c:52-78): NotInitialized, queues (InvalidValue), NULL A/B/C, A sizes, B sizes, C sizes. */
+clblasStatus clblasSsyr2k(
+    clblasOrder order, clblasUplo uplo, clblasTranspose transAB,
+    size_t N, size_t K,
+    float alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    float beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasDsyr2k(
+    clblasOrder order, clblasUplo uplo, clblasTranspose transAB,
+    size_t N, size_t K,
+    double alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    double beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+/* ---- SYMM: replaces clblasSsymm (src/clBLAS.h:8898-8919) and clblasDsymm (:8979-9000), implemented by
+ *      src/library/blas/xsymm.c in the reference.  C <- alpha*A*B + beta*C (Left, A M x M) or alpha*B*A + beta*C
+ *      (Right, A N x N); A is symmetric and only its `uplo` triangle is read.  Checks in the reference's order
+ *      (xsymm.c doSymm): NotInitialized, NULL A/B/C, A sizes, B sizes, C sizes, queues (InvalidValue), wait list.
+ *      Takes an n x n workspace (n the order of A) from the library's stream-ordered pool. */
+clblasStatus clblasSsymm(
+    clblasOrder order, clblasSide side, clblasUplo uplo,
+    size_t M, size_t N,
+    float alpha,
+    const clblasMem A, size_t offa, size_t lda,
+    const clblasMem B, size_t offb, size_t ldb,
+    float beta,
+    clblasMem C, size_t offc, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasDsymm(
+    clblasOrder order, clblasSide side, clblasUplo uplo,
+    size_t M, size_t N,
+    double alpha,
+    const clblasMem A, size_t offa, size_t lda,
+    const clblasMem B, size_t offb, size_t ldb,
+    double beta,
+    clblasMem C, size_t offc, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- DTRSM that allocates nothing (no counterpart in the reference, whose DTRSM creates and
  *      releases two OpenCL buffers inside every call, src/library/blas/xtrsm.cc:1183-1207).
  *      Same arguments, checks and result as clblasDtrsm, but the blocked solve's workspace is a

@@ -80,6 +80,11 @@ def _lib(impl: str) -> ctypes.CDLL:
         getattr(lib, f"{prefix}{p}trmm").restype = None
         getattr(lib, f"{prefix}{p}syrk").argtypes = [i, i, i, sz, sz, ct, ptr, sz, ct, ptr, sz]
         getattr(lib, f"{prefix}{p}syrk").restype = None
+        getattr(lib, f"{prefix}{p}syr2k").argtypes = [i, i, i, sz, sz, ct, ptr, sz, ptr, sz, ct, ptr, sz]
+        getattr(lib, f"{prefix}{p}syr2k").restype = None
+        if prefix == "oracle_":      # the reference's naive BLAS has no symm
+            getattr(lib, f"{prefix}{p}symm").argtypes = [i, i, i, sz, sz, ct, ptr, sz, ptr, sz, ct, ptr, sz]
+            getattr(lib, f"{prefix}{p}symm").restype = None
     lib._prefix = prefix
     _libs[impl] = lib
     return lib
@@ -127,6 +132,23 @@ def syrk(order, uplo, trans, N, K, alpha, A, offA, lda, beta, C, offC, ldc, impl
     p = "s" if C.dtype == np.float32 else "d"
     fn = getattr(lib, f"{lib._prefix}{p}syrk")
     fn(order, uplo, trans, N, K, alpha, _p(A, offA), lda, beta, _p(C, offC), ldc)
+
+
+def syr2k(order, uplo, trans, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, impl: str = "port") -> None:
+    """C <- alpha (op(A) op(B)^T + op(B) op(A)^T) + beta C on the uplo triangle, in place on the flat buffer C."""
+    lib = _lib(impl)
+    p = "s" if C.dtype == np.float32 else "d"
+    fn = getattr(lib, f"{lib._prefix}{p}syr2k")
+    fn(order, uplo, trans, N, K, alpha, _p(A, offA), lda, _p(B, offB), ldb, beta, _p(C, offC), ldc)
+
+
+def symm(order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc) -> None:
+    """C <- alpha A B + beta C (Left) or alpha B A + beta C (Right), A symmetric with the uplo triangle stored.
+    Port only: the reference's naive BLAS has no symm (its tests call an external Fortran BLAS)."""
+    lib = _lib("port")
+    p = "s" if C.dtype == np.float32 else "d"
+    fn = getattr(lib, f"oracle_{p}symm")
+    fn(order, side, uplo, M, N, alpha, _p(A, offA), lda, _p(B, offB), ldb, beta, _p(C, offC), ldc)
 
 
 # --------------------------------------------------------------------------------------------

@@ -181,3 +181,69 @@ void NAME(int order, int uplo, int trans, size_t N, size_t K, T alpha, const T* 
 
 DEFINE_SYRK(oracle_ssyrk, float)
 DEFINE_SYRK(oracle_dsyrk, double)
+
+/* NaiveBlas::syr2k (naive_blas.cpp:728-766): C <- alpha*(op(A)*op(B)^T + op(B)*op(A)^T) + beta*C on the uplo
+ * triangle; one running sum takes both products of each k. */
+#define DEFINE_SYR2K(NAME, T)                                                                  \
+void NAME(int order, int uplo, int trans, size_t N, size_t K, T alpha, const T* A, size_t lda, \
+          const T* B, size_t ldb, T beta, T* C, size_t ldc)                                    \
+{                                                                                              \
+    int tr = trans == ONoTrans ? ONoTrans : OTrans;                                            \
+    acc_t ma = make_acc(order, tr, lda);                                                       \
+    acc_t mb = make_acc(order, tr, ldb);                                                       \
+    acc_t mc = make_acc(order, ONoTrans, ldc);                                                 \
+    long long i;                                                                               \
+    _Pragma("omp parallel for schedule(dynamic, 8)")                                           \
+    for (i = 0; i < (long long)N; i++) {                                                       \
+        size_t j, k;                                                                           \
+        for (j = 0; j < N; j++) {                                                              \
+            T tmp = (T)0.0;                                                                    \
+            if ((uplo == OLower && j > (size_t)i) || (uplo == OUpper && (size_t)i > j)) continue; \
+            for (k = 0; k < K; k++) {                                                          \
+                tmp = tmp + A[at(ma, (size_t)i, k)] * B[at(mb, j, k)] + A[at(ma, j, k)] * B[at(mb, (size_t)i, k)]; \
+            }                                                                                  \
+            C[at(mc, (size_t)i, j)] = C[at(mc, (size_t)i, j)] * beta + tmp * alpha;            \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_SYR2K(oracle_ssyr2k, float)
+DEFINE_SYR2K(oracle_dsyr2k, double)
+
+/* SYMM.  The reference's naive BLAS has no symm; its correctness tests call the external Fortran BLAS
+ * (src/tests/correctness/corr-symm.cpp -> src/tests/blas.c -> ssymm_/dsymm_, blas-lapack.h).  This is the
+ * Netlib definition written in the style of NaiveBlas::gemm: C <- alpha*A*B + beta*C (Left) or
+ * alpha*B*A + beta*C (Right) with A(i,j) taken from the stored uplo triangle. */
+#define DEFINE_SYMM(NAME, T)                                                                   \
+void NAME(int order, int side, int uplo, size_t M, size_t N, T alpha, const T* A, size_t lda,  \
+          const T* B, size_t ldb, T beta, T* C, size_t ldc)                                    \
+{                                                                                              \
+    acc_t ma = make_acc(order, ONoTrans, lda);                                                 \
+    acc_t mb = make_acc(order, ONoTrans, ldb);                                                 \
+    acc_t mc = make_acc(order, ONoTrans, ldc);                                                 \
+    long long i;                                                                               \
+    _Pragma("omp parallel for schedule(dynamic, 8)")                                           \
+    for (i = 0; i < (long long)M; i++) {                                                       \
+        size_t j, k;                                                                           \
+        for (j = 0; j < N; j++) {                                                              \
+            T tmp = (T)0.0;                                                                    \
+            if (side == OLeft) {                                                               \
+                for (k = 0; k < M; k++) {                                                      \
+                    int st = (uplo == OLower) ? ((size_t)i >= k) : ((size_t)i <= k);           \
+                    T a = st ? A[at(ma, (size_t)i, k)] : A[at(ma, k, (size_t)i)];              \
+                    tmp = tmp + a * B[at(mb, k, j)];                                           \
+                }                                                                              \
+            } else {                                                                           \
+                for (k = 0; k < N; k++) {                                                      \
+                    int st = (uplo == OLower) ? (k >= j) : (k <= j);                           \
+                    T a = st ? A[at(ma, k, j)] : A[at(ma, j, k)];                              \
+                    tmp = tmp + B[at(mb, (size_t)i, k)] * a;                                   \
+                }                                                                              \
+            }                                                                                  \
+            C[at(mc, (size_t)i, j)] = C[at(mc, (size_t)i, j)] * beta + tmp * alpha;            \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_SYMM(oracle_ssymm, float)
+DEFINE_SYMM(oracle_dsymm, double)

@@ -85,4 +85,18 @@ void ref_dsyrk(int order, int uplo, int trans, size_t N, size_t K, double alpha,
                             N, K, alpha, A, lda, beta, C, ldc);
 }
 
+void ref_ssyr2k(int order, int uplo, int trans, size_t N, size_t K, float alpha, const float* A, size_t lda,
+                const float* B, size_t ldb, float beta, float* C, size_t ldc)
+{
+    NaiveBlas::syr2k<float>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)trans,
+                            N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+void ref_dsyr2k(int order, int uplo, int trans, size_t N, size_t K, double alpha, const double* A, size_t lda,
+                const double* B, size_t ldb, double beta, double* C, size_t ldc)
+{
+    NaiveBlas::syr2k<double>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)trans,
+                             N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
 }  // extern "C"

@@ -17,7 +17,20 @@ import numpy as np
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "..", ".."))
 import oracle  # noqa: E402
-from tests import cases, cases_syrk, cases_trmm  # noqa: E402
+from tests import cases, cases_sym, cases_syrk, cases_trmm  # noqa: E402
+
+
+def symm_by_external_blas(c):
+    """C buffer after ?symm of the Netlib interface (scipy.linalg.blas); B and C go in as column-major views."""
+    from scipy.linalg import blas
+    from oracle import Left, Lower, NoTrans
+    logical = cases_sym.symm_logical(c)
+    A, full, B, C = logical
+    fn = blas.ssymm if c["prec"] == "s" else blas.dsymm
+    stored = np.where(np.isnan(A), 0, A)      # Fortran symm reads only the uplo triangle
+    R = fn(c["alpha"], np.asfortranarray(stored), np.asfortranarray(B), beta=c["beta"], c=np.asfortranarray(C),
+           side=0 if c["side"] == Left else 1, lower=1 if c["uplo"] == Lower else 0)
+    return oracle.pack(np.ascontiguousarray(R), c["order"], NoTrans, c["ldc"], c["offC"], tail=3)
 
 
 def main():
@@ -44,6 +57,15 @@ def main():
         oracle.syrk(c["order"], c["uplo"], c["trans"], c["N"], c["K"], c["alpha"], A, c["offA"], c["lda"], c["beta"], C,
                     c["offC"], c["ldc"], impl="ref")
         out[name] = C
+    for name, c in cases_sym.golden_syr2k_cases().items():
+        A, B, C = cases_sym.syr2k_buffers(c)
+        oracle.syr2k(c["order"], c["uplo"], c["trans"], c["N"], c["K"], c["alpha"], A, c["offA"], c["lda"], B, c["offB"],
+                     c["ldb"], c["beta"], C, c["offC"], c["ldc"], impl="ref")
+        out[name] = C
+    # SYMM: the reference's naive BLAS has none and its tests call an external Fortran BLAS, so these
+    # vectors come from that interface here (OpenBLAS through scipy), on the dense symmetric matrix
+    for name, c in cases_sym.golden_symm_cases().items():
+        out[name] = symm_by_external_blas(c)
     path = os.path.join(os.path.dirname(__file__), "level3_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} cases, {os.path.getsize(path)} bytes")
