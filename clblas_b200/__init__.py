@@ -55,6 +55,15 @@ def check(status: int, what: str = "clblas call") -> None:
         raise ClblasError(status, what)
 
 
+class FloatComplex(ctypes.Structure):
+    """(re, im) pair passed by value, layout of the reference's FloatComplex (cl_float2)."""
+    _fields_ = [("re", ctypes.c_float), ("im", ctypes.c_float)]
+
+
+class DoubleComplex(ctypes.Structure):
+    _fields_ = [("re", ctypes.c_double), ("im", ctypes.c_double)]
+
+
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -85,6 +94,10 @@ def _load() -> ctypes.CDLL:
         f = getattr(lib, name)
         f.argtypes = [i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
+    for name, ct in (("clblasCgemm", FloatComplex), ("clblasZgemm", DoubleComplex)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, sz, sz, sz, ct, vp, sz, sz, vp, sz, sz, ct, vp, sz, sz, u, pvp, u, pvp, pvp]
+        f.restype = i
     lib.clblasSetup.argtypes = []
     lib.clblasSetup.restype = i
     lib.clblasTeardown.argtypes = []
@@ -112,7 +125,7 @@ EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
            "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
-           "clblasSsymm", "clblasDsymm"]
+           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -262,6 +275,26 @@ def clblasDsymm(order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta
                 queues=None, wait=None, events=None) -> int:
     return _abc(lib.clblasDsymm, order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
                 queues, wait, events)
+
+
+def _cplx(ct, v):
+    v = complex(v)
+    return ct(v.real, v.imag)
+
+
+def clblasCgemm(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues=None, wait=None, events=None) -> int:
+    """complex64 GEMM; alpha and beta are Python complex numbers (src/clBLAS.h:7538-7560)."""
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return lib.clblasCgemm(order, transA, transB, M, N, K, _cplx(FloatComplex, alpha), _ptr(A), offA, lda, _ptr(B), offB, ldb,
+                           _cplx(FloatComplex, beta), _ptr(C), offC, ldc, nq, q, nw, w, e)
+
+
+def clblasZgemm(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                queues=None, wait=None, events=None) -> int:
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return lib.clblasZgemm(order, transA, transB, M, N, K, _cplx(DoubleComplex, alpha), _ptr(A), offA, lda, _ptr(B), offB, ldb,
+                           _cplx(DoubleComplex, beta), _ptr(C), offC, ldc, nq, q, nw, w, e)
 
 
 NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = 4096, 8192

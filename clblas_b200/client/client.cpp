@@ -43,7 +43,7 @@ static void usage()
     std::puts("clblas_b200_client options (same meaning as the clBLAS client):\n"
               "  -m/--sizem -n/--sizen -k/--sizek  --lda --ldb --ldc  --offA --offBX --offCY\n"
               "  --alpha --beta  -o/--order (0 row, 1 column)  --transposeA --transposeB (0/1/2)\n"
-              "  -f/--function gemm|trsm|trmm|syrk|syr2k|symm  -r/--precision s|d  --side --uplo --diag\n"
+              "  -f/--function gemm|trsm|trmm|syrk|syr2k|symm  -r/--precision s|d|c|z  --side --uplo --diag\n"
               "  -p/--profile samples (20)  --apiCallCount calls per sample (10)  -v/--validate 0|1");
 }
 
@@ -270,6 +270,70 @@ static int run(const Options& o)
     return 0;
 }
 
+// Complex GEMM (-r c | z): interleaved (re, im) matrices, flops = 8*M*N*K as the reference client counts
+// them (src/client/clfunc_xgemm.hpp:97 with the complex factor 4).
+template <typename R>
+static int run_complex(const Options& o)
+{
+    size_t ai, ao, bi, bo, ci, co;
+    stored(o.order, o.transA, o.M, o.K, ai, ao);
+    stored(o.order, o.transB, o.K, o.N, bi, bo);
+    stored(o.order, 0, o.M, o.N, ci, co);
+    const size_t lda = o.lda ? o.lda : ai, ldb = o.ldb ? o.ldb : bi, ldc = o.ldc ? o.ldc : ci;
+    const size_t na = o.offA + (ao - 1) * lda + ai, nb = o.offB + (bo - 1) * ldb + bi, nc = o.offC + (co - 1) * ldc + ci;
+    std::vector<R> hA(2 * na), hB(2 * nb), hC(2 * nc);
+    std::srand(10);
+    auto rnd = [] { return (R)((std::rand() % 20) - 10) / (R)10; };
+    for (auto& v : hA) v = rnd();
+    for (auto& v : hB) v = rnd();
+    for (auto& v : hC) v = rnd();
+    R *dA, *dB, *dC;
+    CUDA_OK(cudaMalloc(&dA, hA.size() * sizeof(R)));
+    CUDA_OK(cudaMalloc(&dB, hB.size() * sizeof(R)));
+    CUDA_OK(cudaMalloc(&dC, hC.size() * sizeof(R)));
+    CUDA_OK(cudaMemcpy(dA, hA.data(), hA.size() * sizeof(R), cudaMemcpyHostToDevice));
+    CUDA_OK(cudaMemcpy(dB, hB.data(), hB.size() * sizeof(R), cudaMemcpyHostToDevice));
+    CUDA_OK(cudaMemcpy(dC, hC.data(), hC.size() * sizeof(R), cudaMemcpyHostToDevice));
+    cudaStream_t stream;
+    CUDA_OK(cudaStreamCreate(&stream));
+    clblasQueue q = reinterpret_cast<clblasQueue>(stream);
+    if (clblasSetup() != clblasSuccess) { std::fprintf(stderr, "clblasSetup failed\n"); return 2; }
+    clblasB200SetGemmPath(o.path);
+    auto call = [&]() -> clblasStatus {
+        if (sizeof(R) == 4)
+            return clblasCgemm((clblasOrder)o.order, (clblasTranspose)o.transA, (clblasTranspose)o.transB, o.M, o.N, o.K,
+                               floatComplex((float)o.alpha, 0.f), dA, o.offA, lda, dB, o.offB, ldb, floatComplex((float)o.beta, 0.f),
+                               dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+        return clblasZgemm((clblasOrder)o.order, (clblasTranspose)o.transA, (clblasTranspose)o.transB, o.M, o.N, o.K,
+                           doubleComplex(o.alpha, 0.0), dA, o.offA, lda, dB, o.offB, ldb, doubleComplex(o.beta, 0.0),
+                           dC, o.offC, ldc, 1, &q, 0, nullptr, nullptr);
+    };
+    clblasStatus st = call();
+    if (st != clblasSuccess) { std::fprintf(stderr, "call failed with status %d\n", (int)st); return 3; }
+    CUDA_OK(cudaStreamSynchronize(stream));
+    cudaEvent_t e0, e1;
+    CUDA_OK(cudaEventCreate(&e0));
+    CUDA_OK(cudaEventCreate(&e1));
+    double total_ms = 0;
+    for (unsigned s = 0; s < o.profile; s++) {
+        CUDA_OK(cudaEventRecord(e0, stream));
+        for (unsigned c = 0; c < o.apiCallCount; c++) st = call();
+        CUDA_OK(cudaEventRecord(e1, stream));
+        CUDA_OK(cudaEventSynchronize(e1));
+        float ms = 0;
+        CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+        total_ms += ms;
+    }
+    if (st != clblasSuccess) { std::fprintf(stderr, "call failed with status %d\n", (int)st); return 3; }
+    const double per_call_ns = total_ms * 1e6 / ((double)o.profile * o.apiCallCount);
+    std::printf("BLAS kernel execution time < ns >: %.0f\n", per_call_ns);
+    std::printf("BLAS kernel execution Gflops < 8.0*M*N*K/time >: %.2f\n", 8.0 * o.M * o.N * o.K / per_call_ns);
+    cudaFree(dA); cudaFree(dB); cudaFree(dC);
+    cudaStreamDestroy(stream);
+    clblasTeardown();
+    return 0;
+}
+
 int main(int argc, char** argv)
 {
     Options o;
@@ -278,8 +342,14 @@ int main(int argc, char** argv)
         std::fprintf(stderr, "function must be gemm, trsm, trmm, syrk, syr2k or symm\n");
         return 1;
     }
+    if ((o.precision == "c" || o.precision == "z") && o.function != "gemm") {
+        std::fprintf(stderr, "complex precisions are available for gemm only\n");
+        return 1;
+    }
+    if (o.precision == "c") return run_complex<float>(o);
+    if (o.precision == "z") return run_complex<double>(o);
     if (o.precision == "s") return run<float>(o);
     if (o.precision == "d") return run<double>(o);
-    std::fprintf(stderr, "precision must be s or d\n");
+    std::fprintf(stderr, "precision must be s, d, c or z\n");
     return 1;
 }

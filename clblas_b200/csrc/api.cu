@@ -172,6 +172,44 @@ clblasStatus gemm_entry(clblasOrder order, clblasTranspose transA, clblasTranspo
     return record_out(s, events);
 }
 
+// Complex GEMM front end: the checks of gemm_entry on complex elements (2 * sizeof(R) bytes each).
+template <typename R>
+clblasStatus cgemm_entry(clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+                         size_t M, size_t N, size_t K, R ar, R ai,
+                         const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb,
+                         R br, R bi, void* C, size_t offC, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)transA > 2u || (unsigned)transB > 2u) return clblasInvalidValue;
+    clblasStatus st;
+    const size_t tsize = 2 * sizeof(R);
+    if (K != 0) {
+        if ((st = check_matrix_sizes(tsize, order, transA, M, K, A, offA, lda, SET_A)) != clblasSuccess) return st;
+        if ((st = check_matrix_sizes(tsize, order, transB, K, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    }
+    if ((st = check_matrix_sizes(tsize, order, clblasNoTrans, M, N, C, offC, ldc, SET_C)) != clblasSuccess) return st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+
+    const R* a = static_cast<const R*>(A) + 2 * offA;
+    const R* b = static_cast<const R*>(B) + 2 * offB;
+    R* c = static_cast<R*>(C) + 2 * offC;
+    cudaError_t e;
+    if (order == clblasColumnMajor)
+        e = cgemm_colmajor<R>((int)transA, (int)transB, M, N, K, ar, ai, a, lda, b, ldb, br, bi, c, ldc, s);
+    else    // row-major C is column-major C^T = op(B)^T * op(A)^T; a conjugation stays with its operand
+        e = cgemm_colmajor<R>((int)transB, (int)transA, N, M, K, ar, ai, b, ldb, a, lda, br, bi, c, ldc, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 template <typename T>
 clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
                         size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda,
@@ -508,6 +546,24 @@ clblasStatus clblasDsymm(clblasOrder order, clblasSide side, clblasUplo uplo, si
                          unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
 {
     return symm_entry<double>(order, side, uplo, M, N, alpha, A, offa, lda, B, offb, ldb, beta, C, offc, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasCgemm(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                         FloatComplex alpha, const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb,
+                         FloatComplex beta, clblasMem C, size_t offC, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return cgemm_entry<float>(order, transA, transB, M, N, K, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb,
+                              beta.s[0], beta.s[1], C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZgemm(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                         DoubleComplex alpha, const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb,
+                         DoubleComplex beta, clblasMem C, size_t offC, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return cgemm_entry<double>(order, transA, transB, M, N, K, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb,
+                               beta.s[0], beta.s[1], C, offC, ldc, nq, queues, nev, wait, events);
 }
 
 clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,

@@ -84,6 +84,12 @@ struct ScopedNoAlloc {
 template <typename T>
 cudaError_t gemm_colmajor(const GemmProblem<T>& p, cudaStream_t s);
 
+// Complex GEMM on the real kernels (cgemm.cu).  ta / tb: 0 NoTrans, 1 Trans, 2 ConjTrans; pointers are to
+// the real part of the first element, leading dimensions count complex elements.
+template <typename R>
+cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R ai, const R* A, size_t lda,
+                           const R* B, size_t ldb, R br, R bi, R* C, size_t ldc, cudaStream_t s);
+
 // Blocked triangular solve on a column-major problem (B overwritten by X).
 template <typename T>
 cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,

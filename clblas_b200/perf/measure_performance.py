@@ -47,7 +47,7 @@ def main() -> int:
     ap.add_argument("-s", "--square", help="sizes used for m, n and k together")
     ap.add_argument("-m", "--sizem"), ap.add_argument("-n", "--sizen"), ap.add_argument("-k", "--sizek")
     ap.add_argument("-f", "--function", default="gemm", choices=["gemm", "trsm", "trmm", "syrk", "syr2k", "symm"])
-    ap.add_argument("-r", "--precision", default="s", choices=["s", "d"])
+    ap.add_argument("-r", "--precision", default="s", choices=["s", "d", "c", "z"])
     ap.add_argument("--order", default="column", choices=["row", "column"])
     ap.add_argument("--transa", default="none", choices=list(TRANS)), ap.add_argument("--transb", default="none", choices=list(TRANS))
     ap.add_argument("--side", default="left", choices=["left", "right"])

@@ -28,6 +28,20 @@ typedef struct CUstream_st* clblasQueue;
 typedef struct CUevent_st*  clblasEvent;
 
 /* Enumerations: same names and the same numeric values as src/clBLAS.h:78-113. */
+/* Complex scalars and matrix elements: (re, im) pairs with the layout, size and alignment of the reference's
+ * FloatComplex / DoubleComplex (cl_float2 / cl_double2, src/clBLAS-complex.h:27-58), passed by value. */
+#if defined(__GNUC__) || defined(__clang__) || defined(__CUDACC__)
+#define CLBLAS_B200_ALIGNED(n) __attribute__((aligned(n)))
+#else
+#define CLBLAS_B200_ALIGNED(n)
+#endif
+typedef struct CLBLAS_B200_ALIGNED(8)  { float s[2]; }  FloatComplex;
+typedef struct CLBLAS_B200_ALIGNED(16) { double s[2]; } DoubleComplex;
+static inline FloatComplex floatComplex(float real, float imag) { FloatComplex z; z.s[0] = real; z.s[1] = imag; return z; }
+static inline DoubleComplex doubleComplex(double real, double imag) { DoubleComplex z; z.s[0] = real; z.s[1] = imag; return z; }
+#define CREAL(v) ((v).s[0])
+#define CIMAG(v) ((v).s[1])
+
 typedef enum clblasOrder_     { clblasRowMajor = 0, clblasColumnMajor = 1 } clblasOrder;
 typedef enum clblasTranspose_ { clblasNoTrans = 0, clblasTrans = 1, clblasConjTrans = 2 } clblasTranspose;
 typedef enum clblasUplo_      { clblasUpper = 0, clblasLower = 1 } clblasUplo;
@@ -107,6 +121,33 @@ clblasStatus clblasDgemm(
     const clblasMem A, size_t offA, size_t lda,
     const clblasMem B, size_t offB, size_t ldb,
     double beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+/* ---- complex GEMM: replaces clblasCgemm (src/clBLAS.h:7538-7560) and clblasZgemm (:7614-7636), which the
+ *      reference serves through the same clblasGemm<T> front end (src/library/blas/xgemm.cc:788-905): same
+ *      checks in the same order as the real routines.  Matrices hold interleaved (re, im) pairs; offsets and
+ *      leading dimensions count complex elements; clblasConjTrans conjugates.  Takes a workspace of about
+ *      twice the size of A (plus the size of B when B is transposed) from the library's pool. */
+clblasStatus clblasCgemm(
+    clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+    size_t M, size_t N, size_t K,
+    FloatComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    FloatComplex beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZgemm(
+    clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+    size_t M, size_t N, size_t K,
+    DoubleComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    DoubleComplex beta,
     clblasMem C, size_t offC, size_t ldc,
     unsigned numCommandQueues, clblasQueue* commandQueues,
     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);

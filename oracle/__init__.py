@@ -85,6 +85,10 @@ def _lib(impl: str) -> ctypes.CDLL:
         if prefix == "oracle_":      # the reference's naive BLAS has no symm
             getattr(lib, f"{prefix}{p}symm").argtypes = [i, i, i, sz, sz, ct, ptr, sz, ptr, sz, ct, ptr, sz]
             getattr(lib, f"{prefix}{p}symm").restype = None
+    for p, ct in (("c", ctypes.c_float), ("z", ctypes.c_double)):
+        ptr = ctypes.c_void_p
+        getattr(lib, f"{prefix}{p}gemm").argtypes = [i, i, i, sz, sz, sz, ct, ct, ptr, sz, ptr, sz, ct, ct, ptr, sz]
+        getattr(lib, f"{prefix}{p}gemm").restype = None
     lib._prefix = prefix
     _libs[impl] = lib
     return lib
@@ -124,6 +128,16 @@ def trmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ld
     p = "s" if B.dtype == np.float32 else "d"
     fn = getattr(lib, f"{lib._prefix}{p}trmm")
     fn(order, side, uplo, transA, diag, M, N, alpha, _p(A, offA), lda, _p(B, offB), ldb)
+
+
+def cgemm(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, impl: str = "port") -> None:
+    """Complex GEMM in place on the flat complex64 / complex128 buffer C; alpha, beta Python complex numbers."""
+    lib = _lib(impl)
+    p = "c" if C.dtype == np.complex64 else "z"
+    alpha, beta = complex(alpha), complex(beta)
+    fn = getattr(lib, f"{lib._prefix}{p}gemm")
+    fn(order, transA, transB, M, N, K, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb, beta.real, beta.imag,
+       _p(C, offC), ldc)
 
 
 def syrk(order, uplo, trans, N, K, alpha, A, offA, lda, beta, C, offC, ldc, impl: str = "port") -> None:

@@ -247,3 +247,45 @@ void NAME(int order, int side, int uplo, size_t M, size_t N, T alpha, const T* A
 
 DEFINE_SYMM(oracle_ssymm, float)
 DEFINE_SYMM(oracle_dsymm, double)
+
+/* Complex GEMM: NaiveBlas::gemm<FloatComplex / DoubleComplex> (naive_blas.cpp:546-578) with the complex
+ * operators of naive_blas.cpp:297-372 written out: (a*b) = (ar*br - ai*bi, ar*bi + br*ai); an element read
+ * through a ConjTrans accessor is conjugated (VectorAccessor, naive_blas.cpp:430-485).  Matrices are
+ * interleaved (re, im); alpha and beta arrive as two scalars each. */
+#define DEFINE_CGEMM(NAME, T)                                                                  \
+void NAME(int order, int transA, int transB, size_t M, size_t N, size_t K, T alr, T ali,       \
+          const T* A, size_t lda, const T* B, size_t ldb, T ber, T bei, T* C, size_t ldc)      \
+{                                                                                              \
+    acc_t ma = make_acc(order, transA, lda);                                                   \
+    acc_t mb = make_acc(order, transB, ldb);                                                   \
+    acc_t mc = make_acc(order, ONoTrans, ldc);                                                 \
+    const int ca = (transA == OConjTrans), cb = (transB == OConjTrans);                        \
+    long long i;                                                                               \
+    _Pragma("omp parallel for schedule(static)")                                               \
+    for (i = 0; i < (long long)M; i++) {                                                       \
+        size_t j, k;                                                                           \
+        for (j = 0; j < N; j++) {                                                              \
+            T tr = (T)0.0, ti = (T)0.0;                                                        \
+            for (k = 0; k < K; k++) {                                                          \
+                const T* a = A + 2 * at(ma, (size_t)i, k);                                     \
+                const T* b = B + 2 * at(mb, k, j);                                             \
+                const T ar = a[0], ai = ca ? -a[1] : a[1];                                     \
+                const T br = b[0], bi = cb ? -b[1] : b[1];                                     \
+                const T pr = ar * br - ai * bi, pi = ar * bi + br * ai;                        \
+                tr = tr + pr;                                                                  \
+                ti = ti + pi;                                                                  \
+            }                                                                                  \
+            {                                                                                  \
+                T* c = C + 2 * at(mc, (size_t)i, j);                                           \
+                const T cr = c[0], ci = c[1];                                                  \
+                const T xr = cr * ber - ci * bei, xi = cr * bei + ber * ci;                    \
+                const T yr = tr * alr - ti * ali, yi = tr * ali + alr * ti;                    \
+                c[0] = xr + yr;                                                                \
+                c[1] = xi + yi;                                                                \
+            }                                                                                  \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_CGEMM(oracle_cgemm, float)
+DEFINE_CGEMM(oracle_zgemm, double)

@@ -99,4 +99,22 @@ void ref_dsyr2k(int order, int uplo, int trans, size_t N, size_t K, double alpha
                              N, K, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
+void ref_cgemm(int order, int transA, int transB, size_t M, size_t N, size_t K, float alr, float ali,
+               const float* A, size_t lda, const float* B, size_t ldb, float ber, float bei, float* C, size_t ldc)
+{
+    NaiveBlas::gemm<NaiveBlas::FloatComplex>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasTranspose)transA,
+                                  (NaiveBlas::clblasTranspose)transB, M, N, K, NaiveBlas::floatComplex(alr, ali),
+                                  reinterpret_cast<const NaiveBlas::FloatComplex*>(A), lda, reinterpret_cast<const NaiveBlas::FloatComplex*>(B), ldb,
+                                  NaiveBlas::floatComplex(ber, bei), reinterpret_cast<NaiveBlas::FloatComplex*>(C), ldc);
+}
+
+void ref_zgemm(int order, int transA, int transB, size_t M, size_t N, size_t K, double alr, double ali,
+               const double* A, size_t lda, const double* B, size_t ldb, double ber, double bei, double* C, size_t ldc)
+{
+    NaiveBlas::gemm<NaiveBlas::DoubleComplex>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasTranspose)transA,
+                                   (NaiveBlas::clblasTranspose)transB, M, N, K, NaiveBlas::doubleComplex(alr, ali),
+                                   reinterpret_cast<const NaiveBlas::DoubleComplex*>(A), lda, reinterpret_cast<const NaiveBlas::DoubleComplex*>(B), ldb,
+                                   NaiveBlas::doubleComplex(ber, bei), reinterpret_cast<NaiveBlas::DoubleComplex*>(C), ldc);
+}
+
 }  // extern "C"

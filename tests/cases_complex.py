@@ -1,0 +1,82 @@
+"""Seeded complex GEMM cases (clblasCgemm / clblasZgemm) shared by the oracle tests, the golden-vector
+generator and the GPU parity tests; same conventions as tests/cases.py.  A logical op(X) that was
+produced by ConjTrans is stored conjugated, so that reading it back through ConjTrans gives op(X)."""
+from __future__ import annotations
+
+import itertools
+
+import numpy as np
+
+import oracle
+from oracle import ConjTrans, NoTrans, Trans
+from tests.cases import ORDERS, _min_ld
+
+CDT = {"c": np.complex64, "z": np.complex128}
+RDT = {"c": np.float32, "z": np.float64}
+CNAN = complex(np.nan, np.nan)
+ALL_TRANS = (NoTrans, Trans, ConjTrans)
+
+
+def cgemm_case(prec, order, transA, transB, M, N, K, alpha=1.5 - 0.5j, beta=0.5 + 0.25j, pad=(0, 0, 0), off=(0, 0, 0),
+               mode="uniform", seed=12345):
+    return dict(kind="cgemm", prec=prec, order=order, transA=transA, transB=transB, M=M, N=N, K=K, alpha=alpha, beta=beta,
+                lda=_min_ld(order, transA, M, K) + pad[0], ldb=_min_ld(order, transB, K, N) + pad[1],
+                ldc=_min_ld(order, NoTrans, M, N) + pad[2], offA=off[0], offB=off[1], offC=off[2], mode=mode, seed=seed)
+
+
+def _draw(g, mode, shape, prec):
+    if mode == "int":
+        re, im = g.integers(-6, 7, size=shape), g.integers(-6, 7, size=shape)
+    else:
+        re, im = g.uniform(-1, 1, size=shape), g.uniform(-1, 1, size=shape)
+    return (re + 1j * im).astype(CDT[prec])
+
+
+def cgemm_logical(c):
+    """Logical op(A) (M x K), op(B) (K x N) and C (M x N)."""
+    g = oracle.rng(c["seed"], 37)
+    return (_draw(g, c["mode"], (c["M"], c["K"]), c["prec"]), _draw(g, c["mode"], (c["K"], c["N"]), c["prec"]),
+            _draw(g, c["mode"], (c["M"], c["N"]), c["prec"]))
+
+
+def cgemm_buffers(c, logical=None, tail=3):
+    opA, opB, C = logical if logical is not None else cgemm_logical(c)
+    sA = np.conj(opA) if c["transA"] == ConjTrans else opA
+    sB = np.conj(opB) if c["transB"] == ConjTrans else opB
+    return (oracle.pack(sA, c["order"], c["transA"], c["lda"], c["offA"], pad_value=CNAN, tail=tail),
+            oracle.pack(sB, c["order"], c["transB"], c["ldb"], c["offB"], pad_value=CNAN, tail=tail),
+            oracle.pack(C, c["order"], NoTrans, c["ldc"], c["offC"], pad_value=CNAN, tail=tail))
+
+
+def cgemm_exact(c, logical):
+    """complex128 value of alpha*op(A)*op(B) + beta*C and the magnitude sum that scales the error bound."""
+    opA, opB, C = (x.astype(np.complex128) for x in logical)
+    want = c["alpha"] * (opA @ opB) + c["beta"] * C
+    mag = abs(c["alpha"]) * (np.abs(opA) @ np.abs(opB)) + abs(c["beta"]) * np.abs(C)
+    return want, mag
+
+
+def golden_cgemm_cases():
+    out = {}
+    k = 0
+    for prec in "cz":
+        for order, ta, tb in itertools.product(ORDERS, ALL_TRANS, ALL_TRANS):
+            M, N, K = [(17, 13, 9), (32, 8, 33), (5, 62, 16), (64, 17, 8)][k % 4]
+            out[f"cgemm_{prec}_{order}{ta}{tb}"] = cgemm_case(prec, order, ta, tb, M, N, K, alpha=[2 - 1j, 1.5 + 0.5j][k % 2],
+                                                             beta=[3 + 0j, 0.5 - 2j, 0j][k % 3], pad=(3, 1, 2), off=(5, 2, 7),
+                                                             mode=["int", "uniform"][k % 2], seed=1100 + k)
+            k += 1
+    return out
+
+
+def sweep_cgemm_cases(prec, mode):
+    cases = []
+    seed = 12000
+    for order in ORDERS:
+        for ta, tb in itertools.product(ALL_TRANS, ALL_TRANS):
+            for (M, N, K) in ((8, 8, 8), (17, 17, 17), (64, 62, 144), (128, 144, 17), (129, 257, 65), (300, 200, 130)):
+                seed += 1
+                cases.append(cgemm_case(prec, order, ta, tb, M, N, K, alpha=[1 + 0j, 2 - 1j, -1 + 3j][seed % 3],
+                                        beta=[1 + 0j, 0j, 2 + 1j, -1 + 0j][seed % 4], pad=(seed % 4, seed % 3, seed % 5),
+                                        off=(seed % 3, seed % 4, seed % 6), mode=mode, seed=seed))
+    return cases

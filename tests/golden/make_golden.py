@@ -17,7 +17,7 @@ import numpy as np
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "..", ".."))
 import oracle  # noqa: E402
-from tests import cases, cases_sym, cases_syrk, cases_trmm  # noqa: E402
+from tests import cases, cases_complex, cases_sym, cases_syrk, cases_trmm  # noqa: E402
 
 
 def symm_by_external_blas(c):
@@ -66,6 +66,11 @@ def main():
     # vectors come from that interface here (OpenBLAS through scipy), on the dense symmetric matrix
     for name, c in cases_sym.golden_symm_cases().items():
         out[name] = symm_by_external_blas(c)
+    for name, c in cases_complex.golden_cgemm_cases().items():
+        A, B, C = cases_complex.cgemm_buffers(c)
+        oracle.cgemm(c["order"], c["transA"], c["transB"], c["M"], c["N"], c["K"], c["alpha"], A, c["offA"], c["lda"],
+                     B, c["offB"], c["ldb"], c["beta"], C, c["offC"], c["ldc"], impl="ref")
+        out[name] = C
     path = os.path.join(os.path.dirname(__file__), "level3_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} cases, {os.path.getsize(path)} bytes")

@@ -1,0 +1,49 @@
+"""Pins the complex GEMM part of the CPU oracle to the reference's NaiveBlas::gemm<FloatComplex/DoubleComplex>
+(src/library/tools/ktest/naive/naive_blas.cpp:546-578 with the complex operators at :297-372): committed
+golden outputs made with that code, the code itself where it was compiled, exact integers."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from oracle import NoTrans
+from tests import cases_complex as cc
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "level3_golden.npz")
+
+
+def run(c, impl, logical=None):
+    A, B, C = cc.cgemm_buffers(c, logical)
+    oracle.cgemm(c["order"], c["transA"], c["transB"], c["M"], c["N"], c["K"], c["alpha"], A, c["offA"], c["lda"],
+                 B, c["offB"], c["ldb"], c["beta"], C, c["offC"], c["ldc"], impl=impl)
+    return C
+
+
+def same_bits(a, b):
+    return a.shape == b.shape and np.array_equal(a.view(np.uint8), b.view(np.uint8))
+
+
+def test_port_matches_golden(built_oracle):
+    g = np.load(GOLDEN)
+    items = list(cc.golden_cgemm_cases().items())
+    assert len(items) == 36
+    for name, c in items:
+        assert same_bits(run(c, "port"), g[name]), name
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference's own naive_blas.cpp was not compiled here")
+def test_port_matches_reference_code(built_oracle):
+    for prec in "cz":
+        for c in cc.sweep_cgemm_cases(prec, "uniform")[::4]:
+            if max(c["M"], c["N"], c["K"]) > 150:
+                continue
+            assert same_bits(run(c, "port"), run(c, "ref")), c
+
+
+def test_integer_inputs_are_exact(built_oracle):
+    for c in cc.sweep_cgemm_cases("z", "int")[::3]:
+        logical = cc.cgemm_logical(c)
+        got = oracle.view(run(c, "port", logical), c["order"], NoTrans, c["M"], c["N"], c["ldc"], c["offC"])
+        want, _ = cc.cgemm_exact(c, logical)
+        assert np.array_equal(got, want), c
