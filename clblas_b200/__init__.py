@@ -98,6 +98,10 @@ def _load() -> ctypes.CDLL:
         f = getattr(lib, name)
         f.argtypes = [i, i, i, sz, sz, sz, ct, vp, sz, sz, vp, sz, sz, ct, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
+    for name, ct in (("clblasCtrsm", FloatComplex), ("clblasZtrsm", DoubleComplex)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, i, i, sz, sz, ct, vp, sz, sz, vp, sz, sz, u, pvp, u, pvp, pvp]
+        f.restype = i
     lib.clblasSetup.argtypes = []
     lib.clblasSetup.restype = i
     lib.clblasTeardown.argtypes = []
@@ -125,7 +129,7 @@ EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
            "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
-           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm"]
+           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -295,6 +299,21 @@ def clblasZgemm(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ld
     nq, q, nw, w, e = _queues_events(queues, wait, events)
     return lib.clblasZgemm(order, transA, transB, M, N, K, _cplx(DoubleComplex, alpha), _ptr(A), offA, lda, _ptr(B), offB, ldb,
                            _cplx(DoubleComplex, beta), _ptr(C), offC, ldc, nq, q, nw, w, e)
+
+
+def clblasCtrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                queues=None, wait=None, events=None) -> int:
+    """complex64 triangular solve, B overwritten by X; alpha is a Python complex number (src/clBLAS.h:8132-8151)."""
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return lib.clblasCtrsm(order, side, uplo, transA, diag, M, N, _cplx(FloatComplex, alpha), _ptr(A), offA, lda,
+                           _ptr(B), offB, ldb, nq, q, nw, w, e)
+
+
+def clblasZtrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                queues=None, wait=None, events=None) -> int:
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return lib.clblasZtrsm(order, side, uplo, transA, diag, M, N, _cplx(DoubleComplex, alpha), _ptr(A), offA, lda,
+                           _ptr(B), offB, ldb, nq, q, nw, w, e)
 
 
 NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = 4096, 8192

@@ -275,9 +275,16 @@ static int run(const Options& o)
 template <typename R>
 static int run_complex(const Options& o)
 {
+    const bool trsm = o.function == "trsm";
+    const size_t tri = o.side == 0 ? o.M : o.N;
     size_t ai, ao, bi, bo, ci, co;
-    stored(o.order, o.transA, o.M, o.K, ai, ao);
-    stored(o.order, o.transB, o.K, o.N, bi, bo);
+    if (trsm) {
+        ai = ao = tri;
+        stored(o.order, 0, o.M, o.N, bi, bo);
+    } else {
+        stored(o.order, o.transA, o.M, o.K, ai, ao);
+        stored(o.order, o.transB, o.K, o.N, bi, bo);
+    }
     stored(o.order, 0, o.M, o.N, ci, co);
     const size_t lda = o.lda ? o.lda : ai, ldb = o.ldb ? o.ldb : bi, ldc = o.ldc ? o.ldc : ci;
     const size_t na = o.offA + (ao - 1) * lda + ai, nb = o.offB + (bo - 1) * ldb + bi, nc = o.offC + (co - 1) * ldc + ci;
@@ -287,6 +294,10 @@ static int run_complex(const Options& o)
     for (auto& v : hA) v = rnd();
     for (auto& v : hB) v = rnd();
     for (auto& v : hC) v = rnd();
+    if (trsm) {     // diagonal A, as the reference client: repeated solves in place stay bounded
+        std::fill(hA.begin(), hA.end(), (R)0);
+        for (size_t i = 0; i < tri; i++) hA[2 * (o.offA + i + i * lda)] = (R)1;
+    }
     R *dA, *dB, *dC;
     CUDA_OK(cudaMalloc(&dA, hA.size() * sizeof(R)));
     CUDA_OK(cudaMalloc(&dB, hB.size() * sizeof(R)));
@@ -300,6 +311,15 @@ static int run_complex(const Options& o)
     if (clblasSetup() != clblasSuccess) { std::fprintf(stderr, "clblasSetup failed\n"); return 2; }
     clblasB200SetGemmPath(o.path);
     auto call = [&]() -> clblasStatus {
+        if (trsm) {
+            if (sizeof(R) == 4)
+                return clblasCtrsm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, (clblasTranspose)o.transA,
+                                   (clblasDiag)o.diag, o.M, o.N, floatComplex((float)o.alpha, 0.f), dA, o.offA, lda, dB, o.offB, ldb,
+                                   1, &q, 0, nullptr, nullptr);
+            return clblasZtrsm((clblasOrder)o.order, (clblasSide)o.side, (clblasUplo)o.uplo, (clblasTranspose)o.transA,
+                               (clblasDiag)o.diag, o.M, o.N, doubleComplex(o.alpha, 0.0), dA, o.offA, lda, dB, o.offB, ldb,
+                               1, &q, 0, nullptr, nullptr);
+        }
         if (sizeof(R) == 4)
             return clblasCgemm((clblasOrder)o.order, (clblasTranspose)o.transA, (clblasTranspose)o.transB, o.M, o.N, o.K,
                                floatComplex((float)o.alpha, 0.f), dA, o.offA, lda, dB, o.offB, ldb, floatComplex((float)o.beta, 0.f),
@@ -327,7 +347,11 @@ static int run_complex(const Options& o)
     if (st != clblasSuccess) { std::fprintf(stderr, "call failed with status %d\n", (int)st); return 3; }
     const double per_call_ns = total_ms * 1e6 / ((double)o.profile * o.apiCallCount);
     std::printf("BLAS kernel execution time < ns >: %.0f\n", per_call_ns);
-    std::printf("BLAS kernel execution Gflops < 8.0*M*N*K/time >: %.2f\n", 8.0 * o.M * o.N * o.K / per_call_ns);
+    if (trsm)
+        std::printf("BLAS kernel execution Gflops < 4*M*(M+1)*N/time >: %.2f\n",
+                    4.0 * (o.side == 0 ? (double)o.M * (o.M + 1) * o.N : (double)o.M * (o.N + 1) * o.N) / per_call_ns);
+    else
+        std::printf("BLAS kernel execution Gflops < 8.0*M*N*K/time >: %.2f\n", 8.0 * o.M * o.N * o.K / per_call_ns);
     cudaFree(dA); cudaFree(dB); cudaFree(dC);
     cudaStreamDestroy(stream);
     clblasTeardown();
@@ -342,8 +366,8 @@ int main(int argc, char** argv)
         std::fprintf(stderr, "function must be gemm, trsm, trmm, syrk, syr2k or symm\n");
         return 1;
     }
-    if ((o.precision == "c" || o.precision == "z") && o.function != "gemm") {
-        std::fprintf(stderr, "complex precisions are available for gemm only\n");
+    if ((o.precision == "c" || o.precision == "z") && o.function != "gemm" && o.function != "trsm") {
+        std::fprintf(stderr, "complex precisions are available for gemm and trsm\n");
         return 1;
     }
     if (o.precision == "c") return run_complex<float>(o);

@@ -248,6 +248,41 @@ clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clb
 
 // clblasStrmm / clblasDtrmm: checks of the reference's doTrmm (src/library/blas/xtrmm.c:52-70):
 // initialised, memory objects, A (order x order), B; then the same row-major flip as TRSM.
+// Complex TRSM front end: the checks of trsm_entry on complex elements.
+template <typename R>
+clblasStatus ctrsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, R ar, R ai, const void* A, size_t offA, size_t lda,
+                         void* B, size_t offB, size_t ldb,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u || (unsigned)transA > 2u || (unsigned)diag > 1u) return clblasInvalidValue;
+    const size_t msize = (side == clblasLeft) ? M : N;
+    const size_t tsize = 2 * sizeof(R);
+    if ((st = check_matrix_sizes(tsize, order, transA, msize, msize, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(tsize, order, clblasNoTrans, M, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        // a row-major matrix is its transpose in column-major: the other side, the other triangle, M and N exchanged
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = ctrsm_colmajor<R>(right, lower, (int)transA, diag == clblasUnit, M, N, ar, ai,
+                                      static_cast<const R*>(A) + 2 * offA, lda, static_cast<R*>(B) + 2 * offB, ldb, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 template <typename T>
 clblasStatus trmm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
                         size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda,
@@ -564,6 +599,24 @@ clblasStatus clblasZgemm(clblasOrder order, clblasTranspose transA, clblasTransp
 {
     return cgemm_entry<double>(order, transA, transB, M, N, K, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb,
                                beta.s[0], beta.s[1], C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasCtrsm(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, FloatComplex alpha, const clblasMem A, size_t offA, size_t lda,
+                         clblasMem B, size_t offB, size_t ldb,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return ctrsm_entry<float>(order, side, uplo, transA, diag, M, N, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb,
+                              nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZtrsm(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, DoubleComplex alpha, const clblasMem A, size_t offA, size_t lda,
+                         clblasMem B, size_t offB, size_t ldb,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return ctrsm_entry<double>(order, side, uplo, transA, diag, M, N, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb,
+                               nq, queues, nev, wait, events);
 }
 
 clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,

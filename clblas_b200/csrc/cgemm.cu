@@ -92,16 +92,48 @@ __global__ void __launch_bounds__(256) cscale_kernel(R* __restrict__ C, size_t l
 
 inline unsigned grid_for(size_t total) { return (unsigned)std::min<size_t>((total + 255) / 256, (size_t)sm_count() * 16); }
 
+// dst (cols x rows complex, column-major) = src^T (src rows x cols complex), through 32 x 32 shared tiles
 template <typename R>
-cudaError_t cscale(R* C, size_t ldc, size_t M, size_t N, R br, R bi, cudaStream_t s)
+__global__ void __launch_bounds__(256) ctranspose_kernel(const R* __restrict__ src, size_t lds, R* __restrict__ dst, size_t ldd,
+                                                         size_t rows, size_t cols)
 {
-    if (br == R(1) && bi == R(0)) return cudaSuccess;
+    using R2 = typename Pair<R>::type;
+    __shared__ R2 tile[32][33];
+    const size_t r0 = (size_t)blockIdx.x * 32, c0 = (size_t)blockIdx.y * 32;
+    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+    for (int c = ty; c < 32; c += 8)
+        if (r0 + tx < rows && c0 + c < cols) tile[c][tx] = *reinterpret_cast<const R2*>(src + 2 * (r0 + tx + (c0 + c) * lds));
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8)
+        if (c0 + tx < cols && r0 + r < rows) *reinterpret_cast<R2*>(dst + 2 * (c0 + tx + (r0 + r) * ldd)) = tile[tx][r];
+}
+
+}  // namespace
+
+template <typename R>
+cudaError_t complex_scale(R* C, size_t ldc, size_t M, size_t N, R br, R bi, cudaStream_t s)
+{
+    if (M == 0 || N == 0 || (br == R(1) && bi == R(0))) return cudaSuccess;
     cscale_kernel<R><<<grid_for(M * N), 256, 0, s>>>(C, ldc, M, N, br, bi);
     count_launch();
     return cudaGetLastError();
 }
 
-}  // namespace
+template <typename R>
+cudaError_t complex_transpose(R* dst, size_t ldd, const R* src, size_t lds, size_t rows, size_t cols, cudaStream_t s)
+{
+    if (rows == 0 || cols == 0) return cudaSuccess;
+    const size_t bx = (rows + 31) / 32, by = (cols + 31) / 32;
+    if (by > 65535) return cudaErrorNotSupported;
+    ctranspose_kernel<R><<<dim3((unsigned)bx, (unsigned)by), 256, 0, s>>>(src, lds, dst, ldd, rows, cols);
+    count_launch();
+    return cudaGetLastError();
+}
+
+template cudaError_t complex_scale<float>(float*, size_t, size_t, size_t, float, float, cudaStream_t);
+template cudaError_t complex_scale<double>(double*, size_t, size_t, size_t, double, double, cudaStream_t);
+template cudaError_t complex_transpose<float>(float*, size_t, const float*, size_t, size_t, size_t, cudaStream_t);
+template cudaError_t complex_transpose<double>(double*, size_t, const double*, size_t, size_t, size_t, cudaStream_t);
 
 // ta / tb: 0 = NoTrans, 1 = Trans, 2 = ConjTrans.  Pointers are to the real parts of the first
 // elements; leading dimensions count complex elements.
@@ -110,7 +142,7 @@ cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R
                            const R* B, size_t ldb, R br, R bi, R* C, size_t ldc, cudaStream_t s)
 {
     if (M == 0 || N == 0) return cudaSuccess;
-    if (K == 0 || (ar == R(0) && ai == R(0))) return cscale<R>(C, ldc, M, N, br, bi, s);
+    if (K == 0 || (ar == R(0) && ai == R(0))) return complex_scale<R>(C, ldc, M, N, br, bi, s);
 
     constexpr size_t Q = 16 / sizeof(R);
     auto round_up = [](size_t v, size_t q) { return (v + q - 1) / q * q; };
@@ -126,7 +158,7 @@ cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R
 
     R beta = br;
     if (bi != R(0)) {                       // complex beta: scale first, then accumulate
-        e = cscale<R>(C, ldc, M, N, br, bi, s);
+        e = complex_scale<R>(C, ldc, M, N, br, bi, s);
         beta = R(1);
     }
     if (e == cudaSuccess) {

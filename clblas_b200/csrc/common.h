@@ -90,6 +90,17 @@ template <typename R>
 cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R ai, const R* A, size_t lda,
                            const R* B, size_t ldb, R br, R bi, R* C, size_t ldc, cudaStream_t s);
 
+// C <- beta*C on an M x N complex matrix (beta == 0 stores zeros without reading); dst = src^T for complex matrices.
+template <typename R>
+cudaError_t complex_scale(R* C, size_t ldc, size_t M, size_t N, R br, R bi, cudaStream_t s);
+template <typename R>
+cudaError_t complex_transpose(R* dst, size_t ldd, const R* src, size_t lds, size_t rows, size_t cols, cudaStream_t s);
+
+// Complex triangular solve (trsm.cu): op 0 NoTrans, 1 Trans, 2 ConjTrans; B (M x N complex) overwritten by X.
+template <typename R>
+cudaError_t ctrsm_colmajor(bool right, bool lower, int op, bool unit, size_t M, size_t N, R ar, R ai,
+                           const R* A, size_t lda, R* B, size_t ldb, cudaStream_t s);
+
 // Blocked triangular solve on a column-major problem (B overwritten by X).
 template <typename T>
 cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,

@@ -330,6 +330,196 @@ cudaError_t dtrsm_colmajor_noalloc(bool right, bool lower, bool trans, bool unit
     return solve_range<double>(c, 0, nblk, alpha);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Complex triangular solve (clblasCtrsm / clblasZtrsm, src/clBLAS.h:8132-8151, :8202-8221;
+// src/library/blas/xtrsm.cc:1787-1911) on the real machinery above.
+//
+// With every complex entry a written as the real 2 x 2 block [[re, -im], [im, re]], the complex system
+// op(A) X = B with interleaved (re, im) storage of X and B IS the real system A~ X_real = B_real of twice
+// the order, and A~ is triangular by 128 x 128 blocks (64 complex rows each).  So the recursion, its GEMM
+// updates and the in-place leaf products above run unchanged on A~ (materialised once, strictly
+// block-off-diagonal part only) and on B where it lies; only the inversion of the diagonal blocks is
+// complex-aware: it inverts the 64 x 64 complex blocks and stores the 2 x 2-block form of the inverses.
+// rep(A)^T = rep(A^H), so A^H is the real solver's transposition of rep(A), A^T that of rep(conj A).
+// A Right-side solve is the Left-side solve of the transposed system on a transposed copy of B.
+namespace {
+
+constexpr int CNB = NB / 2;       // complex rows per diagonal block
+
+template <typename R> struct Pair2;
+template <> struct Pair2<float> { using type = float2; };
+template <> struct Pair2<double> { using type = double2; };
+
+// One CTA of CNB threads per diagonal block: thread j computes column j of X = L^-1 by forward
+// substitution (L = the block, or its transpose when the triangle is the upper one); the block is
+// conjugated on load when asked.  inv[b] receives the 128 x 128 real form of the inverse, completed
+// with the identity beyond the order n of the matrix.
+template <typename R>
+__global__ void __launch_bounds__(CNB)
+ctrtri_diag_kernel(const R* __restrict__ A, size_t lda, size_t n, bool lower, bool unit, bool conj, R* __restrict__ inv)
+{
+    using R2 = typename Pair2<R>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    R2* Ls = reinterpret_cast<R2*>(smem_raw);            // Ls[i * CNB + k] = L[i][k]
+    R2* Xs = Ls + CNB * CNB;                             // Xs[k * CNB + j] = X[k][j]
+    R2* rinv = Xs + CNB * CNB;                           // 1 / L[i][i]
+
+    const size_t b = blockIdx.x, r0 = b * CNB;
+    const int nv = (n - r0 < (size_t)CNB) ? (int)(n - r0) : CNB;
+    const R* Ab = A + 2 * (r0 + r0 * lda);
+    const int t = threadIdx.x;
+
+    for (int e = t; e < CNB * CNB; e += CNB) {
+        const int i = e % CNB, k = e / CNB;              // L[i][k]; i >= k is the triangle
+        R2 v; v.x = R(0); v.y = R(0);
+        if (i == k) {
+            v.x = R(1);
+            if (i < nv && !unit) v = *reinterpret_cast<const R2*>(Ab + 2 * ((size_t)i + (size_t)i * lda));
+        } else if (i > k && i < nv) {
+            v = lower ? *reinterpret_cast<const R2*>(Ab + 2 * ((size_t)i + (size_t)k * lda))
+                      : *reinterpret_cast<const R2*>(Ab + 2 * ((size_t)k + (size_t)i * lda));
+        }
+        if (conj) v.y = -v.y;
+        Ls[i * CNB + k] = v;
+    }
+    __syncthreads();
+    {
+        const R2 d = Ls[t * CNB + t];
+        const R den = d.x * d.x + d.y * d.y;
+        R2 r; r.x = d.x / den; r.y = -d.y / den;
+        rinv[t] = r;
+    }
+    __syncthreads();
+
+    const int j = t;
+    for (int i = 0; i < CNB; i++) {
+        R2 x; x.x = R(0); x.y = R(0);
+        if (i == j) {
+            x = rinv[i];
+        } else if (i > j) {
+            R sr = R(0), si = R(0);
+            for (int k = j; k < i; k++) {
+                const R2 l = Ls[i * CNB + k], y = Xs[k * CNB + j];
+                sr += l.x * y.x - l.y * y.y;
+                si += l.x * y.y + l.y * y.x;
+            }
+            const R2 q = rinv[i];
+            x.x = -(sr * q.x - si * q.y);
+            x.y = -(sr * q.y + si * q.x);
+        }
+        Xs[i * CNB + j] = x;                             // only this thread reads column j back
+    }
+    __syncthreads();
+
+    R* out = inv + b * (size_t)(NB * NB);
+    for (int e = t; e < NB * NB; e += CNB) {
+        const int r = e % NB, c = e / NB;
+        const int i = r / 2, k = c / 2;
+        const R2 v = lower ? Xs[i * CNB + k] : Xs[k * CNB + i];      // inverse of an upper block = transposed result
+        const int pr = r & 1, pc = c & 1;
+        out[e] = (pr == pc) ? v.x : (pr ? v.y : -v.y);
+    }
+}
+
+// A~ from the referenced triangle of A, blocks strictly off the block diagonal only (the diagonal blocks
+// are used through their inverses).  i runs along the contiguous direction.
+template <typename R>
+__global__ void __launch_bounds__(256) expand_tri_kernel(const R* __restrict__ A, size_t lda, R* __restrict__ E, size_t lde,
+                                                         size_t n, bool lower, bool conj)
+{
+    using R2 = typename Pair2<R>::type;
+    const size_t total = n * n;
+    for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < total; e += (size_t)gridDim.x * 256) {
+        const size_t i = e % n, j = e / n;
+        const size_t bi = i / CNB, bj = j / CNB;
+        if (lower ? bi <= bj : bi >= bj) continue;
+        R2 a = *reinterpret_cast<const R2*>(A + 2 * (i + j * lda));
+        if (conj) a.y = -a.y;
+        R2 c0, c1;
+        c0.x = a.x; c0.y = a.y; c1.x = -a.y; c1.y = a.x;
+        *reinterpret_cast<R2*>(E + 2 * i + (2 * j) * lde) = c0;
+        *reinterpret_cast<R2*>(E + 2 * i + (2 * j + 1) * lde) = c1;
+    }
+}
+
+template <typename R>
+cudaError_t ctrsm_left(bool lower, int op, bool unit, size_t M, size_t N, const R* A, size_t lda, R* B, size_t ldb,
+                       cudaStream_t s)
+{
+    // op: 0 A, 1 A^T, 2 A^H, 3 conj(A)
+    const bool conj = (op == 1 || op == 3), rtrans = (op == 1 || op == 2);
+    TrsmCtx<R> c;
+    c.right = false; c.lower = lower; c.trans = rtrans; c.eff_lower = (lower != rtrans);
+    c.M = 2 * M; c.N = N; c.n = 2 * M; c.B = B; c.ldb = 2 * ldb; c.s = s;
+    const size_t nblk = (M + CNB - 1) / CNB;
+    const size_t inv_elems = nblk * (size_t)(NB * NB);
+    const size_t tmp_elems = (size_t)NB * N;
+    constexpr size_t Q = 16 / sizeof(R);
+    const size_t lde = (2 * M + Q - 1) / Q * Q;
+    const size_t e_elems = nblk > 1 ? lde * 2 * M : 0;
+
+    R* ws = nullptr;
+    cudaError_t e = ws_alloc(reinterpret_cast<void**>(&ws), (inv_elems + tmp_elems + e_elems) * sizeof(R), s);
+    if (e != cudaSuccess) return e;
+    c.inv = ws;
+    c.tmp = ws + inv_elems;
+    R* E = ws + inv_elems + tmp_elems;
+    c.A = E; c.lda = lde;
+
+    const size_t smem = (size_t)(2 * CNB * CNB + CNB) * 2 * sizeof(R);
+    static bool attr_done[2][64] = {};
+    const int ti = sizeof(R) == 8;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[ti][dev]) {
+        e = cudaFuncSetAttribute(ctrtri_diag_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { ws_free(ws, s); return e; }
+        if (dev >= 0 && dev < 64) attr_done[ti][dev] = true;
+    }
+    ctrtri_diag_kernel<R><<<(unsigned)nblk, CNB, smem, s>>>(A, lda, M, lower, unit, conj, c.inv);
+    count_launch();
+    e = cudaGetLastError();
+    if (e == cudaSuccess && nblk > 1) {
+        const unsigned blocks = (unsigned)std::min<size_t>((M * M + 255) / 256, (size_t)sm_count() * 16);
+        expand_tri_kernel<R><<<blocks, 256, 0, s>>>(A, lda, E, lde, M, lower, conj);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = solve_range<R>(c, 0, nblk, R(1));
+    const cudaError_t e2 = ws_free(ws, s);
+    return e != cudaSuccess ? e : e2;
+}
+
+}  // namespace
+
+template <typename R>
+cudaError_t ctrsm_colmajor(bool right, bool lower, int op, bool unit, size_t M, size_t N, R ar, R ai,
+                           const R* A, size_t lda, R* B, size_t ldb, cudaStream_t s)
+{
+    if (M == 0 || N == 0) return cudaSuccess;
+    // B <- alpha*B first (alpha == 0: B <- 0 and A is not referenced), then the solve with alpha = 1
+    cudaError_t e = complex_scale<R>(B, ldb, M, N, ar, ai, s);
+    if (e != cudaSuccess || (ar == R(0) && ai == R(0))) return e;
+    if (!right) return ctrsm_left<R>(lower, op, unit, M, N, A, lda, B, ldb, s);
+
+    // X op(A) = B  <=>  op(A)^T X^T = B^T: (A)^T -> A^T, (A^T)^T -> A, (A^H)^T -> conj(A)
+    constexpr size_t Q = 16 / sizeof(R);
+    const size_t ldt = (N + Q - 1) / Q * Q;
+    R* Bt = nullptr;
+    e = ws_alloc(reinterpret_cast<void**>(&Bt), 2 * ldt * M * sizeof(R), s);
+    if (e != cudaSuccess) return e;
+    e = complex_transpose<R>(Bt, ldt, B, ldb, M, N, s);
+    if (e == cudaSuccess) e = ctrsm_left<R>(lower, op == 0 ? 1 : op == 1 ? 0 : 3, unit, N, M, A, lda, Bt, ldt, s);
+    if (e == cudaSuccess) e = complex_transpose<R>(B, ldb, Bt, ldt, N, M, s);
+    const cudaError_t e2 = ws_free(Bt, s);
+    return e != cudaSuccess ? e : e2;
+}
+
+template cudaError_t ctrsm_colmajor<float>(bool, bool, int, bool, size_t, size_t, float, float, const float*, size_t, float*,
+                                           size_t, cudaStream_t);
+template cudaError_t ctrsm_colmajor<double>(bool, bool, int, bool, size_t, size_t, double, double, const double*, size_t,
+                                            double*, size_t, cudaStream_t);
+
 template cudaError_t trsm_colmajor<float>(bool, bool, bool, bool, size_t, size_t, float, const float*, size_t,
                                           float*, size_t, cudaStream_t);
 template cudaError_t trsm_colmajor<double>(bool, bool, bool, bool, size_t, size_t, double, const double*, size_t,

@@ -177,6 +177,28 @@ clblasStatus clblasDtrsm(
     unsigned numCommandQueues, clblasQueue* commandQueues,
     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
 
+/* ---- complex TRSM: replaces clblasCtrsm (src/clBLAS.h:8132-8151) and clblasZtrsm (:8202-8221), which the
+ *      reference serves through the same front end and checks as clblasStrsm (src/library/blas/xtrsm.cc:1787-1911,
+ *      functor/functor_xtrsm.cc:57-75).  Interleaved (re, im) matrices; clblasConjTrans conjugates.  Workspace
+ *      from the library's pool: about twice the size of A, plus a copy of B for side == clblasRight. */
+clblasStatus clblasCtrsm(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    FloatComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZtrsm(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    DoubleComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- TRMM: replaces clblasStrmm (src/clBLAS.h:7697-7717) and clblasDtrmm (:7772-7792), implemented by
  *      src/library/blas/xtrmm.c:30-180 in the reference.  B <- alpha*op(A)*B (Left) or alpha*B*op(A) (Right),
  *      A triangular; only the referenced triangle is read and a unit diagonal is not read.  Checks in the

@@ -89,6 +89,8 @@ def _lib(impl: str) -> ctypes.CDLL:
         ptr = ctypes.c_void_p
         getattr(lib, f"{prefix}{p}gemm").argtypes = [i, i, i, sz, sz, sz, ct, ct, ptr, sz, ptr, sz, ct, ct, ptr, sz]
         getattr(lib, f"{prefix}{p}gemm").restype = None
+        getattr(lib, f"{prefix}{p}trsm").argtypes = [i, i, i, i, i, sz, sz, ct, ct, ptr, sz, ptr, sz]
+        getattr(lib, f"{prefix}{p}trsm").restype = None
     lib._prefix = prefix
     _libs[impl] = lib
     return lib
@@ -138,6 +140,15 @@ def cgemm(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, bet
     fn = getattr(lib, f"{lib._prefix}{p}gemm")
     fn(order, transA, transB, M, N, K, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb, beta.real, beta.imag,
        _p(C, offC), ldc)
+
+
+def ctrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, impl: str = "port") -> None:
+    """Complex triangular solve in place on the flat complex buffer B; alpha a Python complex number."""
+    lib = _lib(impl)
+    p = "c" if B.dtype == np.complex64 else "z"
+    alpha = complex(alpha)
+    fn = getattr(lib, f"{lib._prefix}{p}trsm")
+    fn(order, side, uplo, transA, diag, M, N, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb)
 
 
 def syrk(order, uplo, trans, N, K, alpha, A, offA, lda, beta, C, offC, ldc, impl: str = "port") -> None:

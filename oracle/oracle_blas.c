@@ -289,3 +289,71 @@ void NAME(int order, int transA, int transB, size_t M, size_t N, size_t K, T alr
 
 DEFINE_CGEMM(oracle_cgemm, float)
 DEFINE_CGEMM(oracle_zgemm, double)
+
+/* Complex TRSM: NaiveBlas::trsm<FloatComplex / DoubleComplex> (naive_blas.cpp:632-690) with the complex
+ * operators written out; division (a/b) = ((ar*br + ai*bi)/d, (br*ai - ar*bi)/d), d = br*br + bi*bi
+ * (naive_blas.cpp:333-341).  A ConjTrans accessor conjugates what it reads, also after the Right-side flip. */
+#define DEFINE_CTRSM(NAME, T)                                                                  \
+void NAME(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, T alr, T ali, \
+          const T* A, size_t lda, T* B, size_t ldb)                                            \
+{                                                                                              \
+    size_t rowsA = (side == OLeft) ? M : N;                                                    \
+    size_t colsB = (side == OLeft) ? N : M;                                                    \
+    acc_t ma = make_acc(order, transA, lda);                                                   \
+    acc_t mb = make_acc(order, ONoTrans, ldb);                                                 \
+    const int cj = (transA == OConjTrans);                                                     \
+    int revPass = (uplo == OUpper) ^ (transA != ONoTrans);                                     \
+    size_t i;                                                                                  \
+    if (side == ORight) {                                                                      \
+        ma.tra = !ma.tra;                                                                      \
+        mb.tra = !mb.tra;                                                                      \
+        revPass = !revPass;                                                                    \
+    }                                                                                          \
+    for (i = 0; i < rowsA; i++) {                                                              \
+        size_t row = revPass ? (rowsA - i - 1) : i;                                            \
+        size_t boundK = revPass ? (rowsA - row - 1) : row;                                     \
+        long long j;                                                                           \
+        _Pragma("omp parallel for schedule(static)")                                           \
+        for (j = 0; j < (long long)colsB; j++) {                                               \
+            T tr = (T)0.0, ti = (T)0.0;                                                        \
+            size_t k;                                                                          \
+            for (k = 0; k <= boundK; k++) {                                                    \
+                size_t col = revPass ? (rowsA - k - 1) : k;                                    \
+                if (col == row) {                                                              \
+                    T ar = (T)1.0, ai = (T)0.0;                                                \
+                    const T* b = B + 2 * at(mb, row, (size_t)j);                               \
+                    const T nr = b[0] - tr, ni = b[1] - ti;                                    \
+                    T d;                                                                       \
+                    if (diag != OUnit) {                                                       \
+                        const T* a = A + 2 * at(ma, row, col);                                 \
+                        ar = a[0]; ai = cj ? -a[1] : a[1];                                     \
+                    }                                                                          \
+                    d = ar * ar + ai * ai;                                                     \
+                    tr = (nr * ar + ni * ai) / d;                                              \
+                    ti = (ar * ni - nr * ai) / d;                                              \
+                } else {                                                                       \
+                    const T* a = A + 2 * at(ma, row, col);                                     \
+                    const T* b = B + 2 * at(mb, col, (size_t)j);                               \
+                    const T ar = a[0], ai = cj ? -a[1] : a[1];                                 \
+                    const T pr = ar * b[0] - ai * b[1], pi = ar * b[1] + b[0] * ai;            \
+                    tr = tr + pr;                                                              \
+                    ti = ti + pi;                                                              \
+                }                                                                              \
+            }                                                                                  \
+            B[2 * at(mb, row, (size_t)j)] = tr;                                                \
+            B[2 * at(mb, row, (size_t)j) + 1] = ti;                                            \
+        }                                                                                      \
+    }                                                                                          \
+    for (i = 0; i < rowsA; i++) {                                                              \
+        size_t j;                                                                              \
+        for (j = 0; j < colsB; j++) {                                                          \
+            T* b = B + 2 * at(mb, i, j);                                                       \
+            const T xr = b[0] * alr - b[1] * ali, xi = b[0] * ali + alr * b[1];                \
+            b[0] = xr;                                                                         \
+            b[1] = xi;                                                                         \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_CTRSM(oracle_ctrsm, float)
+DEFINE_CTRSM(oracle_ztrsm, double)

@@ -117,4 +117,22 @@ void ref_zgemm(int order, int transA, int transB, size_t M, size_t N, size_t K, 
                                    NaiveBlas::doubleComplex(ber, bei), reinterpret_cast<NaiveBlas::DoubleComplex*>(C), ldc);
 }
 
+void ref_ctrsm(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, float alr, float ali,
+               const float* A, size_t lda, float* B, size_t ldb)
+{
+    NaiveBlas::trsm<NaiveBlas::FloatComplex>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasSide)side, (NaiveBlas::clblasUplo)uplo,
+                                             (NaiveBlas::clblasTranspose)transA, (NaiveBlas::clblasDiag)diag, M, N,
+                                             NaiveBlas::floatComplex(alr, ali), reinterpret_cast<const NaiveBlas::FloatComplex*>(A), lda,
+                                             reinterpret_cast<NaiveBlas::FloatComplex*>(B), ldb);
+}
+
+void ref_ztrsm(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, double alr, double ali,
+               const double* A, size_t lda, double* B, size_t ldb)
+{
+    NaiveBlas::trsm<NaiveBlas::DoubleComplex>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasSide)side, (NaiveBlas::clblasUplo)uplo,
+                                              (NaiveBlas::clblasTranspose)transA, (NaiveBlas::clblasDiag)diag, M, N,
+                                              NaiveBlas::doubleComplex(alr, ali), reinterpret_cast<const NaiveBlas::DoubleComplex*>(A), lda,
+                                              reinterpret_cast<NaiveBlas::DoubleComplex*>(B), ldb);
+}
+
 }  // extern "C"

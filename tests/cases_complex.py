@@ -80,3 +80,74 @@ def sweep_cgemm_cases(prec, mode):
                                         beta=[1 + 0j, 0j, 2 + 1j, -1 + 0j][seed % 4], pad=(seed % 4, seed % 3, seed % 5),
                                         off=(seed % 3, seed % 4, seed % 6), mode=mode, seed=seed))
     return cases
+
+
+# ------------------------------------------------------------------------------------- complex TRSM
+from oracle import Left, Lower, NonUnit, Right, Unit, Upper  # noqa: E402
+
+
+def ctrsm_case(prec, order, side, uplo, transA, diag, M, N, alpha=1 + 0j, pad=(0, 0), off=(0, 0), seed=12345):
+    n = M if side == Left else N
+    return dict(kind="ctrsm", prec=prec, order=order, side=side, uplo=uplo, transA=transA, diag=diag, M=M, N=N, alpha=alpha,
+                lda=n + pad[0], ldb=_min_ld(order, NoTrans, M, N) + pad[1], offA=off[0], offB=off[1], seed=seed)
+
+
+def ctrsm_logical(c):
+    """Stored triangular A (n x n complex; NaN outside the referenced triangle and on a unit diagonal) and B.
+    Real and imaginary parts each follow the reference-style generator of the real TRSM cases, so rows
+    stay diagonally dominant."""
+    n = c["M"] if c["side"] == Left else c["N"]
+    rd = RDT[c["prec"]]
+    Ar, Br = oracle.trsm_inputs(n, (c["M"], c["N"]), c["uplo"], c["diag"], rd, c["seed"])
+    Ai, Bi = oracle.trsm_inputs(n, (c["M"], c["N"]), c["uplo"], c["diag"], rd, c["seed"] + 7919)
+    return (Ar + 1j * (Ai / 2)).astype(CDT[c["prec"]]), (Br + 1j * Bi).astype(CDT[c["prec"]])
+
+
+def ctrsm_buffers(c, logical=None, tail=3):
+    A, B = logical if logical is not None else ctrsm_logical(c)
+    return (oracle.pack(A, c["order"], NoTrans, c["lda"], c["offA"], pad_value=CNAN, tail=tail),
+            oracle.pack(B, c["order"], NoTrans, c["ldb"], c["offB"], pad_value=CNAN, tail=tail))
+
+
+def ctrsm_op_triangle(c, A):
+    """Dense op(A): zeros outside the triangle, ones on a unit diagonal, transposed / conjugated as asked."""
+    T = np.tril(np.nan_to_num(A, nan=0.0)) if c["uplo"] == Lower else np.triu(np.nan_to_num(A, nan=0.0))
+    if c["diag"] == Unit:
+        T = T.copy()
+        T[np.arange(T.shape[0]), np.arange(T.shape[0])] = 1.0
+    return T if c["transA"] == NoTrans else (T.T if c["transA"] == Trans else np.conj(T.T))
+
+
+def ctrsm_backward_ratio(c, X, T, B):
+    """max |alpha B - op(A) X| / (|op(A)||X| + |alpha||B|) (X op(A) for Right), divided by 4*(2n)*u."""
+    T, X, B = (x.astype(np.complex128) for x in (T, X, B))
+    if c["side"] == Left:
+        res, den = c["alpha"] * B - T @ X, np.abs(T) @ np.abs(X) + abs(c["alpha"]) * np.abs(B)
+    else:
+        res, den = c["alpha"] * B - X @ T, np.abs(X) @ np.abs(T) + abs(c["alpha"]) * np.abs(B)
+    den = np.where(den == 0, np.finfo(np.float64).tiny, den)
+    return float(np.max(np.abs(res) / den) / (4.0 * 2 * T.shape[0] * oracle.unit_roundoff(RDT[c["prec"]])))
+
+
+def golden_ctrsm_cases():
+    out = {}
+    k = 0
+    for prec in "cz":
+        for order, side, uplo, ta, diag in itertools.product(ORDERS, (Left, Right), (Upper, Lower), ALL_TRANS, (Unit, NonUnit)):
+            M, N = [(9, 5), (16, 17), (7, 12)][k % 3]
+            out[f"ctrsm_{prec}_{order}{side}{uplo}{ta}{diag}"] = ctrsm_case(prec, order, side, uplo, ta, diag, M, N,
+                                                                           alpha=[1 + 0j, -2 + 1j, 0.5j][k % 3], pad=(2, 3),
+                                                                           off=(1, 4), seed=1300 + k)
+            k += 1
+    return out
+
+
+def sweep_ctrsm_cases(prec):
+    cases = []
+    seed = 14000
+    for order, side, uplo, ta, diag in itertools.product(ORDERS, (Left, Right), (Upper, Lower), ALL_TRANS, (Unit, NonUnit)):
+        for (M, N) in ((8, 8), (17, 33), (64, 64), (130, 257), (300, 129)):
+            seed += 1
+            cases.append(ctrsm_case(prec, order, side, uplo, ta, diag, M, N, alpha=[1 + 0j, 2.5 - 1j, -0.5j][seed % 3],
+                                    pad=(seed % 5, seed % 7), off=(seed % 3, seed % 11), seed=seed))
+    return cases

@@ -71,6 +71,11 @@ def main():
         oracle.cgemm(c["order"], c["transA"], c["transB"], c["M"], c["N"], c["K"], c["alpha"], A, c["offA"], c["lda"],
                      B, c["offB"], c["ldb"], c["beta"], C, c["offC"], c["ldc"], impl="ref")
         out[name] = C
+    for name, c in cases_complex.golden_ctrsm_cases().items():
+        A, B = cases_complex.ctrsm_buffers(c)
+        oracle.ctrsm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A, c["offA"],
+                     c["lda"], B, c["offB"], c["ldb"], impl="ref")
+        out[name] = B
     path = os.path.join(os.path.dirname(__file__), "level3_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} cases, {os.path.getsize(path)} bytes")

@@ -47,3 +47,40 @@ def test_integer_inputs_are_exact(built_oracle):
         got = oracle.view(run(c, "port", logical), c["order"], NoTrans, c["M"], c["N"], c["ldc"], c["offC"])
         want, _ = cc.cgemm_exact(c, logical)
         assert np.array_equal(got, want), c
+
+
+# ------------------------------------------------------------------------------------- complex TRSM
+def run_trsm(c, impl, logical=None):
+    A, B = cc.ctrsm_buffers(c, logical)
+    oracle.ctrsm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A, c["offA"], c["lda"],
+                 B, c["offB"], c["ldb"], impl=impl)
+    return B
+
+
+def test_trsm_port_matches_golden(built_oracle):
+    """Golden outputs made with NaiveBlas::trsm<FloatComplex/DoubleComplex> (naive_blas.cpp:632-690)."""
+    g = np.load(GOLDEN)
+    items = list(cc.golden_ctrsm_cases().items())
+    assert len(items) == 96
+    for name, c in items:
+        assert same_bits(run_trsm(c, "port"), g[name]), name
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference's own naive_blas.cpp was not compiled here")
+def test_trsm_port_matches_reference_code(built_oracle):
+    for prec in "cz":
+        for c in cc.sweep_ctrsm_cases(prec)[::7]:
+            if max(c["M"], c["N"]) > 140:
+                continue
+            assert same_bits(run_trsm(c, "port"), run_trsm(c, "ref")), c
+
+
+def test_trsm_solves_the_system(built_oracle):
+    """Poisoned entries are never read and the solution satisfies op(A) X = alpha B within the bound."""
+    for c in cc.sweep_ctrsm_cases("z")[::5]:
+        if max(c["M"], c["N"]) > 140:
+            continue
+        logical = cc.ctrsm_logical(c)
+        X = oracle.view(run_trsm(c, "port", logical), c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
+        assert np.all(np.isfinite(X)), c
+        assert cc.ctrsm_backward_ratio(c, X, cc.ctrsm_op_triangle(c, logical[0]), logical[1]) <= 1.0, c
