@@ -64,6 +64,12 @@ class DoubleComplex(ctypes.Structure):
     _fields_ = [("re", ctypes.c_double), ("im", ctypes.c_double)]
 
 
+MATRIX_HELPERS = (["clblasMatrixSizeInfo", "clblasCreateMatrix", "clblasCreateMatrixWithLd", "clblasCreateMatrixFromHost",
+                   "clblasFillVector", "clblasFillVectorAsync", "clblasFillSubMatrix", "clblasFillSubMatrixAsync",
+                   "clblasFillMatrix", "clblasFillMatrixAsync"]
+                  + [f"clblas{k}{s}Matrix{a}" for k in ("Write", "Read", "Copy") for s in ("Sub", "") for a in ("", "Async")])
+
+
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -102,6 +108,30 @@ def _load() -> ctypes.CDLL:
         f = getattr(lib, name)
         f.argtypes = [i, i, i, i, i, sz, sz, ct, vp, sz, sz, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
+    # matrix helpers (one stream, not an array of queues)
+    psz, pint = ctypes.POINTER(sz), ctypes.POINTER(i)
+    lib.clblasMatrixSizeInfo.argtypes = [i, sz, sz, sz, sz, psz, psz]
+    lib.clblasCreateMatrix.argtypes = [vp, i, sz, sz, sz, sz, psz, psz, pint]
+    lib.clblasCreateMatrixWithLd.argtypes = [vp, i, sz, sz, sz, sz, psz, pint]
+    lib.clblasCreateMatrixFromHost.argtypes = [vp, i, sz, sz, sz, sz, vp, sz, sz, vp, u, pvp, pint]
+    for name in ("clblasCreateMatrix", "clblasCreateMatrixWithLd", "clblasCreateMatrixFromHost"):
+        getattr(lib, name).restype = vp
+    sub = [i, sz, vp, sz, sz, sz, sz, sz, sz, vp, sz, sz, sz, sz, sz, sz, sz, sz, vp, u, pvp]
+    full = [i, sz, sz, sz, vp, sz, sz, vp, sz, sz, vp, u, pvp]
+    for kind in ("Write", "Read", "Copy"):
+        getattr(lib, f"clblas{kind}SubMatrix").argtypes = sub
+        getattr(lib, f"clblas{kind}SubMatrixAsync").argtypes = sub + [pvp]
+        getattr(lib, f"clblas{kind}Matrix").argtypes = full
+        getattr(lib, f"clblas{kind}MatrixAsync").argtypes = full + [pvp]
+    lib.clblasFillVector.argtypes = [sz, sz, vp, sz, vp, vp, u, pvp]
+    lib.clblasFillVectorAsync.argtypes = lib.clblasFillVector.argtypes + [pvp]
+    lib.clblasFillSubMatrix.argtypes = [i, sz, vp, sz, sz, sz, sz, sz, sz, sz, sz, vp, vp, u, pvp]
+    lib.clblasFillSubMatrixAsync.argtypes = lib.clblasFillSubMatrix.argtypes + [pvp]
+    lib.clblasFillMatrix.argtypes = [i, sz, vp, sz, sz, sz, sz, vp, vp, u, pvp]
+    lib.clblasFillMatrixAsync.argtypes = lib.clblasFillMatrix.argtypes + [pvp]
+    for name in MATRIX_HELPERS:
+        if not name.startswith("clblasCreate"):
+            getattr(lib, name).restype = i
     lib.clblasSetup.argtypes = []
     lib.clblasSetup.restype = i
     lib.clblasTeardown.argtypes = []
@@ -129,7 +159,7 @@ EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
            "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
-           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm"]
+           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm"] + MATRIX_HELPERS
 
 
 def _ptr(x) -> Optional[int]:
@@ -314,6 +344,69 @@ def clblasZtrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, o
     nq, q, nw, w, e = _queues_events(queues, wait, events)
     return lib.clblasZtrsm(order, side, uplo, transA, diag, M, N, _cplx(DoubleComplex, alpha), _ptr(A), offA, lda,
                            _ptr(B), offB, ldb, nq, q, nw, w, e)
+
+
+# ---- matrix helpers (src/clBLAS.h:9665-10238).  Host matrices are numpy arrays, device matrices torch tensors or
+# raw addresses; `queue` defaults to torch's current stream; the blocking variants are mirrored here, the Async
+# ones are reachable through `lib`.
+def _host_ptr(a):
+    return a if a is None or isinstance(a, int) else a.ctypes.data
+
+
+def _stream(queue):
+    if queue is None:
+        import torch
+        queue = torch.cuda.current_stream()
+    return _handle(queue)
+
+
+def clblasMatrixSizeInfo(order, rows, columns, elemsize, padding):
+    """(status, ld, fullsize in bytes) of a rows x columns matrix with `padding` extra elements per line."""
+    ld, full = ctypes.c_size_t(), ctypes.c_size_t()
+    st = lib.clblasMatrixSizeInfo(order, rows, columns, elemsize, padding, ctypes.byref(ld), ctypes.byref(full))
+    return st, ld.value, full.value
+
+
+def clblasWriteMatrix(order, sx, sy, element_size, A, offA, ldA, B, offB, ldB, queue=None) -> int:
+    """Host matrix A (numpy) -> device matrix B, sx rows by sy columns."""
+    return lib.clblasWriteMatrix(order, sx, sy, element_size, _host_ptr(A), offA, ldA, _ptr(B), offB, ldB, _stream(queue), 0, None)
+
+
+def clblasReadMatrix(order, sx, sy, element_size, A, offA, ldA, B, offB, ldB, queue=None) -> int:
+    """Device matrix A -> host matrix B (numpy)."""
+    return lib.clblasReadMatrix(order, sx, sy, element_size, _ptr(A), offA, ldA, _host_ptr(B), offB, ldB, _stream(queue), 0, None)
+
+
+def clblasCopyMatrix(order, sx, sy, element_size, A, offA, ldA, B, offB, ldB, queue=None) -> int:
+    return lib.clblasCopyMatrix(order, sx, sy, element_size, _ptr(A), offA, ldA, _ptr(B), offB, ldB, _stream(queue), 0, None)
+
+
+def clblasWriteSubMatrix(order, element_size, A, offA, ldA, nrA, ncA, xA, yA, B, offB, ldB, nrB, ncB, xB, yB, nx, ny, queue=None) -> int:
+    return lib.clblasWriteSubMatrix(order, element_size, _host_ptr(A), offA, ldA, nrA, ncA, xA, yA, _ptr(B), offB, ldB, nrB, ncB,
+                                    xB, yB, nx, ny, _stream(queue), 0, None)
+
+
+def clblasReadSubMatrix(order, element_size, A, offA, ldA, nrA, ncA, xA, yA, B, offB, ldB, nrB, ncB, xB, yB, nx, ny, queue=None) -> int:
+    return lib.clblasReadSubMatrix(order, element_size, _ptr(A), offA, ldA, nrA, ncA, xA, yA, _host_ptr(B), offB, ldB, nrB, ncB,
+                                   xB, yB, nx, ny, _stream(queue), 0, None)
+
+
+def clblasCopySubMatrix(order, element_size, A, offA, ldA, nrA, ncA, xA, yA, B, offB, ldB, nrB, ncB, xB, yB, nx, ny, queue=None) -> int:
+    return lib.clblasCopySubMatrix(order, element_size, _ptr(A), offA, ldA, nrA, ncA, xA, yA, _ptr(B), offB, ldB, nrB, ncB,
+                                   xB, yB, nx, ny, _stream(queue), 0, None)
+
+
+def clblasFillVector(nb_elem, element_size, A, offA, pattern: bytes, queue=None) -> int:
+    return lib.clblasFillVector(nb_elem, element_size, _ptr(A), offA, ctypes.c_char_p(pattern), _stream(queue), 0, None)
+
+
+def clblasFillSubMatrix(order, element_size, A, offA, ldA, nrA, ncA, xA, yA, nx, ny, pattern: bytes, queue=None) -> int:
+    return lib.clblasFillSubMatrix(order, element_size, _ptr(A), offA, ldA, nrA, ncA, xA, yA, nx, ny, ctypes.c_char_p(pattern),
+                                   _stream(queue), 0, None)
+
+
+def clblasFillMatrix(order, element_size, A, offA, ldA, nrA, ncA, pattern: bytes, queue=None) -> int:
+    return lib.clblasFillMatrix(order, element_size, _ptr(A), offA, ldA, nrA, ncA, ctypes.c_char_p(pattern), _stream(queue), 0, None)
 
 
 NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = 4096, 8192

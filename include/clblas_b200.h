@@ -362,6 +362,88 @@ const char* clblasB200LastGemmKernel(void);
  * src/library/blas/impl.c:81-129).  Returns the previous value. */
 int clblasB200SetGemmPath(int path);
 
+/* ---- matrix helpers: replace clblasMatrixSizeInfo, clblasCreateMatrix*, clblas{Write,Read,Copy}{Sub,}Matrix{,Async}
+ *      and clblasFill{Vector,SubMatrix,Matrix}{,Async} (src/clBLAS.h:9665-10238; src/library/blas/matrix.c, fill.cc).
+ *      Same argument lists; `command_queue` is ONE cudaStream_t; host pointers are plain host memory (pinned memory
+ *      makes the Async variants truly asynchronous).  Offsets, leading dimensions, positions and extents count
+ *      elements of `element_size` bytes; for clblasRowMajor x / y and rows / columns are exchanged, as in the
+ *      reference.  A region outside either matrix is clblasInvalidValue.  The blocking variants return after the
+ *      stream has finished the copy; the Async variants record *event (created by the caller; may be NULL).
+ *      clblasCreateMatrix* ignore `context` (the current CUDA device is used) and return cudaMalloc memory that
+ *      the caller frees with cudaFree. */
+clblasStatus clblasMatrixSizeInfo(clblasOrder order, size_t rows, size_t columns, size_t elemsize, size_t padding,
+                                  size_t* ld, size_t* fullsize);
+clblasMem clblasCreateMatrix(void* context, clblasOrder order, size_t rows, size_t columns, size_t elemsize, size_t padding,
+                             size_t* ld, size_t* fullsize, int* err);
+clblasMem clblasCreateMatrixWithLd(void* context, clblasOrder order, size_t rows, size_t columns, size_t elemsize, size_t ld,
+                                   size_t* fullsize, int* err);
+clblasMem clblasCreateMatrixFromHost(void* context, clblasOrder order, size_t rows, size_t columns, size_t elemsize, size_t ld,
+                                     void* host, size_t off_host, size_t ld_host, clblasQueue command_queue,
+                                     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, int* err);
+
+clblasStatus clblasWriteSubMatrix(clblasOrder order, size_t element_size, const void* A, size_t offA, size_t ldA, size_t nrA,
+                                  size_t ncA, size_t xA, size_t yA, clblasMem B, size_t offB, size_t ldB, size_t nrB, size_t ncB,
+                                  size_t xB, size_t yB, size_t nx, size_t ny, clblasQueue command_queue,
+                                  unsigned numEventsInWaitList, const clblasEvent* eventWaitList);
+clblasStatus clblasWriteSubMatrixAsync(clblasOrder order, size_t element_size, const void* A, size_t offA, size_t ldA, size_t nrA,
+                                       size_t ncA, size_t xA, size_t yA, clblasMem B, size_t offB, size_t ldB, size_t nrB,
+                                       size_t ncB, size_t xB, size_t yB, size_t nx, size_t ny, clblasQueue command_queue,
+                                       unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* event);
+clblasStatus clblasReadSubMatrix(clblasOrder order, size_t element_size, const clblasMem A, size_t offA, size_t ldA, size_t nrA,
+                                 size_t ncA, size_t xA, size_t yA, void* B, size_t offB, size_t ldB, size_t nrB, size_t ncB,
+                                 size_t xB, size_t yB, size_t nx, size_t ny, clblasQueue command_queue,
+                                 unsigned numEventsInWaitList, const clblasEvent* eventWaitList);
+clblasStatus clblasReadSubMatrixAsync(clblasOrder order, size_t element_size, const clblasMem A, size_t offA, size_t ldA, size_t nrA,
+                                      size_t ncA, size_t xA, size_t yA, void* B, size_t offB, size_t ldB, size_t nrB, size_t ncB,
+                                      size_t xB, size_t yB, size_t nx, size_t ny, clblasQueue command_queue,
+                                      unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* event);
+clblasStatus clblasCopySubMatrix(clblasOrder order, size_t element_size, const clblasMem A, size_t offA, size_t ldA, size_t nrA,
+                                 size_t ncA, size_t xA, size_t yA, clblasMem B, size_t offB, size_t ldB, size_t nrB, size_t ncB,
+                                 size_t xB, size_t yB, size_t nx, size_t ny, clblasQueue command_queue,
+                                 unsigned numEventsInWaitList, const clblasEvent* eventWaitList);
+clblasStatus clblasCopySubMatrixAsync(clblasOrder order, size_t element_size, const clblasMem A, size_t offA, size_t ldA, size_t nrA,
+                                      size_t ncA, size_t xA, size_t yA, clblasMem B, size_t offB, size_t ldB, size_t nrB, size_t ncB,
+                                      size_t xB, size_t yB, size_t nx, size_t ny, clblasQueue command_queue,
+                                      unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* event);
+
+clblasStatus clblasWriteMatrix(clblasOrder order, size_t sx, size_t sy, size_t element_size, const void* A, size_t offA, size_t ldA,
+                               clblasMem B, size_t offB, size_t ldB, clblasQueue command_queue, unsigned numEventsInWaitList,
+                               const clblasEvent* eventWaitList);
+clblasStatus clblasWriteMatrixAsync(clblasOrder order, size_t sx, size_t sy, size_t element_size, const void* A, size_t offA,
+                                    size_t ldA, clblasMem B, size_t offB, size_t ldB, clblasQueue command_queue,
+                                    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* event);
+clblasStatus clblasReadMatrix(clblasOrder order, size_t sx, size_t sy, size_t element_size, const clblasMem A, size_t offA, size_t ldA,
+                              void* B, size_t offB, size_t ldB, clblasQueue command_queue, unsigned numEventsInWaitList,
+                              const clblasEvent* eventWaitList);
+clblasStatus clblasReadMatrixAsync(clblasOrder order, size_t sx, size_t sy, size_t element_size, const clblasMem A, size_t offA,
+                                   size_t ldA, void* B, size_t offB, size_t ldB, clblasQueue command_queue,
+                                   unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* event);
+clblasStatus clblasCopyMatrix(clblasOrder order, size_t sx, size_t sy, size_t element_size, const clblasMem A, size_t offA, size_t ldA,
+                              clblasMem B, size_t offB, size_t ldB, clblasQueue command_queue, unsigned numEventsInWaitList,
+                              const clblasEvent* eventWaitList);
+clblasStatus clblasCopyMatrixAsync(clblasOrder order, size_t sx, size_t sy, size_t element_size, const clblasMem A, size_t offA,
+                                   size_t ldA, clblasMem B, size_t offB, size_t ldB, clblasQueue command_queue,
+                                   unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* event);
+
+clblasStatus clblasFillVector(size_t nb_elem, size_t element_size, clblasMem A, size_t offA, const void* pattern,
+                              clblasQueue command_queue, unsigned numEventsInWaitList, const clblasEvent* eventWaitList);
+clblasStatus clblasFillVectorAsync(size_t nb_elem, size_t element_size, clblasMem A, size_t offA, const void* pattern,
+                                   clblasQueue command_queue, unsigned numEventsInWaitList, const clblasEvent* eventWaitList,
+                                   clblasEvent* event);
+clblasStatus clblasFillSubMatrix(clblasOrder order, size_t element_size, clblasMem A, size_t offA, size_t ldA, size_t nrA,
+                                 size_t ncA, size_t xA, size_t yA, size_t nx, size_t ny, const void* pattern,
+                                 clblasQueue command_queue, unsigned numEventsInWaitList, const clblasEvent* eventWaitList);
+clblasStatus clblasFillSubMatrixAsync(clblasOrder order, size_t element_size, clblasMem A, size_t offA, size_t ldA, size_t nrA,
+                                      size_t ncA, size_t xA, size_t yA, size_t nx, size_t ny, const void* pattern,
+                                      clblasQueue command_queue, unsigned numEventsInWaitList, const clblasEvent* eventWaitList,
+                                      clblasEvent* event);
+clblasStatus clblasFillMatrix(clblasOrder order, size_t element_size, clblasMem A, size_t offA, size_t ldA, size_t nrA, size_t ncA,
+                              const void* pattern, clblasQueue command_queue, unsigned numEventsInWaitList,
+                              const clblasEvent* eventWaitList);
+clblasStatus clblasFillMatrixAsync(clblasOrder order, size_t element_size, clblasMem A, size_t offA, size_t ldA, size_t nrA,
+                                   size_t ncA, const void* pattern, clblasQueue command_queue, unsigned numEventsInWaitList,
+                                   const clblasEvent* eventWaitList, clblasEvent* event);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,7 +16,7 @@ HEADER = os.path.join(ROOT, "include", "clblas_b200.h")
 def declared_functions():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"^\s*(?:clblasStatus|void|unsigned long long|unsigned|double|const char\*|int)\s+(clblas\w+)\s*\(", text, flags=re.M)
+    names = re.findall(r"^\s*(?:clblasStatus|clblasMem|void|unsigned long long|unsigned|double|const char\*|int)\s+(clblas\w+)\s*\(", text, flags=re.M)
     return sorted(set(names))
 
 
