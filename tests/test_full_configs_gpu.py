@@ -85,11 +85,19 @@ def test_config4_dtrsm_left_lower_8192x16384(lib):
     Bs = B0.view(N, M)[ci].cpu().numpy().T
     T = np.tril(np.nan_to_num(Av.cpu().numpy().T, nan=0.0))
     assert oracle.trsm_backward_ratio(Xs, 1.0, T, Bs, oracle.Left, np.float64) <= 1.0
-    # property: right-hand-side columns are independent -- solving a slab alone reproduces it bit for bit
+    # property: right-hand-side columns are independent -- solving a slab alone gives the same solution.  Not bit
+    # for bit: the GEMM kernels walk K forwards or backwards depending on a tile's place in the grid, and the
+    # grid depends on N, so only the rounding differs.
     Y = B0[: M * 256].clone()
     lib.clblasDtrsm(lib.clblasColumnMajor, lib.clblasLeft, lib.clblasLower, lib.clblasNoTrans, lib.clblasNonUnit,
                     M, 256, 1.0, A, 0, M, Y, 0, M)
-    assert torch.equal(Y, X[: M * 256])
+    ref = X[: M * 256]
+    assert float((Y - ref).abs().max()) <= 16 * M * 2.0 ** -53 * float(ref.abs().max())
+    # and the same call twice is bit-identical
+    Y2 = B0[: M * 256].clone()
+    lib.clblasDtrsm(lib.clblasColumnMajor, lib.clblasLeft, lib.clblasLower, lib.clblasNoTrans, lib.clblasNonUnit,
+                    M, 256, 1.0, A, 0, M, Y2, 0, M)
+    assert torch.equal(Y, Y2)
     assert lib.device_fault() == 0
 
 

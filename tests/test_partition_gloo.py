@@ -70,6 +70,20 @@ def _worker(rank, world, port, q):
         st = partition.trsm_rhs_sharded("d", Lower, NoTrans, NonUnit, n, j1 - j0, 1.0, A, n, Bl, n, root=0, trsm_fn=_oracle_trsm)
         X = Bl.numpy().reshape(j1 - j0, n).T if j1 > j0 else np.zeros((n, 0))
         results["trsm"] = (st, bool(np.allclose(T @ X, Bf[:, j0:j1], atol=1e-10)), True)
+        # pipelined panels (3 column panels of A, broadcast in substitution order), both triangles, alpha != 1
+        from oracle import Upper
+        for name, uplo, Tm in (("trsm_panels_lower", Lower, T), ("trsm_panels_upper", Upper, T.T.copy())):
+            n2 = 300
+            T2 = np.tril(g.uniform(-1, 1, (n2, n2)) / n2) + np.diag(g.uniform(1, 2, n2))
+            T2 = T2 if uplo == Lower else T2.T.copy()
+            B2 = g.standard_normal((n2, nrhs))
+            stored = T2.ravel(order="F").copy()
+            A2 = torch.from_numpy(stored.copy() if rank == 0 else np.zeros(n2 * n2))
+            Bl2 = torch.from_numpy(np.asfortranarray(B2[:, j0:j1]).ravel(order="F").copy())
+            st = partition.trsm_rhs_sharded("d", uplo, NoTrans, NonUnit, n2, j1 - j0, -2.0, A2, n2, Bl2, n2, root=0, panels=3,
+                                            trsm_fn=_oracle_trsm, gemm_fn=_oracle_gemm)
+            X2 = Bl2.numpy().reshape(j1 - j0, n2).T if j1 > j0 else np.zeros((n2, 0))
+            results[name] = (st, bool(np.allclose(T2 @ X2, -2.0 * B2[:, j0:j1], atol=1e-9)), bool(np.array_equal(A2.numpy(), stored)))
         q.put((rank, results))
     finally:
         dist.destroy_process_group()
@@ -89,7 +103,7 @@ def test_two_rank_partition_over_gloo():
         assert p.exitcode == 0
     assert sorted(r for r, _ in out) == [0, 1]
     for rank, results in out:
-        assert len(results) == 5
+        assert len(results) == 7
         for name, (st, ok, a_ok) in results.items():
             assert st == 0 and ok and a_ok, (rank, name, st, ok, a_ok)
 
