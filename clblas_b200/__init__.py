@@ -78,7 +78,8 @@ def _load() -> ctypes.CDLL:
     lib = ctypes.CDLL(LIB_PATH)
     sz, u, i, vp = ctypes.c_size_t, ctypes.c_uint, ctypes.c_int, ctypes.c_void_p
     pvp = ctypes.POINTER(ctypes.c_void_p)
-    for name, ft in (("clblasSgemm", ctypes.c_float), ("clblasDgemm", ctypes.c_double)):
+    for name, ft in (("clblasSgemm", ctypes.c_float), ("clblasDgemm", ctypes.c_double),
+                     ("clblasB200SgemmHost", ctypes.c_float), ("clblasB200DgemmHost", ctypes.c_double)):
         f = getattr(lib, name)
         f.argtypes = [i, i, i, sz, sz, sz, ft, vp, sz, sz, vp, sz, sz, ft, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
@@ -159,7 +160,7 @@ EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
            "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
-           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm"] + MATRIX_HELPERS
+           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost"] + MATRIX_HELPERS
 
 
 def _ptr(x) -> Optional[int]:
@@ -233,6 +234,37 @@ def clblasDgemm(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ld
                 queues=None, wait=None, events=None) -> int:
     return _gemm(lib.clblasDgemm, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta,
                  C, offC, ldc, queues, wait, events)
+
+
+def _host_addr(x) -> Optional[int]:
+    """Address of a host matrix: a numpy array, a CPU torch tensor or a raw integer."""
+    if x is None or isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        if getattr(x, "is_cuda", False):
+            raise TypeError("host GEMM takes host memory; use clblasSgemm / clblasDgemm for device tensors")
+        return x.data_ptr()
+    return x.ctypes.data
+
+
+def _gemm_host(fn, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, queues, wait, events):
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return fn(order, transA, transB, M, N, K, alpha, _host_addr(A), offA, lda, _host_addr(B), offB, ldb, beta,
+              _host_addr(C), offC, ldc, nq, q, nw, w, e)
+
+
+def clblasB200SgemmHost(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                        queues=None, wait=None, events=None) -> int:
+    """float GEMM on HOST matrices (numpy arrays or CPU tensors, pinned for speed): uploads, products and downloads
+    overlap.  The result is in C once the stream (default: torch's current stream) has completed."""
+    return _gemm_host(lib.clblasB200SgemmHost, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta,
+                      C, offC, ldc, queues, wait, events)
+
+
+def clblasB200DgemmHost(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                        queues=None, wait=None, events=None) -> int:
+    return _gemm_host(lib.clblasB200DgemmHost, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta,
+                      C, offC, ldc, queues, wait, events)
 
 
 def _trsm(fn, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, queues, wait, events):

@@ -210,6 +210,50 @@ clblasStatus cgemm_entry(clblasOrder order, clblasTranspose transA, clblasTransp
     return record_out(s, events);
 }
 
+// Leading-dimension check of checkMatrixSizes for a matrix in host memory (no allocation extent to compare with).
+clblasStatus check_host_matrix(clblasOrder order, clblasTranspose trans, size_t rows, size_t cols, size_t ld, ErrSet e)
+{
+    if (rows == 0 || cols == 0) return clblasInvalidDim;
+    const bool tra = (order == clblasRowMajor && trans != clblasNoTrans) || (order == clblasColumnMajor && trans == clblasNoTrans);
+    if (ld < (tra ? rows : cols)) return pick(e, clblasInvalidLeadDimA, clblasInvalidLeadDimB, clblasInvalidLeadDimC);
+    return clblasSuccess;
+}
+
+// GEMM on host matrices: the checks of gemm_entry in the same order, then the pipelined upload / multiply / download.
+template <typename T>
+clblasStatus gemm_host_entry(clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+                             size_t M, size_t N, size_t K, T alpha,
+                             const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb,
+                             T beta, void* C, size_t offC, size_t ldc,
+                             unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)transA > 2u || (unsigned)transB > 2u) return clblasInvalidValue;
+    clblasStatus st;
+    if (K != 0) {
+        if ((st = check_host_matrix(order, transA, M, K, lda, SET_A)) != clblasSuccess) return st;
+        if ((st = check_host_matrix(order, transB, K, N, ldb, SET_B)) != clblasSuccess) return st;
+    }
+    if ((st = check_host_matrix(order, clblasNoTrans, M, N, ldc, SET_C)) != clblasSuccess) return st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    const T* a = static_cast<const T*>(A) + offA;
+    const T* b = static_cast<const T*>(B) + offB;
+    T* c = static_cast<T*>(C) + offC;
+    const bool ta = transA != clblasNoTrans, tb = transB != clblasNoTrans;
+    cudaError_t e;
+    if (order == clblasColumnMajor) e = gemm_host_colmajor<T>(ta, tb, M, N, K, alpha, a, lda, b, ldb, beta, c, ldc, s);
+    else                            e = gemm_host_colmajor<T>(tb, ta, N, M, K, alpha, b, ldb, a, lda, beta, c, ldc, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 template <typename T>
 clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
                         size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda,
@@ -479,6 +523,7 @@ clblasStatus clblasSetup(void)
 
 void clblasTeardown(void)
 {
+    host_pipeline_release();
     trsm_release_workspaces();
     g_initialized.store(0);
 }
@@ -617,6 +662,24 @@ clblasStatus clblasZtrsm(clblasOrder order, clblasSide side, clblasUplo uplo, cl
 {
     return ctrsm_entry<double>(order, side, uplo, transA, diag, M, N, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb,
                                nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasB200SgemmHost(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                                 float alpha, const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb,
+                                 float beta, void* C, size_t offC, size_t ldc, unsigned nq, clblasQueue* queues,
+                                 unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return gemm_host_entry<float>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                                  nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasB200DgemmHost(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                                 double alpha, const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb,
+                                 double beta, void* C, size_t offC, size_t ldc, unsigned nq, clblasQueue* queues,
+                                 unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return gemm_host_entry<double>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                                   nq, queues, nev, wait, events);
 }
 
 clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,

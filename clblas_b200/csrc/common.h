@@ -101,6 +101,12 @@ template <typename R>
 cudaError_t ctrsm_colmajor(bool right, bool lower, int op, bool unit, size_t M, size_t N, R ar, R ai,
                            const R* A, size_t lda, R* B, size_t ldb, cudaStream_t s);
 
+// GEMM on host matrices with uploads, products and downloads overlapped (host_gemm.cu); ordered on `user`.
+template <typename T>
+cudaError_t gemm_host_colmajor(bool ta, bool tb, size_t M, size_t N, size_t K, T alpha, const T* hA, size_t lda,
+                               const T* hB, size_t ldb, T beta, T* hC, size_t ldc, cudaStream_t user);
+void host_pipeline_release();
+
 // Blocked triangular solve on a column-major problem (B overwritten by X).
 template <typename T>
 cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,

@@ -1,0 +1,206 @@
+// GEMM on HOST matrices: clblasB200SgemmHost / clblasB200DgemmHost.
+//
+// What a clBLAS program does around clblasDgemm -- clEnqueueWriteBuffer of A, B and C, the call,
+// clEnqueueReadBuffer of C (src/samples/example_sgemm.c:118-160; src/client/clfunc_xgemm.hpp
+// initialize_gpu_buffer / read_gpu_buffer) -- serialises PCIe and the GPU.  This entry point takes the same
+// argument list with host pointers and overlaps the three: the problem is cut into column blocks of C and
+// K-slabs; a copy stream uploads the pieces in the order the products need them (slab s of A and of B's
+// block j, C's block j once), the compute stream multiplies block (j, s) as soon as its pieces have
+// landed (beta on the first slab, 1 afterwards: the reference's split-K accumulation,
+// src/library/blas/specialCases/GemmSpecialCases.cpp:127-191), and a third stream downloads block j of C
+// while later blocks are still being multiplied.  Operands are laid out on the device with aligned leading
+// dimensions, so every product takes the TMA kernels whatever the host leading dimensions are.
+// Pinned host memory makes the copies asynchronous; pageable memory works but is staged by the driver.
+#include "common.h"
+
+#include <algorithm>
+#include <mutex>
+#include <vector>
+
+namespace cb200 {
+
+namespace {
+
+struct HostPipe {
+    std::mutex mu;
+    cudaStream_t in = nullptr, cmp = nullptr, out = nullptr;
+    std::vector<cudaEvent_t> events;
+};
+HostPipe g_pipe[64];
+
+cudaError_t pipe_for_current_device(HostPipe** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    HostPipe& p = g_pipe[dev];
+    static std::mutex create_mu;
+    std::lock_guard<std::mutex> lock(create_mu);
+    if (p.in == nullptr) {
+        if ((e = cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&p.cmp, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking)) != cudaSuccess) return e;
+    }
+    *out = &p;
+    return cudaSuccess;
+}
+
+cudaError_t event_at(HostPipe& p, size_t i, cudaEvent_t* ev)
+{
+    while (p.events.size() <= i) {
+        cudaEvent_t e;
+        cudaError_t err = cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+        if (err != cudaSuccess) return err;
+        p.events.push_back(e);
+    }
+    *ev = p.events[i];
+    return cudaSuccess;
+}
+
+size_t round_up(size_t v, size_t q) { return (v + q - 1) / q * q; }
+
+template <typename T>
+cudaError_t copy2d(T* dst, size_t ldd, const T* src, size_t lds, size_t rows, size_t cols, cudaMemcpyKind kind, cudaStream_t s)
+{
+    if (rows == 0 || cols == 0) return cudaSuccess;
+    if (ldd == rows && lds == rows) return cudaMemcpyAsync(dst, src, rows * cols * sizeof(T), kind, s);
+    return cudaMemcpy2DAsync(dst, ldd * sizeof(T), src, lds * sizeof(T), rows * sizeof(T), cols, kind, s);
+}
+
+#define CK(x) do { e = (x); if (e != cudaSuccess) goto done; } while (0)
+
+}  // namespace
+
+// Column-major problem, host pointers already offset.  Work is ordered after what `user` holds at the time
+// of the call, and `user` waits for the last download: the caller synchronises `user` (or an event recorded
+// on it) before reading C.
+template <typename T>
+cudaError_t gemm_host_colmajor(bool ta, bool tb, size_t M, size_t N, size_t K, T alpha, const T* hA, size_t lda,
+                               const T* hB, size_t ldb, T beta, T* hC, size_t ldc, cudaStream_t user)
+{
+    if (M == 0 || N == 0) return cudaSuccess;
+    const bool product = (K != 0 && alpha != T(0));
+    constexpr size_t Q = 16 / sizeof(T);
+    // stored shapes (rows = contiguous direction)
+    const size_t a_rows = ta ? K : M, a_cols = ta ? M : K;
+    const size_t b_rows = tb ? N : K, b_cols = tb ? K : N;
+    const size_t dlda = round_up(std::max<size_t>(a_rows, 1), Q), dldb = round_up(std::max<size_t>(b_rows, 1), Q), dldc = round_up(M, Q);
+    const size_t a_elems = product ? dlda * a_cols : 0, b_elems = product ? dldb * b_cols : 0, c_elems = dldc * N;
+
+    // column blocks of C: wide enough for several full waves of tiles; K-slabs: a product can start after 1/ns of A
+    const size_t rows128 = (M + 127) / 128;
+    size_t w = round_up(std::max<size_t>((size_t)148 * 7 / std::max<size_t>(rows128, 1), 1) * 128, 128);   // ~7 waves per product
+    w = std::min(std::max<size_t>(w, 512), round_up(N, 128));
+    const size_t nb = (N + w - 1) / w;
+    const size_t ns = !product ? 1 : K >= 8192 ? 4 : K >= 2048 ? 2 : 1;
+    const size_t kslab = round_up((K + ns - 1) / ns, 64);
+
+    // One block and one slab leave nothing to overlap: everything goes on the caller's stream, without events.
+    const bool single = (nb == 1 && ns == 1);
+    HostPipe* pp = nullptr;
+    cudaError_t e = pipe_for_current_device(&pp);
+    if (e != cudaSuccess) return e;
+    std::unique_lock<std::mutex> lock(pp->mu, std::defer_lock);
+    if (!single) lock.lock();                     // one pipelined call per device is enqueued at a time
+    HostPipe& p = *pp;
+    const cudaStream_t s_in = single ? user : p.in, s_cmp = single ? user : p.cmp, s_out = single ? user : p.out;
+
+    T* ws = nullptr;
+    e = ws_alloc(reinterpret_cast<void**>(&ws), (round_up(a_elems, 64) + round_up(b_elems, 64) + c_elems) * sizeof(T) + 256, user);
+    if (e != cudaSuccess) return e;
+    T* dA = ws;
+    T* dB = dA + round_up(a_elems, 64);
+    T* dC = dB + round_up(b_elems, 64);
+
+    cudaEvent_t ev_start, ev;
+    size_t next_event = 0;
+    if (!single) {
+        CK(event_at(p, next_event++, &ev_start));
+        CK(cudaEventRecord(ev_start, user));
+        CK(cudaStreamWaitEvent(s_in, ev_start, 0));
+        CK(cudaStreamWaitEvent(s_cmp, ev_start, 0));
+        CK(cudaStreamWaitEvent(s_out, ev_start, 0));
+    }
+
+    for (size_t j = 0; j < nb; j++) {
+        const size_t j0 = j * w, wj = std::min(w, N - j0);
+        for (size_t s = 0; s < ns; s++) {
+            const size_t k0 = std::min(s * kslab, K), kw = std::min(kslab, K - k0);
+            if (product && kw == 0) continue;
+            // ---- uploads of what product (j, s) needs and nothing has brought yet
+            if (product && j == 0) {
+                if (ta) CK(copy2d(dA + k0, dlda, hA + k0, lda, kw, M, cudaMemcpyHostToDevice, s_in));            // rows k0.. of the K x M matrix
+                else    CK(copy2d(dA + k0 * dlda, dlda, hA + k0 * lda, lda, M, kw, cudaMemcpyHostToDevice, s_in)); // columns k0.. of M x K
+            }
+            if (product) {
+                if (tb) CK(copy2d(dB + j0 + k0 * dldb, dldb, hB + j0 + k0 * ldb, ldb, wj, kw, cudaMemcpyHostToDevice, s_in));  // N x K stored
+                else    CK(copy2d(dB + k0 + j0 * dldb, dldb, hB + k0 + j0 * ldb, ldb, kw, wj, cudaMemcpyHostToDevice, s_in));  // K x N stored
+            }
+            if (s == 0 && beta != T(0))
+                CK(copy2d(dC + j0 * dldc, dldc, hC + j0 * ldc, ldc, M, wj, cudaMemcpyHostToDevice, s_in));
+            if (!single) {
+                CK(event_at(p, next_event++, &ev));
+                CK(cudaEventRecord(ev, s_in));
+                CK(cudaStreamWaitEvent(s_cmp, ev, 0));
+            }
+            // ---- the product of this block and slab
+            GemmProblem<T> g;
+            g.ta = ta; g.tb = tb; g.M = M; g.N = wj; g.K = product ? kw : 0;
+            g.alpha = alpha; g.beta = (s == 0) ? beta : T(1);
+            g.A = ta ? dA + k0 : dA + k0 * dlda; g.lda = dlda;
+            g.B = tb ? dB + j0 + k0 * dldb : dB + k0 + j0 * dldb; g.ldb = dldb;
+            g.C = dC + j0 * dldc; g.ldc = dldc;
+            CK(gemm_colmajor<T>(g, s_cmp));
+        }
+        // ---- download of block j, behind its last product
+        if (!single) {
+            CK(event_at(p, next_event++, &ev));
+            CK(cudaEventRecord(ev, s_cmp));
+            CK(cudaStreamWaitEvent(s_out, ev, 0));
+        }
+        CK(copy2d(hC + j0 * ldc, ldc, dC + j0 * dldc, dldc, M, wj, cudaMemcpyDeviceToHost, s_out));
+    }
+    if (!single) {
+        CK(event_at(p, next_event++, &ev));
+        CK(cudaEventRecord(ev, s_out));
+        CK(cudaStreamWaitEvent(user, ev, 0));
+    }
+    // the copy stream is done before the last product; the compute stream before the last download
+done:
+    if (e != cudaSuccess && !single) {
+        // bring the helper streams to rest before the workspace goes back to the pool
+        cudaStreamSynchronize(p.in); cudaStreamSynchronize(p.cmp); cudaStreamSynchronize(p.out);
+    }
+    const cudaError_t e2 = ws_free(ws, user);
+    return e != cudaSuccess ? e : e2;
+}
+
+#undef CK
+
+void host_pipeline_release()
+{
+    for (int d = 0; d < 64; d++) {
+        HostPipe& p = g_pipe[d];
+        std::lock_guard<std::mutex> lock(p.mu);
+        if (p.in == nullptr && p.events.empty()) continue;
+        int cur = 0;
+        cudaGetDevice(&cur);
+        cudaSetDevice(d);
+        for (cudaEvent_t ev : p.events) cudaEventDestroy(ev);
+        p.events.clear();
+        if (p.in) cudaStreamDestroy(p.in);
+        if (p.cmp) cudaStreamDestroy(p.cmp);
+        if (p.out) cudaStreamDestroy(p.out);
+        p.in = p.cmp = p.out = nullptr;
+        cudaSetDevice(cur);
+    }
+    cudaGetLastError();
+}
+
+template cudaError_t gemm_host_colmajor<float>(bool, bool, size_t, size_t, size_t, float, const float*, size_t, const float*, size_t,
+                                               float, float*, size_t, cudaStream_t);
+template cudaError_t gemm_host_colmajor<double>(bool, bool, size_t, size_t, size_t, double, const double*, size_t, const double*,
+                                                size_t, double, double*, size_t, cudaStream_t);
+
+}  // namespace cb200

@@ -362,6 +362,37 @@ const char* clblasB200LastGemmKernel(void);
  * src/library/blas/impl.c:81-129).  Returns the previous value. */
 int clblasB200SetGemmPath(int path);
 
+/* ---- GEMM on HOST matrices (no single counterpart in the reference: it is what a clBLAS program does with
+ *      clEnqueueWriteBuffer x3 + clblasXgemm + clEnqueueReadBuffer, src/samples/example_sgemm.c:118-160, done as one
+ *      call).  Same argument list as clblasSgemm / clblasDgemm, but A, B and C are HOST pointers (pinned memory for
+ *      asynchronous copies; pageable memory works, staged by the driver).  Uploads, products and downloads overlap:
+ *      the problem is cut into column blocks of C and K-slabs that travel and multiply in a pipeline on the
+ *      library's own streams.  The work starts after what commandQueues[0] holds and the wait list; the result is
+ *      in host C once commandQueues[0] (or events[0]) has completed.  Same checks and status codes as the device
+ *      routines, without the memory-extent checks.  Device memory for the three matrices comes from the
+ *      library's pool (clblasOutOfResources when they do not fit). */
+clblasStatus clblasB200SgemmHost(
+    clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+    size_t M, size_t N, size_t K,
+    float alpha,
+    const void* A, size_t offA, size_t lda,
+    const void* B, size_t offB, size_t ldb,
+    float beta,
+    void* C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasB200DgemmHost(
+    clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+    size_t M, size_t N, size_t K,
+    double alpha,
+    const void* A, size_t offA, size_t lda,
+    const void* B, size_t offB, size_t ldb,
+    double beta,
+    void* C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- matrix helpers: replace clblasMatrixSizeInfo, clblasCreateMatrix*, clblas{Write,Read,Copy}{Sub,}Matrix{,Async}
  *      and clblasFill{Vector,SubMatrix,Matrix}{,Async} (src/clBLAS.h:9665-10238; src/library/blas/matrix.c, fill.cc).
  *      Same argument lists; `command_queue` is ONE cudaStream_t; host pointers are plain host memory (pinned memory
