@@ -11,9 +11,13 @@
 // while later blocks are still being multiplied.  Operands are laid out on the device with aligned leading
 // dimensions, so every product takes the TMA kernels whatever the host leading dimensions are.
 // Pinned host memory makes the copies asynchronous; pageable memory works but is staged by the driver.
+// Tuning knobs (environment, read per call): CLBLAS_B200_HOST_W = width of the column blocks,
+// CLBLAS_B200_HOST_NS = number of K-slabs.  On 8192^3 FP64 the defaults (2048, 4) and (2048, 2) were the best
+// of eight settings; the first column block is upload-bound whatever the setting because it needs all of A.
 #include "common.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -92,8 +96,10 @@ cudaError_t gemm_host_colmajor(bool ta, bool tb, size_t M, size_t N, size_t K, T
     const size_t rows128 = (M + 127) / 128;
     size_t w = round_up(std::max<size_t>((size_t)148 * 7 / std::max<size_t>(rows128, 1), 1) * 128, 128);   // ~7 waves per product
     w = std::min(std::max<size_t>(w, 512), round_up(N, 128));
+    size_t ns = !product ? 1 : K >= 8192 ? 4 : K >= 2048 ? 2 : 1;
+    if (const char* v = getenv("CLBLAS_B200_HOST_W")) { const size_t x = strtoull(v, nullptr, 10); if (x) w = std::min(round_up(x, 128), round_up(N, 128)); }
+    if (const char* v = getenv("CLBLAS_B200_HOST_NS")) { const size_t x = strtoull(v, nullptr, 10); if (x && product) ns = x; }
     const size_t nb = (N + w - 1) / w;
-    const size_t ns = !product ? 1 : K >= 8192 ? 4 : K >= 2048 ? 2 : 1;
     const size_t kslab = round_up((K + ns - 1) / ns, 64);
 
     // One block and one slab leave nothing to overlap: everything goes on the caller's stream, without events.
