@@ -31,6 +31,8 @@
 #include "common.h"
 #include "tma_pipeline.cuh"
 
+#include <cstdlib>
+
 namespace cb200 {
 
 namespace {
@@ -297,6 +299,187 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
     return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------
+// N/T kernel with a 16 x 8 register tile: 128 x 128 tile of C, 128 threads (8 along M x 16 along N),
+// both operands M/N-contiguous (the layout every large SGEMM is repacked into).
+//
+// Why a second kernel: with the 8 x 8 register tile above, a CTA moves 16 KB from shared memory to
+// registers per k-slab row (256 threads x 16 floats), which at 128 B per cycle costs as many cycles as
+// the 128 x 128 FMAs themselves -- the profile shows the shared-memory pipe at 83 % next to the FMA
+// pipe at 82 %.  A 16 x 8 register tile needs 24 floats per 128 FMAs instead of 16 per 64: 12 KB per
+// k row and CTA, 75 % of the FMA time, which leaves the FMA pipe as the only limiter.  The 64 packed
+// accumulators take 128 registers, so the budget is 255 registers and two CTAs (eight warps) per SM.
+constexpr int T16_THREADS = 128;
+constexpr int T16_STAGES = 3;
+constexpr int T16_REFILL_KC = 3;        // quarter of the slab (0..3) in which the slot freed one slab earlier is refilled
+constexpr int T16_STAGE_BYTES = (128 + 128) * BK * 4;          // 32 KB
+constexpr int T16_SMEM = T16_STAGES * T16_STAGE_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(T16_THREADS, 2)
+sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                     float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
+                     unsigned tilesM, unsigned tilesN, unsigned wave, int tri)
+{
+    constexpr int BN = 128;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + T16_STAGES * T16_STAGE_BYTES);
+    uint64_t* empty = full + T16_STAGES;
+
+    unsigned tm, tn;
+    {
+        const unsigned per_group = GROUP_M * tilesN;
+        const unsigned g = blockIdx.x / per_group;
+        const unsigned first = g * GROUP_M;
+        const unsigned rows = min((unsigned)GROUP_M, tilesM - first);
+        const unsigned r = blockIdx.x - g * per_group;
+        tm = first + r % rows;
+        tn = r / rows;
+    }
+    const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
+    if (tri_tile_outside(tri, m0, BM, n0, BN)) return;
+    if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
+    const int nk = (int)((K + BK - 1) / BK);
+    const bool reverse_k = wave != 0 && ((blockIdx.x / wave) & 1);
+    const int lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T16_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], T16_THREADS / 32);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int kt) {
+        const int s = kt % T16_STAGES;
+        unsigned char* sa = smem + s * T16_STAGE_BYTES;
+        unsigned char* sb = sa + A_BYTES;
+        mbar_expect_tx(&full[s], T16_STAGE_BYTES);
+        const int k0 = (reverse_k ? nk - 1 - kt : kt) * BK;
+        tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
+        tma_load_2d(sb, &mapB, (int)n0, k0, &full[s]);
+    };
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&mapA);
+        tma_prefetch_descriptor(&mapB);
+        for (int kt = 0; kt < T16_STAGES - 1 && kt < nk; kt++) issue(kt);
+    }
+
+    const int tx = threadIdx.x % 8, ty = threadIdx.x / 8;
+    // rows tx*4 + 32*g + (0..3), g < 4; columns ty*4 + 64*h + (0..3), h < 2
+    // acc2[2*g + q][4*h + c] = rows (tx*4 + 32*g + 2*q, +1) of column ty*4 + 64*h + c
+    unsigned long long acc2[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc2[i][j] = 0ull;
+
+    const int offA = tx * 16, offB = ty * 16;
+    bool alive = true;
+    for (int kt = 0; kt < nk; kt++) {
+        const int s = kt % T16_STAGES;
+        if (!mbar_wait(&full[s], (kt / T16_STAGES) & 1)) break;
+        const unsigned char* sa = smem + s * T16_STAGE_BYTES + offA;
+        const unsigned char* sb = smem + s * T16_STAGE_BYTES + A_BYTES + offB;
+        // Fully unrolled: a trip count of eight k rows keeps the code in the instruction cache but costs 3 % at
+        // 8192^3 (fragment loads are not carried across trips), measured.
+#pragma unroll
+        for (int kc = 0; kc < BK / 8; kc++) {
+            // Refill the slot consumed during the previous slab, in the last quarter of this one (by then even a
+            // lagging warp has released it) and from a different warp every slab, so that the wait, when there
+            // is one, does not always hold back the same quarter of the CTA.  Measured at 8192^3: first quarter /
+            // thread 0: 61.7, last quarter / thread 0: 63.3, last quarter / rotating: 63.5 TFLOP/s.
+            if (kc == T16_REFILL_KC && threadIdx.x == 32 * (kt & 3) && kt + T16_STAGES - 1 < nk) {
+                if (kt >= 1) alive = mbar_wait(&empty[(kt - 1) % T16_STAGES], ((kt - 1) / T16_STAGES) & 1);
+                if (alive) issue(kt + T16_STAGES - 1);
+            }
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                unsigned long long a2[8], bd[8];
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    // 16 bytes = rows (0,1) and (2,3) of the group: already the two packed operands
+                    const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(sa + (kc * 8 + q) * 512 + g * 128);
+                    a2[2 * g] = v.x; a2[2 * g + 1] = v.y;
+                }
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const float4 v = *reinterpret_cast<const float4*>(sb + (kc * 8 + q) * 512 + h * 256);
+                    bd[4 * h + 0] = pack2(v.x, v.x); bd[4 * h + 1] = pack2(v.y, v.y);
+                    bd[4 * h + 2] = pack2(v.z, v.z); bd[4 * h + 3] = pack2(v.w, v.w);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc2[i][j] = ffma2(a2[i], bd[j], acc2[i][j]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+
+    // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
+    const bool useC = (beta != 0.f);
+    const bool vec = tri == TRI_FULL && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const size_t col = n0 + ty * 4 + (j & 3) + 64 * (j >> 2);
+        if (col >= N) continue;
+        float* cc = C + col * ldc;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const size_t row = m0 + tx * 4 + 32 * g;
+            float v[4];
+            unpack2(acc2[2 * g][j], v[0], v[1]);
+            unpack2(acc2[2 * g + 1][j], v[2], v[3]);
+            if (vec && row + 3 < M) {
+                float4 r;
+                r.x = alpha * v[0]; r.y = alpha * v[1]; r.z = alpha * v[2]; r.w = alpha * v[3];
+                if (useC) {
+                    const float4 o = *reinterpret_cast<const float4*>(cc + row);
+                    r.x = fmaf(beta, o.x, r.x); r.y = fmaf(beta, o.y, r.y);
+                    r.z = fmaf(beta, o.z, r.z); r.w = fmaf(beta, o.w, r.w);
+                }
+                *reinterpret_cast<float4*>(cc + row) = r;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    if (row + e < M && !tri_masked(tri, row + e, col)) {
+                        float r = alpha * v[e];
+                        if (useC) r = fmaf(beta, cc[row + e], r);
+                        cc[row + e] = r;
+                    }
+                }
+            }
+        }
+    }
+}
+
+cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s)
+{
+    void* enc = get_tensor_map_encoder();
+    CUtensorMap mapA, mapB;
+    if (!make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.A, p.M, p.K, p.lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return cudaErrorNotSupported;
+    if (!make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.N, p.K, p.ldb, 128, BK, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return cudaErrorNotSupported;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(sgemm_nt_16x8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T16_SMEM);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128;
+    sgemm_nt_16x8_kernel<<<(unsigned)(tilesM * tilesN), T16_THREADS, T16_SMEM, s>>>(
+        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 2), p.tri);
+    count_launch();
+    return cudaGetLastError();
+}
+
 template <int BN, int STAGES, int MIN_CTAS>
 cudaError_t launch_any(const GemmProblem<float>& p, cudaStream_t s)
 {
@@ -328,6 +511,12 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     // A K-contiguous operand is fetched 4 k at a time (32 fragment registers on top of the
     // accumulators), which the two-CTA budget of 128 registers holds only for B; measured at 8192^3
     // with packed FMAs: N/T 60.2 (two CTAs) vs 53.6 TFLOP/s (one), N/N 48.6 vs 47.2.
+    // The 16 x 8 register-tile kernel has four warps per CTA: it needs both of an SM's CTA slots filled for
+    // several waves and a K loop long enough to amortise its per-thread epilogue.  Measured against the 8 x 8
+    // kernel: 8192^3 63.5 vs 57.8-60.2, 3008 x 4100 x 1537 48.6 vs 47.2, but 1536^3 (144 tiles) 38.3 vs 50.9 and
+    // 4096 x 4096 x 512 48.7 vs 53.9 TFLOP/s.
+    if (!p.ta && p.tb && tiles128 >= (size_t)sm_count() * 4 && p.K >= 1024 && getenv("CLBLAS_B200_SGEMM_8X8") == nullptr)
+        return launch_nt_16x8(p, s);
     if (!p.ta) return launch_any<128, 3, 2>(p, s);
     return launch_any<128, 5, 1>(p, s);
 }
