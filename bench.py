@@ -195,6 +195,11 @@ class TrsmWorkload(Workload):
         return partition.trsm_rhs_sharded("d", cb.clblasLower, cb.clblasNoTrans, cb.clblasNonUnit, self.M, nl, self.alpha,
                                           A, self.M, B, self.M, root=0)
 
+    def call_host(self, cb, bufs):
+        A, B = bufs
+        return cb.clblasB200DtrsmHost(cb.clblasColumnMajor, cb.clblasLeft, cb.clblasLower, cb.clblasNoTrans, cb.clblasNonUnit,
+                                      self.M, self.N, self.alpha, A, 0, self.M, B, 0, self.M)
+
     def config(self, world):
         return {"workload": f"{self.name}: {self.desc}", "M": self.M, "N": self.N, "alpha": self.alpha,
                 "lda": self.M, "ldb": self.M}
@@ -538,7 +543,8 @@ def main():
             ems = float(t.item())
         e2e = {"value": wl.flops(world) / (ems / n_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": n_e2e,
-               "api": ("clblasB200%sgemmHost (pipelined copies and products)" % wl.prec.upper()) if host_call is not None
+               "api": ("clblasB200%s%sHost (pipelined copies and products)" % (getattr(wl, "prec", "d").upper(), "trsm" if wl.name == "cfg4" else "gemm"))
+                      if host_call is not None
                       else "pinned copies + device entry point on one stream"}
         del host, dev_bufs, out_host
 

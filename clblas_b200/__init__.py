@@ -85,6 +85,7 @@ def _load() -> ctypes.CDLL:
         f.restype = i
     for name, ft in (("clblasStrsm", ctypes.c_float), ("clblasDtrsm", ctypes.c_double),
                      ("clblasB200DtrsmNoAlloc", ctypes.c_double), ("clblasStrmm", ctypes.c_float),
+                     ("clblasB200StrsmHost", ctypes.c_float), ("clblasB200DtrsmHost", ctypes.c_double),
                      ("clblasDtrmm", ctypes.c_double)):
         f = getattr(lib, name)
         f.argtypes = [i, i, i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, u, pvp, u, pvp, pvp]
@@ -160,7 +161,7 @@ EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
            "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
-           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost"] + MATRIX_HELPERS
+           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost", "clblasB200StrsmHost", "clblasB200DtrsmHost"] + MATRIX_HELPERS
 
 
 def _ptr(x) -> Optional[int]:
@@ -265,6 +266,24 @@ def clblasB200DgemmHost(order, transA, transB, M, N, K, alpha, A, offA, lda, B, 
                         queues=None, wait=None, events=None) -> int:
     return _gemm_host(lib.clblasB200DgemmHost, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta,
                       C, offC, ldc, queues, wait, events)
+
+
+def _trsm_host(fn, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, queues, wait, events):
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return fn(order, side, uplo, transA, diag, M, N, alpha, _host_addr(A), offA, lda, _host_addr(B), offB, ldb, nq, q, nw, w, e)
+
+
+def clblasB200StrsmHost(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                        queues=None, wait=None, events=None) -> int:
+    """float TRSM on HOST matrices: blocks of right-hand sides uploaded, solved and downloaded in a pipeline."""
+    return _trsm_host(lib.clblasB200StrsmHost, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                      queues, wait, events)
+
+
+def clblasB200DtrsmHost(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                        queues=None, wait=None, events=None) -> int:
+    return _trsm_host(lib.clblasB200DtrsmHost, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                      queues, wait, events)
 
 
 def _trsm(fn, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, queues, wait, events):

@@ -254,6 +254,38 @@ clblasStatus gemm_host_entry(clblasOrder order, clblasTranspose transA, clblasTr
     return record_out(s, events);
 }
 
+// TRSM on host matrices: the checks of trsm_entry in the same order (without memory extents).
+template <typename T>
+clblasStatus trsm_host_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                             size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda, void* B, size_t offB, size_t ldb,
+                             unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u || (unsigned)transA > 2u || (unsigned)diag > 1u) return clblasInvalidValue;
+    const size_t msize = (side == clblasLeft) ? M : N;
+    if ((st = check_host_matrix(order, transA, msize, msize, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_host_matrix(order, clblasNoTrans, M, N, ldb, SET_B)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = trsm_host_colmajor<T>(right, lower, transA != clblasNoTrans, diag == clblasUnit, M, N, alpha,
+                                          static_cast<const T*>(A) + offA, lda, static_cast<T*>(B) + offB, ldb, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 template <typename T>
 clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
                         size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda,
@@ -680,6 +712,22 @@ clblasStatus clblasB200DgemmHost(clblasOrder order, clblasTranspose transA, clbl
 {
     return gemm_host_entry<double>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
                                    nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasB200StrsmHost(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                                 size_t M, size_t N, float alpha, const void* A, size_t offA, size_t lda, void* B, size_t offB,
+                                 size_t ldb, unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait,
+                                 clblasEvent* events)
+{
+    return trsm_host_entry<float>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasB200DtrsmHost(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                                 size_t M, size_t N, double alpha, const void* A, size_t offA, size_t lda, void* B, size_t offB,
+                                 size_t ldb, unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait,
+                                 clblasEvent* events)
+{
+    return trsm_host_entry<double>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, nq, queues, nev, wait, events);
 }
 
 clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,

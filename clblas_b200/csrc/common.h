@@ -105,6 +105,9 @@ cudaError_t ctrsm_colmajor(bool right, bool lower, int op, bool unit, size_t M, 
 template <typename T>
 cudaError_t gemm_host_colmajor(bool ta, bool tb, size_t M, size_t N, size_t K, T alpha, const T* hA, size_t lda,
                                const T* hB, size_t ldb, T beta, T* hC, size_t ldc, cudaStream_t user);
+template <typename T>
+cudaError_t trsm_host_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
+                               const T* hA, size_t lda, T* hB, size_t ldb, cudaStream_t user);
 void host_pipeline_release();
 
 // Blocked triangular solve on a column-major problem (B overwritten by X).

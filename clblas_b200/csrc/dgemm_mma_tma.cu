@@ -51,12 +51,15 @@ __device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b)
 __device__ __forceinline__ int perm8(int g) { return 2 * (g & 3) + (g >> 2); }
 
 // TA: A is stored K x M (K contiguous).  TB: B is stored N x K (N contiguous).
-template <bool TA, bool TB, int BN>
+// TRI: compiled-in support for the triangular update (SYRK); without it `tri` is ignored and the epilogue carries
+// no per-entry mask (a run-time mask alone cost 4-13 % on short-K products).
+template <bool TA, bool TB, int BN, bool TRI>
 __global__ void __launch_bounds__(THREADS, 1)
 dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      double* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, double alpha, double beta,
-                     unsigned tilesM, unsigned tilesN, unsigned wave, int tri)
+                     unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg)
 {
+    int tri = TRI ? tri_arg : TRI_FULL;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int STAGE_BYTES = stage_bytes(BN);
@@ -77,8 +80,10 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         tn = r / rows;
     }
     const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
-    if (tri_tile_outside(tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
-    if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
+    if (TRI) {
+        if (tri_tile_outside(tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
+        if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
+    }
     const int nk = (int)((K + BK - 1) / BK);
     // Every other wave of CTAs walks K backwards: it starts on the K range the wave before it
     // finished on, which is what L2 still holds, instead of re-streaming those panels from DRAM.
@@ -176,7 +181,7 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
 #pragma unroll
             for (int mi = 0; mi < 8; mi++) {
                 const size_t row = m0 + wm * 64 + mi * 8 + (TA ? pg : g);
-                if (row >= M || tri_masked(tri, row, col)) continue;
+                if (row >= M || (TRI && tri_masked(tri, row, col))) continue;
                 double r = alpha * acc[mi][ni][e];
                 if (useC) r = fma(beta, cc[row], r);
                 cc[row] = r;
@@ -184,7 +189,7 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         }
 }
 
-template <bool TA, bool TB, int BN>
+template <bool TA, bool TB, int BN, bool TRI>
 cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
 {
     void* enc = get_tensor_map_encoder();
@@ -201,12 +206,12 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(dgemm_mma_tma_kernel<TA, TB, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN));
+        cudaError_t e = cudaFuncSetAttribute(dgemm_mma_tma_kernel<TA, TB, BN, TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN));
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
-    dgemm_mma_tma_kernel<TA, TB, BN><<<(unsigned)(tilesM * tilesN), THREADS, smem_bytes(BN), s>>>(
+    dgemm_mma_tma_kernel<TA, TB, BN, TRI><<<(unsigned)(tilesM * tilesN), THREADS, smem_bytes(BN), s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 1), p.tri);
     count_launch();
     return cudaGetLastError();
@@ -215,10 +220,16 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
 template <int BN>
 cudaError_t launch_t(const GemmProblem<double>& p, cudaStream_t s)
 {
-    if (!p.ta && !p.tb) return launch<false, false, BN>(p, s);
-    if (!p.ta && p.tb) return launch<false, true, BN>(p, s);
-    if (p.ta && !p.tb) return launch<true, false, BN>(p, s);
-    return launch<true, true, BN>(p, s);
+    if (p.tri != TRI_FULL) {
+        if (!p.ta && !p.tb) return launch<false, false, BN, true>(p, s);
+        if (!p.ta && p.tb) return launch<false, true, BN, true>(p, s);
+        if (p.ta && !p.tb) return launch<true, false, BN, true>(p, s);
+        return launch<true, true, BN, true>(p, s);
+    }
+    if (!p.ta && !p.tb) return launch<false, false, BN, false>(p, s);
+    if (!p.ta && p.tb) return launch<false, true, BN, false>(p, s);
+    if (p.ta && !p.tb) return launch<true, false, BN, false>(p, s);
+    return launch<true, true, BN, false>(p, s);
 }
 
 }  // namespace

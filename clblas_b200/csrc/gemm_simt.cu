@@ -30,7 +30,7 @@ __device__ __forceinline__ void lds16(const double* p, double* out)
     out[0] = v.x; out[1] = v.y;
 }
 
-template <typename T, int BM, int BN, int BK, int TM, int TN, bool TA, bool TB>
+template <typename T, int BM, int BN, int BK, int TM, int TN, bool TA, bool TB, bool TRI>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(const GemmProblem<T> p, const unsigned tilesM)
 {
@@ -51,7 +51,7 @@ gemm_simt_kernel(const GemmProblem<T> p, const unsigned tilesM)
     const size_t m0 = (size_t)(blockIdx.x % tilesM) * BM;
     const size_t n0 = (size_t)(blockIdx.x / tilesM) * BN;
     const size_t M = p.M, N = p.N, K = p.K;
-    if (tri_tile_outside(p.tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
+    if (TRI && tri_tile_outside(p.tri, m0, BM, n0, BN)) return;   // triangular update: nothing of this tile is referenced
 
     // ---- loader mapping: f = index along the memory-contiguous direction, s = the strided one
     constexpr int FA = TA ? BK : BM;           // extent of f for A
@@ -145,7 +145,7 @@ gemm_simt_kernel(const GemmProblem<T> p, const unsigned tilesM)
 #pragma unroll
                 for (int jm = 0; jm < V; jm++) {
                     const size_t m = m0 + cm * (BM / CM) + tx * V + jm;
-                    if (m >= M || tri_masked(p.tri, m, n)) continue;
+                    if (m >= M || (TRI && tri_masked(p.tri, m, n))) continue;
                     T* c = p.C + m + n * p.ldc;
                     T r = alpha * acc[cm * V + jm][cn * V + jn];
                     if (useC) r = fma(beta, *c, r);
@@ -172,10 +172,18 @@ cudaError_t launch_cfg(const GemmProblem<T>& p, cudaStream_t s)
     if (tiles > 0x7fffffffULL) return cudaErrorInvalidConfiguration;
     constexpr int NT = (BM / TM) * (BN / TN);
     const dim3 grid((unsigned)tiles), block(NT);
-    if (!p.ta && !p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, false, false><<<grid, block, 0, s>>>(p, (unsigned)tilesM);
-    else if (!p.ta && p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, false, true><<<grid, block, 0, s>>>(p, (unsigned)tilesM);
-    else if (p.ta && !p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, true, false><<<grid, block, 0, s>>>(p, (unsigned)tilesM);
-    else gemm_simt_kernel<T, BM, BN, BK, TM, TN, true, true><<<grid, block, 0, s>>>(p, (unsigned)tilesM);
+    const unsigned tm = (unsigned)tilesM;
+    if (p.tri != TRI_FULL) {
+        if (!p.ta && !p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, false, false, true><<<grid, block, 0, s>>>(p, tm);
+        else if (!p.ta && p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, false, true, true><<<grid, block, 0, s>>>(p, tm);
+        else if (p.ta && !p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, true, false, true><<<grid, block, 0, s>>>(p, tm);
+        else gemm_simt_kernel<T, BM, BN, BK, TM, TN, true, true, true><<<grid, block, 0, s>>>(p, tm);
+    } else {
+        if (!p.ta && !p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, false, false, false><<<grid, block, 0, s>>>(p, tm);
+        else if (!p.ta && p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, false, true, false><<<grid, block, 0, s>>>(p, tm);
+        else if (p.ta && !p.tb) gemm_simt_kernel<T, BM, BN, BK, TM, TN, true, false, false><<<grid, block, 0, s>>>(p, tm);
+        else gemm_simt_kernel<T, BM, BN, BK, TM, TN, true, true, false><<<grid, block, 0, s>>>(p, tm);
+    }
     count_launch();
     return cudaGetLastError();
 }

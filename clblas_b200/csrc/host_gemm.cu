@@ -1,4 +1,4 @@
-// GEMM on HOST matrices: clblasB200SgemmHost / clblasB200DgemmHost.
+// GEMM and TRSM on HOST matrices: clblasB200SgemmHost / clblasB200DgemmHost / clblasB200StrsmHost / clblasB200DtrsmHost.
 //
 // What a clBLAS program does around clblasDgemm -- clEnqueueWriteBuffer of A, B and C, the call,
 // clEnqueueReadBuffer of C (src/samples/example_sgemm.c:118-160; src/client/clfunc_xgemm.hpp
@@ -182,6 +182,90 @@ done:
     return e != cudaSuccess ? e : e2;
 }
 
+// TRSM on host matrices.  The referenced triangle of A goes up first (column panels, so that only the
+// triangle crosses PCIe), then B travels in blocks of right-hand sides -- column blocks for side = Left, row
+// blocks for side = Right -- which are independent systems: block j is solved while block j+1 is uploaded
+// and block j-1 downloaded.
+template <typename T>
+cudaError_t trsm_host_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
+                               const T* hA, size_t lda, T* hB, size_t ldb, cudaStream_t user)
+{
+    if (M == 0 || N == 0) return cudaSuccess;
+    constexpr size_t Q = 16 / sizeof(T);
+    const size_t n = right ? N : M;                    // order of A
+    const size_t other = right ? M : N;                // independent right-hand sides
+    const size_t dlda = round_up(n, Q), dldb = round_up(M, Q);
+    const bool solve = alpha != T(0);
+    const size_t nbt = std::min<size_t>(8, std::max<size_t>(1, other / 4096));
+    const size_t w = round_up((other + nbt - 1) / nbt, 128);
+    const size_t nb = (other + w - 1) / w;
+    const bool single = nb == 1;
+
+    HostPipe* pp = nullptr;
+    cudaError_t e = pipe_for_current_device(&pp);
+    if (e != cudaSuccess) return e;
+    std::unique_lock<std::mutex> lock(pp->mu, std::defer_lock);
+    if (!single) lock.lock();
+    HostPipe& p = *pp;
+    const cudaStream_t s_in = single ? user : p.in, s_cmp = single ? user : p.cmp, s_out = single ? user : p.out;
+
+    const size_t a_elems = solve ? dlda * n : 0;
+    T* ws = nullptr;
+    e = ws_alloc(reinterpret_cast<void**>(&ws), (round_up(a_elems, 64) + dldb * N) * sizeof(T) + 256, user);
+    if (e != cudaSuccess) return e;
+    T* dA = ws;
+    T* dB = ws + round_up(a_elems, 64);
+
+    cudaEvent_t ev;
+    size_t next_event = 0;
+    if (!single) {
+        CK(event_at(p, next_event++, &ev));
+        CK(cudaEventRecord(ev, user));
+        CK(cudaStreamWaitEvent(s_in, ev, 0));
+        CK(cudaStreamWaitEvent(s_cmp, ev, 0));
+        CK(cudaStreamWaitEvent(s_out, ev, 0));
+    }
+    if (solve) {
+        // the referenced triangle, in panels of 1024 columns: rows c0.. (lower) or ..c1 (upper) of each panel
+        for (size_t c0 = 0; c0 < n; c0 += 1024) {
+            const size_t c1 = std::min(n, c0 + 1024);
+            const size_t r0 = lower ? c0 : 0, r1 = lower ? n : c1;
+            CK(copy2d(dA + r0 + c0 * dlda, dlda, hA + r0 + c0 * lda, lda, r1 - r0, c1 - c0, cudaMemcpyHostToDevice, s_in));
+        }
+    }
+    for (size_t j = 0; j < nb; j++) {
+        const size_t j0 = j * w, wj = std::min(w, other - j0);
+        // block j of B: columns j0.. (Left) or rows j0.. (Right)
+        T* db = right ? dB + j0 : dB + j0 * dldb;
+        T* hb = right ? hB + j0 : hB + j0 * ldb;
+        const size_t rows = right ? wj : M, cols = right ? N : wj;
+        if (solve) CK(copy2d(db, dldb, hb, ldb, rows, cols, cudaMemcpyHostToDevice, s_in));
+        if (!single) {
+            CK(event_at(p, next_event++, &ev));
+            CK(cudaEventRecord(ev, s_in));
+            CK(cudaStreamWaitEvent(s_cmp, ev, 0));
+        }
+        CK(trsm_colmajor<T>(right, lower, trans, unit, rows, cols, alpha, dA, dlda, db, dldb, s_cmp));   // alpha == 0: B <- 0
+        if (!single) {
+            CK(event_at(p, next_event++, &ev));
+            CK(cudaEventRecord(ev, s_cmp));
+            CK(cudaStreamWaitEvent(s_out, ev, 0));
+        }
+        CK(copy2d(hb, ldb, db, dldb, rows, cols, cudaMemcpyDeviceToHost, s_out));
+    }
+    if (!single) {
+        CK(event_at(p, next_event++, &ev));
+        CK(cudaEventRecord(ev, s_out));
+        CK(cudaStreamWaitEvent(user, ev, 0));
+    }
+done:
+    if (e != cudaSuccess && !single) {
+        cudaStreamSynchronize(p.in); cudaStreamSynchronize(p.cmp); cudaStreamSynchronize(p.out);
+    }
+    const cudaError_t e2 = ws_free(ws, user);
+    return e != cudaSuccess ? e : e2;
+}
+
 #undef CK
 
 void host_pipeline_release()
@@ -204,6 +288,10 @@ void host_pipeline_release()
     cudaGetLastError();
 }
 
+template cudaError_t trsm_host_colmajor<float>(bool, bool, bool, bool, size_t, size_t, float, const float*, size_t, float*, size_t,
+                                               cudaStream_t);
+template cudaError_t trsm_host_colmajor<double>(bool, bool, bool, bool, size_t, size_t, double, const double*, size_t, double*,
+                                                size_t, cudaStream_t);
 template cudaError_t gemm_host_colmajor<float>(bool, bool, size_t, size_t, size_t, float, const float*, size_t, const float*, size_t,
                                                float, float*, size_t, cudaStream_t);
 template cudaError_t gemm_host_colmajor<double>(bool, bool, size_t, size_t, size_t, double, const double*, size_t, const double*,

@@ -63,12 +63,15 @@ __device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsign
     return d;
 }
 
-template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS>
+// TRI: compiled-in support for the triangular update (SYRK); without it `tri` is ignored and the epilogue carries
+// no per-entry mask.
+template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS, bool TRI>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                      unsigned tilesM, unsigned tilesN, unsigned wave, int tri)
+                      unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg)
 {
+    int tri = TRI ? tri_arg : TRI_FULL;
     constexpr int STAGE_BYTES = stage_bytes(BN);
     constexpr int NJ = BN / 16;                     // columns per thread: 8 or 4
     constexpr int NH = NJ / 4;                      // 4-column groups per thread (64 columns apart)
@@ -90,8 +93,10 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         tn = r / rows;
     }
     const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
-    if (tri_tile_outside(tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
-    if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
+    if (TRI) {
+        if (tri_tile_outside(tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
+        if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
+    }
     const int nk = (int)((K + BK - 1) / BK);
     // Every other wave of CTAs walks K backwards: it starts on the K range the wave before it
     // finished on, which is what L2 still holds, instead of re-streaming those panels from DRAM.
@@ -224,7 +229,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 
     // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
     const bool useC = (beta != 0.f);
-    const bool vec = !TA && tri == TRI_FULL && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
+    const bool vec = !TA && (!TRI || tri == TRI_FULL) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const size_t col = n0 + colB(j);
@@ -247,7 +252,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
                 } else {
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        if (row + e < M && !tri_masked(tri, row + e, col)) {
+                        if (row + e < M && !(TRI && tri_masked(tri, row + e, col))) {
                             float r = alpha * acc[4 * h + e][j];
                             if (useC) r = fmaf(beta, cc[row + e], r);
                             cc[row + e] = r;
@@ -259,7 +264,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const size_t row = m0 + rowA(i);
-                if (row < M && !tri_masked(tri, row, col)) {
+                if (row < M && !(TRI && tri_masked(tri, row, col))) {
                     float r = alpha * acc[i][j];
                     if (useC) r = fmaf(beta, cc[row], r);
                     cc[row] = r;
@@ -269,7 +274,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     }
 }
 
-template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS>
+template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS, bool TRI>
 cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
 {
     void* enc = get_tensor_map_encoder();
@@ -287,13 +292,13 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS>,
+        cudaError_t e = cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
-    sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
+    sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * MIN_CTAS), p.tri);
     count_launch();
     return cudaGetLastError();
@@ -315,11 +320,13 @@ constexpr int T16_REFILL_KC = 3;        // quarter of the slab (0..3) in which t
 constexpr int T16_STAGE_BYTES = (128 + 128) * BK * 4;          // 32 KB
 constexpr int T16_SMEM = T16_STAGES * T16_STAGE_BYTES + 1024 + 256;
 
+template <bool TRI>
 __global__ void __launch_bounds__(T16_THREADS, 2)
 sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                     unsigned tilesM, unsigned tilesN, unsigned wave, int tri)
+                     unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg)
 {
+    int tri = TRI ? tri_arg : TRI_FULL;
     constexpr int BN = 128;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -337,8 +344,10 @@ sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         tn = r / rows;
     }
     const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
-    if (tri_tile_outside(tri, m0, BM, n0, BN)) return;
-    if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
+    if (TRI) {
+        if (tri_tile_outside(tri, m0, BM, n0, BN)) return;
+        if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
+    }
     const int nk = (int)((K + BK - 1) / BK);
     const bool reverse_k = wave != 0 && ((blockIdx.x / wave) & 1);
     const int lane = threadIdx.x % 32;
@@ -422,7 +431,7 @@ sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
 
     // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
     const bool useC = (beta != 0.f);
-    const bool vec = tri == TRI_FULL && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
+    const bool vec = (!TRI || tri == TRI_FULL) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         const size_t col = n0 + ty * 4 + (j & 3) + 64 * (j >> 2);
@@ -446,7 +455,7 @@ sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    if (row + e < M && !tri_masked(tri, row + e, col)) {
+                    if (row + e < M && !(TRI && tri_masked(tri, row + e, col))) {
                         float r = alpha * v[e];
                         if (useC) r = fmaf(beta, cc[row + e], r);
                         cc[row + e] = r;
@@ -457,6 +466,7 @@ sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
 }
 
+template <bool TRI>
 cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s)
 {
     void* enc = get_tensor_map_encoder();
@@ -469,12 +479,12 @@ cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s)
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(sgemm_nt_16x8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T16_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(sgemm_nt_16x8_kernel<TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, T16_SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128;
-    sgemm_nt_16x8_kernel<<<(unsigned)(tilesM * tilesN), T16_THREADS, T16_SMEM, s>>>(
+    sgemm_nt_16x8_kernel<TRI><<<(unsigned)(tilesM * tilesN), T16_THREADS, T16_SMEM, s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 2), p.tri);
     count_launch();
     return cudaGetLastError();
@@ -483,10 +493,16 @@ cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s)
 template <int BN, int STAGES, int MIN_CTAS>
 cudaError_t launch_any(const GemmProblem<float>& p, cudaStream_t s)
 {
-    if (!p.ta && !p.tb) return launch<false, false, BN, STAGES, MIN_CTAS>(p, s);
-    if (!p.ta && p.tb) return launch<false, true, BN, STAGES, MIN_CTAS>(p, s);
-    if (p.ta && !p.tb) return launch<true, false, BN, STAGES, MIN_CTAS>(p, s);
-    return launch<true, true, BN, STAGES, MIN_CTAS>(p, s);
+    if (p.tri != TRI_FULL) {
+        if (!p.ta && !p.tb) return launch<false, false, BN, STAGES, MIN_CTAS, true>(p, s);
+        if (!p.ta && p.tb) return launch<false, true, BN, STAGES, MIN_CTAS, true>(p, s);
+        if (p.ta && !p.tb) return launch<true, false, BN, STAGES, MIN_CTAS, true>(p, s);
+        return launch<true, true, BN, STAGES, MIN_CTAS, true>(p, s);
+    }
+    if (!p.ta && !p.tb) return launch<false, false, BN, STAGES, MIN_CTAS, false>(p, s);
+    if (!p.ta && p.tb) return launch<false, true, BN, STAGES, MIN_CTAS, false>(p, s);
+    if (p.ta && !p.tb) return launch<true, false, BN, STAGES, MIN_CTAS, false>(p, s);
+    return launch<true, true, BN, STAGES, MIN_CTAS, false>(p, s);
 }
 
 }  // namespace
@@ -516,7 +532,7 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     // kernel: 8192^3 63.5 vs 57.8-60.2, 3008 x 4100 x 1537 48.6 vs 47.2, but 1536^3 (144 tiles) 38.3 vs 50.9 and
     // 4096 x 4096 x 512 48.7 vs 53.9 TFLOP/s.
     if (!p.ta && p.tb && tiles128 >= (size_t)sm_count() * 4 && p.K >= 1024 && getenv("CLBLAS_B200_SGEMM_8X8") == nullptr)
-        return launch_nt_16x8(p, s);
+        return p.tri != TRI_FULL ? launch_nt_16x8<true>(p, s) : launch_nt_16x8<false>(p, s);
     if (!p.ta) return launch_any<128, 3, 2>(p, s);
     return launch_any<128, 5, 1>(p, s);
 }

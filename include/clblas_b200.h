@@ -393,6 +393,28 @@ clblasStatus clblasB200DgemmHost(
     unsigned numCommandQueues, clblasQueue* commandQueues,
     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
 
+/* ---- TRSM on HOST matrices: the argument list of clblasStrsm / clblasDtrsm with host pointers, in the manner of
+ *      clblasB200SgemmHost.  The referenced triangle of A is uploaded once; B travels in blocks of independent
+ *      right-hand sides (columns for clblasLeft, rows for clblasRight) that are uploaded, solved and downloaded in a
+ *      pipeline.  Needs clblasSetup(), like clblasDtrsm. */
+clblasStatus clblasB200StrsmHost(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    float alpha,
+    const void* A, size_t offA, size_t lda,
+    void* B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasB200DtrsmHost(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    double alpha,
+    const void* A, size_t offA, size_t lda,
+    void* B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- matrix helpers: replace clblasMatrixSizeInfo, clblasCreateMatrix*, clblas{Write,Read,Copy}{Sub,}Matrix{,Async}
  *      and clblasFill{Vector,SubMatrix,Matrix}{,Async} (src/clBLAS.h:9665-10238; src/library/blas/matrix.c, fill.cc).
  *      Same argument lists; `command_queue` is ONE cudaStream_t; host pointers are plain host memory (pinned memory

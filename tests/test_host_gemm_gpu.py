@@ -73,3 +73,47 @@ def test_beta_zero_does_not_upload_c_and_degenerate_cases(lib):
     assert lib.clblasB200DgemmHost(*k, 1.0, A, 0, M - 1, B, 0, K, 0.0, C, 0, M) == lib.clblasInvalidLeadDimA
     assert lib.clblasB200DgemmHost(*k, 1.0, A, 0, M, B, 0, K, 0.0, C, 0, M - 1) == lib.clblasInvalidLeadDimC
     assert lib.clblasB200DgemmHost(*k, 1.0, A, 0, M, B, 0, K, 0.0, C, 0, M, queues=[]) == lib.clblasInvalidCommandQueue
+
+
+# --------------------------------------------------------------------------------- TRSM on host matrices
+def run_trsm_host(cb, c, bufs):
+    A, B = (torch.from_numpy(x).pin_memory() for x in bufs)
+    fn = cb.clblasB200StrsmHost if c["prec"] == "s" else cb.clblasB200DtrsmHost
+    st = fn(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A, c["offA"], c["lda"],
+            B, c["offB"], c["ldb"])
+    torch.cuda.synchronize()
+    return st, B.numpy().copy()
+
+
+@pytest.mark.parametrize("prec", ["s", "d"])
+def test_trsm_host_small_cases(lib, prec):
+    """Every order / side / triangle / transposition / diagonal: same acceptance as the device routine (backward
+    error within 4*M*u, NaN-poisoned triangle never read, padding of the host B untouched)."""
+    for c in cases.sweep_trsm_cases(prec)[::4]:
+        logical = cases.trsm_logical(c)
+        bufs = cases.trsm_buffers(c, logical)
+        st, got = run_trsm_host(lib, c, bufs)
+        assert st == lib.clblasSuccess, (lib.STATUS_NAME.get(st, st), c)
+        mask = oracle.outside_mask(got.size, c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
+        assert same_bits(got[mask], bufs[1][mask]), c
+        X = oracle.view(got, c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
+        assert np.all(np.isfinite(X)), c
+        T = cases.trsm_op_triangle(c, logical[0])
+        assert oracle.trsm_backward_ratio(X, c["alpha"], T, logical[1], c["side"], cases.DT[prec]) <= 1.0, c
+
+
+@pytest.mark.parametrize("side", [oracle.Left, oracle.Right])
+def test_trsm_host_several_blocks(lib, side):
+    """2048 x 9000 (Left) / 9000 x 2048 (Right): three blocks of right-hand sides through the pipeline."""
+    M, N = (2048, 9000) if side == oracle.Left else (9000, 2048)
+    c = cases.trsm_case("d", ColumnMajor, side, oracle.Lower, NoTrans, oracle.NonUnit, M, N, alpha=-2.0, pad=(3, 5), off=(2, 4), seed=91)
+    logical = cases.trsm_logical(c)
+    bufs = cases.trsm_buffers(c, logical)
+    st, got = run_trsm_host(lib, c, bufs)
+    assert st == lib.clblasSuccess
+    mask = oracle.outside_mask(got.size, ColumnMajor, NoTrans, M, N, c["ldb"], c["offB"])
+    assert same_bits(got[mask], bufs[1][mask])
+    X = oracle.view(got, ColumnMajor, NoTrans, M, N, c["ldb"], c["offB"])
+    T = cases.trsm_op_triangle(c, logical[0])
+    assert oracle.trsm_backward_ratio(X, c["alpha"], T, logical[1], side, np.float64) <= 1.0
+    assert lib.device_fault() == 0
