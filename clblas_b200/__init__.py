@@ -70,6 +70,9 @@ MATRIX_HELPERS = (["clblasMatrixSizeInfo", "clblasCreateMatrix", "clblasCreateMa
                   + [f"clblas{k}{s}Matrix{a}" for k in ("Write", "Read", "Copy") for s in ("Sub", "") for a in ("", "Async")])
 
 
+COMPLEX_SYM = [f"clblas{p}{r}" for p in "CZ" for r in ("syrk", "herk", "syr2k", "her2k", "symm", "hemm")]
+
+
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -134,6 +137,20 @@ def _load() -> ctypes.CDLL:
     for name in MATRIX_HELPERS:
         if not name.startswith("clblasCreate"):
             getattr(lib, name).restype = i
+    tail = [u, pvp, u, pvp, pvp]
+    for name, ct, rt in (("clblasCsyrk", FloatComplex, None), ("clblasZsyrk", DoubleComplex, None),
+                         ("clblasCherk", None, ctypes.c_float), ("clblasZherk", None, ctypes.c_double)):
+        a = ct or rt
+        getattr(lib, name).argtypes = [i, i, i, sz, sz, a, vp, sz, sz, a, vp, sz, sz] + tail
+        getattr(lib, name).restype = i
+    for name, ct, bt in (("clblasCsyr2k", FloatComplex, FloatComplex), ("clblasZsyr2k", DoubleComplex, DoubleComplex),
+                         ("clblasCher2k", FloatComplex, ctypes.c_float), ("clblasZher2k", DoubleComplex, ctypes.c_double)):
+        getattr(lib, name).argtypes = [i, i, i, sz, sz, ct, vp, sz, sz, vp, sz, sz, bt, vp, sz, sz] + tail
+        getattr(lib, name).restype = i
+    for name, ct in (("clblasCsymm", FloatComplex), ("clblasZsymm", DoubleComplex), ("clblasChemm", FloatComplex),
+                     ("clblasZhemm", DoubleComplex)):
+        getattr(lib, name).argtypes = [i, i, i, sz, sz, ct, vp, sz, sz, vp, sz, sz, ct, vp, sz, sz] + tail
+        getattr(lib, name).restype = i
     lib.clblasSetup.argtypes = []
     lib.clblasSetup.restype = i
     lib.clblasTeardown.argtypes = []
@@ -161,7 +178,7 @@ EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
            "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
-           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost", "clblasB200StrsmHost", "clblasB200DtrsmHost"] + MATRIX_HELPERS
+           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost", "clblasB200StrsmHost", "clblasB200DtrsmHost"] + MATRIX_HELPERS + COMPLEX_SYM
 
 
 def _ptr(x) -> Optional[int]:
@@ -458,6 +475,40 @@ def clblasFillSubMatrix(order, element_size, A, offA, ldA, nrA, ncA, xA, yA, nx,
 
 def clblasFillMatrix(order, element_size, A, offA, ldA, nrA, ncA, pattern: bytes, queue=None) -> int:
     return lib.clblasFillMatrix(order, element_size, _ptr(A), offA, ldA, nrA, ncA, ctypes.c_char_p(pattern), _stream(queue), 0, None)
+
+
+def _complex_routine(name: str):
+    """Builds the Python mirror of one complex symmetric / Hermitian routine (src/clBLAS.h:8417-9640): complex scalars
+    are Python complex numbers, real ones (HERK's alpha and beta, HER2K's beta) floats."""
+    prec = name[6]
+    ct = FloatComplex if prec == "C" else DoubleComplex
+    kind = name[7:]
+    fn = getattr(lib, name)
+
+    def conv(v, is_complex):
+        return _cplx(ct, v) if is_complex else float(v)
+
+    if kind in ("syrk", "herk"):
+        def f(order, uplo, trans, N, K, alpha, A, offA, lda, beta, C, offC, ldc, queues=None, wait=None, events=None) -> int:
+            nq, q, nw, w, e = _queues_events(queues, wait, events)
+            cz = kind == "syrk"
+            return fn(order, uplo, trans, N, K, conv(alpha, cz), _ptr(A), offA, lda, conv(beta, cz), _ptr(C), offC, ldc, nq, q, nw, w, e)
+    elif kind in ("syr2k", "her2k"):
+        def f(order, uplo, trans, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, queues=None, wait=None, events=None) -> int:
+            nq, q, nw, w, e = _queues_events(queues, wait, events)
+            return fn(order, uplo, trans, N, K, conv(alpha, True), _ptr(A), offA, lda, _ptr(B), offB, ldb,
+                      conv(beta, kind == "syr2k"), _ptr(C), offC, ldc, nq, q, nw, w, e)
+    else:
+        def f(order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, queues=None, wait=None, events=None) -> int:
+            nq, q, nw, w, e = _queues_events(queues, wait, events)
+            return fn(order, side, uplo, M, N, conv(alpha, True), _ptr(A), offA, lda, _ptr(B), offB, ldb, conv(beta, True),
+                      _ptr(C), offC, ldc, nq, q, nw, w, e)
+    f.__name__ = name
+    return f
+
+
+for _n in COMPLEX_SYM:
+    globals()[_n] = _complex_routine(_n)
 
 
 NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = 4096, 8192

@@ -286,6 +286,86 @@ clblasStatus trsm_host_entry(clblasOrder order, clblasSide side, clblasUplo uplo
     return record_out(s, events);
 }
 
+// Complex SYRK / HERK, SYR2K / HER2K, SYMM / HEMM front ends.  Checks in the order of the reference's doSyrk /
+// doHerk (src/library/blas/xsyrk.c:48-70, xherk.c:52-85), doSyr2k / doHer2k and doSymm (xsymm.c, shared by HEMM).
+// A symmetric update refuses clblasConjTrans and a Hermitian one clblasTrans (clblasInvalidValue), as there.
+// Row-major calls become column-major calls on the transposed problem: other triangle, other transposition
+// (N <-> T, or N <-> C with alpha conjugated for the Hermitian rank-2k update), other side for SYMM / HEMM.
+template <typename R>
+clblasStatus csyrk_entry(bool herm, bool two, clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K,
+                         R ar, R ai, const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb,
+                         R br, R bi, void* C, size_t offC, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (nq == 0 || queues == nullptr) return clblasInvalidValue;
+    if (nev != 0 && wait == nullptr) return clblasInvalidEventWaitList;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (two && B == nullptr) return clblasInvalidMatB;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)uplo > 1u || (unsigned)trans > 2u) return clblasInvalidValue;
+    if (trans == (herm ? clblasTrans : clblasConjTrans)) return clblasInvalidValue;
+    const size_t tsize = 2 * sizeof(R);
+    if ((st = check_matrix_sizes(tsize, order, trans, N, K, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if (two && (st = check_matrix_sizes(tsize, order, trans, N, K, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(tsize, order, clblasNoTrans, N, N, C, offC, ldc, SET_C)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool lower = (uplo == clblasLower);
+    int op = (trans == clblasNoTrans) ? 0 : (herm ? 2 : 1);
+    if (order == clblasRowMajor) {
+        lower = !lower;
+        op = (op == 0) ? (herm ? 2 : 1) : 0;
+        if (herm && two) ai = -ai;
+    }
+    const R* a = static_cast<const R*>(A) + 2 * offA;
+    R* c = static_cast<R*>(C) + 2 * offC;
+    cudaError_t e;
+    if (two) e = csyr2k_colmajor<R>(herm, lower, op, N, K, ar, ai, a, lda, static_cast<const R*>(B) + 2 * offB, ldb, br, bi, c, ldc, s);
+    else     e = csyrk_colmajor<R>(herm, lower, op, N, K, ar, ai, a, lda, br, bi, c, ldc, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
+template <typename R>
+clblasStatus csymm_entry(bool herm, clblasOrder order, clblasSide side, clblasUplo uplo, size_t M, size_t N, R ar, R ai,
+                         const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb, R br, R bi,
+                         void* C, size_t offC, size_t ldc,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u) return clblasInvalidValue;
+    const size_t n = (side == clblasLeft) ? M : N;
+    const size_t tsize = 2 * sizeof(R);
+    if ((st = check_matrix_sizes(tsize, order, clblasNoTrans, n, n, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(tsize, order, clblasNoTrans, M, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(tsize, order, clblasNoTrans, M, N, C, offC, ldc, SET_C)) != clblasSuccess) return st;
+    if (nq == 0 || queues == nullptr) return clblasInvalidValue;
+    if (nev != 0 && wait == nullptr) return clblasInvalidEventWaitList;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = csymm_colmajor<R>(herm, right, lower, M, N, ar, ai, static_cast<const R*>(A) + 2 * offA, lda,
+                                      static_cast<const R*>(B) + 2 * offB, ldb, br, bi, static_cast<R*>(C) + 2 * offC, ldc, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 template <typename T>
 clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
                         size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda,
@@ -728,6 +808,106 @@ clblasStatus clblasB200DtrsmHost(clblasOrder order, clblasSide side, clblasUplo 
                                  clblasEvent* events)
 {
     return trsm_host_entry<double>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasCsyrk(clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K, FloatComplex alpha,
+        const clblasMem A, size_t offA, size_t lda, FloatComplex beta, clblasMem C, size_t offC, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csyrk_entry<float>(false, false, order, uplo, trans, N, K, alpha.s[0], alpha.s[1], A, offA, lda, nullptr, 0, 0, beta.s[0], beta.s[1],
+                            C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZsyrk(clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K, DoubleComplex alpha,
+        const clblasMem A, size_t offA, size_t lda, DoubleComplex beta, clblasMem C, size_t offC, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csyrk_entry<double>(false, false, order, uplo, trans, N, K, alpha.s[0], alpha.s[1], A, offA, lda, nullptr, 0, 0, beta.s[0], beta.s[1],
+                            C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasCherk(clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K, float alpha,
+        const clblasMem A, size_t offA, size_t lda, float beta, clblasMem C, size_t offC, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csyrk_entry<float>(true, false, order, uplo, trans, N, K, alpha, (float)0, A, offA, lda, nullptr, 0, 0, beta, (float)0,
+                            C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZherk(clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K, double alpha,
+        const clblasMem A, size_t offA, size_t lda, double beta, clblasMem C, size_t offC, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csyrk_entry<double>(true, false, order, uplo, trans, N, K, alpha, (double)0, A, offA, lda, nullptr, 0, 0, beta, (double)0,
+                            C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasCsyr2k(clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K, FloatComplex alpha,
+        const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb, FloatComplex beta, clblasMem C, size_t offC, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csyrk_entry<float>(false, true, order, uplo, trans, N, K, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb, beta.s[0], beta.s[1],
+                            C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZsyr2k(clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K, DoubleComplex alpha,
+        const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb, DoubleComplex beta, clblasMem C, size_t offC, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csyrk_entry<double>(false, true, order, uplo, trans, N, K, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb, beta.s[0], beta.s[1],
+                            C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasCher2k(clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K, FloatComplex alpha,
+        const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb, float beta, clblasMem C, size_t offC, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csyrk_entry<float>(true, true, order, uplo, trans, N, K, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb, beta, (float)0,
+                            C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZher2k(clblasOrder order, clblasUplo uplo, clblasTranspose trans, size_t N, size_t K, DoubleComplex alpha,
+        const clblasMem A, size_t offA, size_t lda, const clblasMem B, size_t offB, size_t ldb, double beta, clblasMem C, size_t offC, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csyrk_entry<double>(true, true, order, uplo, trans, N, K, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb, beta, (double)0,
+                            C, offC, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasCsymm(clblasOrder order, clblasSide side, clblasUplo uplo, size_t M, size_t N, FloatComplex alpha,
+        const clblasMem A, size_t offa, size_t lda, const clblasMem B, size_t offb, size_t ldb, FloatComplex beta,
+        clblasMem C, size_t offc, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csymm_entry<float>(false, order, side, uplo, M, N, alpha.s[0], alpha.s[1], A, offa, lda, B, offb, ldb,
+                            beta.s[0], beta.s[1], C, offc, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZsymm(clblasOrder order, clblasSide side, clblasUplo uplo, size_t M, size_t N, DoubleComplex alpha,
+        const clblasMem A, size_t offa, size_t lda, const clblasMem B, size_t offb, size_t ldb, DoubleComplex beta,
+        clblasMem C, size_t offc, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csymm_entry<double>(false, order, side, uplo, M, N, alpha.s[0], alpha.s[1], A, offa, lda, B, offb, ldb,
+                            beta.s[0], beta.s[1], C, offc, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasChemm(clblasOrder order, clblasSide side, clblasUplo uplo, size_t M, size_t N, FloatComplex alpha,
+        const clblasMem A, size_t offa, size_t lda, const clblasMem B, size_t offb, size_t ldb, FloatComplex beta,
+        clblasMem C, size_t offc, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csymm_entry<float>(true, order, side, uplo, M, N, alpha.s[0], alpha.s[1], A, offa, lda, B, offb, ldb,
+                            beta.s[0], beta.s[1], C, offc, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZhemm(clblasOrder order, clblasSide side, clblasUplo uplo, size_t M, size_t N, DoubleComplex alpha,
+        const clblasMem A, size_t offa, size_t lda, const clblasMem B, size_t offb, size_t ldb, DoubleComplex beta,
+        clblasMem C, size_t offc, size_t ldc,
+        unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return csymm_entry<double>(true, order, side, uplo, M, N, alpha.s[0], alpha.s[1], A, offa, lda, B, offb, ldb,
+                            beta.s[0], beta.s[1], C, offc, ldc, nq, queues, nev, wait, events);
 }
 
 clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,

@@ -139,10 +139,13 @@ template cudaError_t complex_transpose<double>(double*, size_t, const double*, s
 // elements; leading dimensions count complex elements.
 template <typename R>
 cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R ai, const R* A, size_t lda,
-                           const R* B, size_t ldb, R br, R bi, R* C, size_t ldc, cudaStream_t s)
+                           const R* B, size_t ldb, R br, R bi, R* C, size_t ldc, cudaStream_t s, int tri)
 {
     if (M == 0 || N == 0) return cudaSuccess;
-    if (K == 0 || (ar == R(0) && ai == R(0))) return complex_scale<R>(C, ldc, M, N, br, bi, s);
+    if (K == 0 || (ar == R(0) && ai == R(0))) {
+        if (tri != TRI_FULL) return complex_tri_scale<R>(tri == TRI_LOWER, N, br, bi, C, ldc, false, s);
+        return complex_scale<R>(C, ldc, M, N, br, bi, s);
+    }
 
     constexpr size_t Q = 16 / sizeof(R);
     auto round_up = [](size_t v, size_t q) { return (v + q - 1) / q * q; };
@@ -158,7 +161,8 @@ cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R
 
     R beta = br;
     if (bi != R(0)) {                       // complex beta: scale first, then accumulate
-        e = complex_scale<R>(C, ldc, M, N, br, bi, s);
+        e = tri != TRI_FULL ? complex_tri_scale<R>(tri == TRI_LOWER, N, br, bi, C, ldc, false, s)
+                            : complex_scale<R>(C, ldc, M, N, br, bi, s);
         beta = R(1);
     }
     if (e == cudaSuccess) {
@@ -180,6 +184,7 @@ cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R
         p.A = E; p.lda = lde;
         if (tb) { p.B = P; p.ldb = ldp; } else { p.B = B; p.ldb = 2 * ldb; }
         p.C = C; p.ldc = 2 * ldc;
+        if (tri != TRI_FULL) p.tri = tri | TRI_PAIRED_ROWS;
         e = gemm_colmajor<R>(p, s);
     }
     const cudaError_t e2 = ws_free(ws, s);
@@ -187,8 +192,8 @@ cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R
 }
 
 template cudaError_t cgemm_colmajor<float>(int, int, size_t, size_t, size_t, float, float, const float*, size_t, const float*,
-                                           size_t, float, float, float*, size_t, cudaStream_t);
+                                           size_t, float, float, float*, size_t, cudaStream_t, int);
 template cudaError_t cgemm_colmajor<double>(int, int, size_t, size_t, size_t, double, double, const double*, size_t,
-                                            const double*, size_t, double, double, double*, size_t, cudaStream_t);
+                                            const double*, size_t, double, double, double*, size_t, cudaStream_t, int);
 
 }  // namespace cb200

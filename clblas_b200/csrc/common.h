@@ -27,21 +27,29 @@ struct GemmProblem {
     int tri = 0;
 };
 
-enum { TRI_FULL = 0, TRI_LOWER = 1, TRI_UPPER = 2 };
+// TRI_PAIRED_ROWS (or-ed in): rows 2i and 2i+1 of C both belong to row i of the triangle -- a complex matrix
+// seen as a real one with interleaved (re, im) rows.
+enum { TRI_FULL = 0, TRI_LOWER = 1, TRI_UPPER = 2, TRI_PAIRED_ROWS = 4 };
 
 // true when no entry of the bm x bn tile at (m0, n0) lies in the triangle
 __host__ __device__ inline bool tri_tile_outside(int tri, size_t m0, size_t bm, size_t n0, size_t bn)
 {
-    return tri == TRI_LOWER ? m0 + bm - 1 < n0 : tri == TRI_UPPER ? n0 + bn - 1 < m0 : false;
+    const int sh = (tri >> 2) & 1, kind = tri & 3;
+    const size_t r0 = m0 >> sh, r1 = (m0 + bm - 1) >> sh;
+    return kind == TRI_LOWER ? r1 < n0 : kind == TRI_UPPER ? n0 + bn - 1 < r0 : false;
 }
 // true when every entry of the tile lies in the triangle (no masking needed)
 __host__ __device__ inline bool tri_tile_inside(int tri, size_t m0, size_t bm, size_t n0, size_t bn)
 {
-    return tri == TRI_LOWER ? m0 >= n0 + bn - 1 : tri == TRI_UPPER ? n0 >= m0 + bm - 1 : true;
+    const int sh = (tri >> 2) & 1, kind = tri & 3;
+    const size_t r0 = m0 >> sh, r1 = (m0 + bm - 1) >> sh;
+    return kind == TRI_LOWER ? r0 >= n0 + bn - 1 : kind == TRI_UPPER ? n0 >= r1 : true;
 }
 __host__ __device__ inline bool tri_masked(int tri, size_t row, size_t col)
 {
-    return tri == TRI_LOWER ? row < col : tri == TRI_UPPER ? row > col : false;
+    const int sh = (tri >> 2) & 1, kind = tri & 3;
+    const size_t r = row >> sh;
+    return kind == TRI_LOWER ? r < col : kind == TRI_UPPER ? r > col : false;
 }
 
 // Kernel families (reported by clblasB200LastGemmKernel).
@@ -86,8 +94,25 @@ cudaError_t gemm_colmajor(const GemmProblem<T>& p, cudaStream_t s);
 
 // Complex GEMM on the real kernels (cgemm.cu).  ta / tb: 0 NoTrans, 1 Trans, 2 ConjTrans; pointers are to
 // the real part of the first element, leading dimensions count complex elements.
+// tri: TRI_FULL, or TRI_LOWER / TRI_UPPER to compute and store only that triangle of the (square) complex C.
 template <typename R>
 cudaError_t cgemm_colmajor(int ta, int tb, size_t M, size_t N, size_t K, R ar, R ai, const R* A, size_t lda,
+                           const R* B, size_t ldb, R br, R bi, R* C, size_t ldc, cudaStream_t s, int tri = TRI_FULL);
+
+// C <- beta*C on one triangle of an N x N complex matrix; imaginary parts of the diagonal set to zero when asked.
+template <typename R>
+cudaError_t complex_tri_scale(bool lower, size_t N, R br, R bi, R* C, size_t ldc, bool zero_diag_imag, cudaStream_t s);
+
+// Complex symmetric / Hermitian rank-k and rank-2k updates and symmetric / Hermitian products (csyrk.cu).
+// op: 0 NoTrans, 1 Trans (SYRK/SYR2K), 2 ConjTrans (HERK/HER2K).
+template <typename R>
+cudaError_t csyrk_colmajor(bool herm, bool lower, int op, size_t N, size_t K, R ar, R ai, const R* A, size_t lda,
+                           R br, R bi, R* C, size_t ldc, cudaStream_t s);
+template <typename R>
+cudaError_t csyr2k_colmajor(bool herm, bool lower, int op, size_t N, size_t K, R ar, R ai, const R* A, size_t lda,
+                            const R* B, size_t ldb, R br, R bi, R* C, size_t ldc, cudaStream_t s);
+template <typename R>
+cudaError_t csymm_colmajor(bool herm, bool right, bool lower, size_t M, size_t N, R ar, R ai, const R* A, size_t lda,
                            const R* B, size_t ldb, R br, R bi, R* C, size_t ldc, cudaStream_t s);
 
 // C <- beta*C on an M x N complex matrix (beta == 0 stores zeros without reading); dst = src^T for complex matrices.

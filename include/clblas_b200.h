@@ -362,6 +362,141 @@ const char* clblasB200LastGemmKernel(void);
  * src/library/blas/impl.c:81-129).  Returns the previous value. */
 int clblasB200SetGemmPath(int path);
 
+/* ---- complex symmetric / Hermitian level-3: replace clblasCsyrk / Zsyrk (src/clBLAS.h:8417, :8485), clblasCherk / Zherk
+ *      (:9389, :9458; real alpha and beta), clblasCsyr2k / Zsyr2k (:8722, :8798), clblasCher2k / Zher2k (:9545, :9623;
+ *      real beta), clblasCsymm / Zsymm (:9052, :9124) and clblasChemm / Zhemm (:9224, :9305); reference front ends
+ *      src/library/blas/xsyrk.c, xherk.c, xsyr2k.c, xher2k.c, xsymm.c, xhemm.c.  Same checks in the same order; a
+ *      symmetric update refuses clblasConjTrans and a Hermitian one clblasTrans (clblasInvalidValue).  Only the
+ *      `uplo` triangle of C (rank-k updates) or of A (SYMM / HEMM) is referenced; Hermitian results have a real
+ *      diagonal.  All run on the complex GEMM (workspaces from the library's pool). */
+clblasStatus clblasCsyrk(
+    clblasOrder order, clblasUplo uplo, clblasTranspose trans,
+    size_t N, size_t K,
+    FloatComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    FloatComplex beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZsyrk(
+    clblasOrder order, clblasUplo uplo, clblasTranspose trans,
+    size_t N, size_t K,
+    DoubleComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    DoubleComplex beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasCherk(
+    clblasOrder order, clblasUplo uplo, clblasTranspose trans,
+    size_t N, size_t K,
+    float alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    float beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZherk(
+    clblasOrder order, clblasUplo uplo, clblasTranspose trans,
+    size_t N, size_t K,
+    double alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    double beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasCsyr2k(
+    clblasOrder order, clblasUplo uplo, clblasTranspose trans,
+    size_t N, size_t K,
+    FloatComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    FloatComplex beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZsyr2k(
+    clblasOrder order, clblasUplo uplo, clblasTranspose trans,
+    size_t N, size_t K,
+    DoubleComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    DoubleComplex beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasCher2k(
+    clblasOrder order, clblasUplo uplo, clblasTranspose trans,
+    size_t N, size_t K,
+    FloatComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    float beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZher2k(
+    clblasOrder order, clblasUplo uplo, clblasTranspose trans,
+    size_t N, size_t K,
+    DoubleComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    const clblasMem B, size_t offB, size_t ldb,
+    double beta,
+    clblasMem C, size_t offC, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasCsymm(
+    clblasOrder order, clblasSide side, clblasUplo uplo,
+    size_t M, size_t N,
+    FloatComplex alpha,
+    const clblasMem A, size_t offa, size_t lda,
+    const clblasMem B, size_t offb, size_t ldb,
+    FloatComplex beta,
+    clblasMem C, size_t offc, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZsymm(
+    clblasOrder order, clblasSide side, clblasUplo uplo,
+    size_t M, size_t N,
+    DoubleComplex alpha,
+    const clblasMem A, size_t offa, size_t lda,
+    const clblasMem B, size_t offb, size_t ldb,
+    DoubleComplex beta,
+    clblasMem C, size_t offc, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasChemm(
+    clblasOrder order, clblasSide side, clblasUplo uplo,
+    size_t M, size_t N,
+    FloatComplex alpha,
+    const clblasMem A, size_t offa, size_t lda,
+    const clblasMem B, size_t offb, size_t ldb,
+    FloatComplex beta,
+    clblasMem C, size_t offc, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZhemm(
+    clblasOrder order, clblasSide side, clblasUplo uplo,
+    size_t M, size_t N,
+    DoubleComplex alpha,
+    const clblasMem A, size_t offa, size_t lda,
+    const clblasMem B, size_t offb, size_t ldb,
+    DoubleComplex beta,
+    clblasMem C, size_t offc, size_t ldc,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- GEMM on HOST matrices (no single counterpart in the reference: it is what a clBLAS program does with
  *      clEnqueueWriteBuffer x3 + clblasXgemm + clEnqueueReadBuffer, src/samples/example_sgemm.c:118-160, done as one
  *      call).  Same argument list as clblasSgemm / clblasDgemm, but A, B and C are HOST pointers (pinned memory for

@@ -91,6 +91,16 @@ def _lib(impl: str) -> ctypes.CDLL:
         getattr(lib, f"{prefix}{p}gemm").restype = None
         getattr(lib, f"{prefix}{p}trsm").argtypes = [i, i, i, i, i, sz, sz, ct, ct, ptr, sz, ptr, sz]
         getattr(lib, f"{prefix}{p}trsm").restype = None
+        if prefix == "oracle_":      # herm flag after trans / uplo; the reference's naive BLAS has only the symmetric updates
+            getattr(lib, f"{prefix}{p}syrk").argtypes = [i, i, i, i, sz, sz, ct, ct, ptr, sz, ct, ct, ptr, sz]
+            getattr(lib, f"{prefix}{p}syr2k").argtypes = [i, i, i, i, sz, sz, ct, ct, ptr, sz, ptr, sz, ct, ct, ptr, sz]
+            getattr(lib, f"{prefix}{p}symm").argtypes = [i, i, i, i, sz, sz, ct, ct, ptr, sz, ptr, sz, ct, ct, ptr, sz]
+            getattr(lib, f"{prefix}{p}symm").restype = None
+        else:
+            getattr(lib, f"{prefix}{p}syrk").argtypes = [i, i, i, sz, sz, ct, ct, ptr, sz, ct, ct, ptr, sz]
+            getattr(lib, f"{prefix}{p}syr2k").argtypes = [i, i, i, sz, sz, ct, ct, ptr, sz, ptr, sz, ct, ct, ptr, sz]
+        getattr(lib, f"{prefix}{p}syrk").restype = None
+        getattr(lib, f"{prefix}{p}syr2k").restype = None
     lib._prefix = prefix
     _libs[impl] = lib
     return lib
@@ -149,6 +159,44 @@ def ctrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, l
     alpha = complex(alpha)
     fn = getattr(lib, f"{lib._prefix}{p}trsm")
     fn(order, side, uplo, transA, diag, M, N, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb)
+
+
+def _cz(arr):
+    return "c" if arr.dtype == np.complex64 else "z"
+
+
+def csyrk(order, uplo, trans, N, K, alpha, A, offA, lda, beta, C, offC, ldc, herm=False, impl: str = "port") -> None:
+    """Complex SYRK (herm=False; impl "ref" = NaiveBlas::syrk) or HERK (herm=True, port only) in place on C."""
+    lib = _lib(impl)
+    alpha, beta = complex(alpha), complex(beta)
+    fn = getattr(lib, f"{lib._prefix}{_cz(C)}syrk")
+    if impl == "port":
+        fn(order, uplo, trans, int(herm), N, K, alpha.real, alpha.imag, _p(A, offA), lda, beta.real, beta.imag, _p(C, offC), ldc)
+    else:
+        assert not herm
+        fn(order, uplo, trans, N, K, alpha.real, alpha.imag, _p(A, offA), lda, beta.real, beta.imag, _p(C, offC), ldc)
+
+
+def csyr2k(order, uplo, trans, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, herm=False, impl: str = "port") -> None:
+    """Complex SYR2K (herm=False; impl "ref" = NaiveBlas::syr2k) or HER2K (herm=True, port only) in place on C."""
+    lib = _lib(impl)
+    alpha, beta = complex(alpha), complex(beta)
+    fn = getattr(lib, f"{lib._prefix}{_cz(C)}syr2k")
+    if impl == "port":
+        fn(order, uplo, trans, int(herm), N, K, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb, beta.real, beta.imag,
+           _p(C, offC), ldc)
+    else:
+        assert not herm
+        fn(order, uplo, trans, N, K, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb, beta.real, beta.imag, _p(C, offC), ldc)
+
+
+def csymm(order, side, uplo, M, N, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, herm=False) -> None:
+    """Complex SYMM (herm=False) or HEMM (herm=True) in place on C; port only (Netlib definition)."""
+    lib = _lib("port")
+    alpha, beta = complex(alpha), complex(beta)
+    fn = getattr(lib, f"oracle_{_cz(C)}symm")
+    fn(order, side, uplo, int(herm), M, N, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb, beta.real, beta.imag,
+       _p(C, offC), ldc)
 
 
 def syrk(order, uplo, trans, N, K, alpha, A, offA, lda, beta, C, offC, ldc, impl: str = "port") -> None:

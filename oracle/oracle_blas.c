@@ -357,3 +357,144 @@ void NAME(int order, int side, int uplo, int transA, int diag, size_t M, size_t 
 
 DEFINE_CTRSM(oracle_ctrsm, float)
 DEFINE_CTRSM(oracle_ztrsm, double)
+
+/* Complex rank-k / rank-2k updates and symmetric / Hermitian products.
+ * herm == 0: NaiveBlas::syrk / syr2k on FloatComplex / DoubleComplex (naive_blas.cpp:692-766; the accessor
+ * treats ConjTrans as Trans there, so nothing is conjugated).  herm != 0 (HERK, HER2K, HEMM) and SYMM have no
+ * counterpart in the reference's naive BLAS -- its tests call the external Fortran BLAS -- and follow the Netlib
+ * definitions: C <- alpha*op(A)*op(A)^H + beta*C with real alpha, beta; C <- alpha*op(A)*op(B)^H +
+ * conj(alpha)*op(B)*op(A)^H + beta*C with real beta; imaginary parts of the diagonal of C set to zero. */
+#define DEFINE_CSYRK(NAME, T)                                                                  \
+void NAME(int order, int uplo, int trans, int herm, size_t N, size_t K, T alr, T ali,          \
+          const T* A, size_t lda, T ber, T bei, T* C, size_t ldc)                              \
+{                                                                                              \
+    acc_t ma = make_acc(order, trans == ONoTrans ? ONoTrans : OTrans, lda);                    \
+    acc_t mc = make_acc(order, ONoTrans, ldc);                                                 \
+    const int cj = herm && trans != ONoTrans;   /* op(A) = A^H: elements read conjugated */    \
+    long long i;                                                                               \
+    _Pragma("omp parallel for schedule(dynamic, 8)")                                           \
+    for (i = 0; i < (long long)N; i++) {                                                       \
+        size_t j, k;                                                                           \
+        for (j = 0; j < N; j++) {                                                              \
+            T tr = (T)0.0, ti = (T)0.0;                                                        \
+            if ((uplo == OLower && j > (size_t)i) || (uplo == OUpper && (size_t)i > j)) continue; \
+            for (k = 0; k < K; k++) {                                                          \
+                const T* a = A + 2 * at(ma, (size_t)i, k);                                     \
+                const T* b = A + 2 * at(ma, j, k);                                             \
+                const T ar = a[0], ai = cj ? -a[1] : a[1];                                     \
+                T br = b[0], bi = cj ? -b[1] : b[1];                                           \
+                if (herm) bi = -bi;             /* times conj(op(A)[j][k]) */                  \
+                tr = tr + (ar * br - ai * bi);                                                 \
+                ti = ti + (ar * bi + br * ai);                                                 \
+            }                                                                                  \
+            {                                                                                  \
+                T* c = C + 2 * at(mc, (size_t)i, j);                                           \
+                const T cr = c[0], ci = c[1];                                                  \
+                const T xr = cr * ber - ci * bei, xi = cr * bei + ber * ci;                    \
+                const T yr = tr * alr - ti * ali, yi = tr * ali + alr * ti;                    \
+                c[0] = xr + yr;                                                                \
+                c[1] = (herm && (size_t)i == j) ? (T)0.0 : xi + yi;                            \
+            }                                                                                  \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_CSYRK(oracle_csyrk, float)
+DEFINE_CSYRK(oracle_zsyrk, double)
+
+#define DEFINE_CSYR2K(NAME, T)                                                                 \
+void NAME(int order, int uplo, int trans, int herm, size_t N, size_t K, T alr, T ali,          \
+          const T* A, size_t lda, const T* B, size_t ldb, T ber, T bei, T* C, size_t ldc)      \
+{                                                                                              \
+    int tr_ = trans == ONoTrans ? ONoTrans : OTrans;                                           \
+    acc_t ma = make_acc(order, tr_, lda);                                                      \
+    acc_t mb = make_acc(order, tr_, ldb);                                                      \
+    acc_t mc = make_acc(order, ONoTrans, ldc);                                                 \
+    const int cj = herm && trans != ONoTrans;                                                  \
+    long long i;                                                                               \
+    _Pragma("omp parallel for schedule(dynamic, 8)")                                           \
+    for (i = 0; i < (long long)N; i++) {                                                       \
+        size_t j, k;                                                                           \
+        for (j = 0; j < N; j++) {                                                              \
+            T tr = (T)0.0, ti = (T)0.0;                                                        \
+            if ((uplo == OLower && j > (size_t)i) || (uplo == OUpper && (size_t)i > j)) continue; \
+            for (k = 0; k < K; k++) {                                                          \
+                const T* pa_i = A + 2 * at(ma, (size_t)i, k);                                  \
+                const T* pa_j = A + 2 * at(ma, j, k);                                          \
+                const T* pb_i = B + 2 * at(mb, (size_t)i, k);                                  \
+                const T* pb_j = B + 2 * at(mb, j, k);                                          \
+                const T air = pa_i[0], aii = cj ? -pa_i[1] : pa_i[1];                          \
+                const T ajr = pa_j[0], aji = cj ? -pa_j[1] : pa_j[1];                          \
+                const T bir = pb_i[0], bii = cj ? -pb_i[1] : pb_i[1];                          \
+                const T bjr = pb_j[0], bji = cj ? -pb_j[1] : pb_j[1];                          \
+                if (!herm) {                                                                   \
+                    /* tmp + a_ik*b_jk + a_jk*b_ik, summed in that order (naive_blas.cpp:760) */ \
+                    const T p1r = air * bjr - aii * bji, p1i = air * bji + bjr * aii;          \
+                    const T p2r = ajr * bir - aji * bii, p2i = ajr * bii + bir * aji;          \
+                    tr = tr + p1r + p2r;                                                       \
+                    ti = ti + p1i + p2i;                                                       \
+                } else {                                                                       \
+                    /* alpha*a_ik*conj(b_jk) + conj(alpha)*b_ik*conj(a_jk) */                  \
+                    const T p1r = air * bjr + aii * bji, p1i = aii * bjr - air * bji;          \
+                    const T p2r = bir * ajr + bii * aji, p2i = bii * ajr - bir * aji;          \
+                    tr = tr + (alr * p1r - ali * p1i) + (alr * p2r + ali * p2i);               \
+                    ti = ti + (alr * p1i + ali * p1r) + (alr * p2i - ali * p2r);               \
+                }                                                                              \
+            }                                                                                  \
+            {                                                                                  \
+                T* c = C + 2 * at(mc, (size_t)i, j);                                           \
+                const T cr = c[0], ci = c[1];                                                  \
+                const T xr = cr * ber - ci * bei, xi = cr * bei + ber * ci;                    \
+                if (!herm) {                                                                   \
+                    const T yr = tr * alr - ti * ali, yi = tr * ali + alr * ti;                \
+                    c[0] = xr + yr;                                                            \
+                    c[1] = xi + yi;                                                            \
+                } else {                                                                       \
+                    c[0] = xr + tr;                                                            \
+                    c[1] = ((size_t)i == j) ? (T)0.0 : xi + ti;                                \
+                }                                                                              \
+            }                                                                                  \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_CSYR2K(oracle_csyr2k, float)
+DEFINE_CSYR2K(oracle_zsyr2k, double)
+
+#define DEFINE_CSYMM(NAME, T)                                                                  \
+void NAME(int order, int side, int uplo, int herm, size_t M, size_t N, T alr, T ali,           \
+          const T* A, size_t lda, const T* B, size_t ldb, T ber, T bei, T* C, size_t ldc)      \
+{                                                                                              \
+    acc_t ma = make_acc(order, ONoTrans, lda);                                                 \
+    acc_t mb = make_acc(order, ONoTrans, ldb);                                                 \
+    acc_t mc = make_acc(order, ONoTrans, ldc);                                                 \
+    const size_t n = (side == OLeft) ? M : N;                                                  \
+    long long i;                                                                               \
+    _Pragma("omp parallel for schedule(dynamic, 8)")                                           \
+    for (i = 0; i < (long long)M; i++) {                                                       \
+        size_t j, k;                                                                           \
+        for (j = 0; j < N; j++) {                                                              \
+            T tr = (T)0.0, ti = (T)0.0;                                                        \
+            for (k = 0; k < n; k++) {                                                          \
+                /* full(r, c): entry (r, c) of the symmetric / Hermitian matrix from its stored triangle */ \
+                const size_t r = (side == OLeft) ? (size_t)i : k, c = (side == OLeft) ? k : j; \
+                const int st = (uplo == OLower) ? (r >= c) : (r <= c);                         \
+                const T* a = A + 2 * (st ? at(ma, r, c) : at(ma, c, r));                       \
+                const T* b = B + 2 * ((side == OLeft) ? at(mb, k, j) : at(mb, (size_t)i, k));  \
+                T ar = a[0], ai = a[1];                                                        \
+                if (herm) { if (!st) ai = -ai; if (r == c) ai = (T)0.0; }                      \
+                tr = tr + (ar * b[0] - ai * b[1]);                                             \
+                ti = ti + (ar * b[1] + b[0] * ai);                                             \
+            }                                                                                  \
+            {                                                                                  \
+                T* c = C + 2 * at(mc, (size_t)i, j);                                           \
+                const T cr = c[0], ci = c[1];                                                  \
+                c[0] = (cr * ber - ci * bei) + (tr * alr - ti * ali);                          \
+                c[1] = (cr * bei + ber * ci) + (tr * ali + alr * ti);                          \
+            }                                                                                  \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_CSYMM(oracle_csymm, float)
+DEFINE_CSYMM(oracle_zsymm, double)

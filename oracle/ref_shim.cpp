@@ -135,4 +135,29 @@ void ref_ztrsm(int order, int side, int uplo, int transA, int diag, size_t M, si
                                               reinterpret_cast<NaiveBlas::DoubleComplex*>(B), ldb);
 }
 
+#define REF_CSYRK(NAME, CT, MK, T)                                                                                   \
+    void NAME(int order, int uplo, int trans, size_t N, size_t K, T alr, T ali, const T* A, size_t lda, T ber, T bei,    \
+              T* C, size_t ldc)                                                                                          \
+    {                                                                                                                    \
+        NaiveBlas::syrk<NaiveBlas::CT>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasUplo)uplo,                       \
+                                       (NaiveBlas::clblasTranspose)trans, N, K, NaiveBlas::MK(alr, ali),                 \
+                                       reinterpret_cast<const NaiveBlas::CT*>(A), lda, NaiveBlas::MK(ber, bei),          \
+                                       reinterpret_cast<NaiveBlas::CT*>(C), ldc);                                        \
+    }
+REF_CSYRK(ref_csyrk, FloatComplex, floatComplex, float)
+REF_CSYRK(ref_zsyrk, DoubleComplex, doubleComplex, double)
+
+#define REF_CSYR2K(NAME, CT, MK, T)                                                                                  \
+    void NAME(int order, int uplo, int trans, size_t N, size_t K, T alr, T ali, const T* A, size_t lda, const T* B,      \
+              size_t ldb, T ber, T bei, T* C, size_t ldc)                                                                \
+    {                                                                                                                    \
+        NaiveBlas::syr2k<NaiveBlas::CT>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasUplo)uplo,                      \
+                                        (NaiveBlas::clblasTranspose)trans, N, K, NaiveBlas::MK(alr, ali),                \
+                                        reinterpret_cast<const NaiveBlas::CT*>(A), lda,                                  \
+                                        reinterpret_cast<const NaiveBlas::CT*>(B), ldb, NaiveBlas::MK(ber, bei),         \
+                                        reinterpret_cast<NaiveBlas::CT*>(C), ldc);                                       \
+    }
+REF_CSYR2K(ref_csyr2k, FloatComplex, floatComplex, float)
+REF_CSYR2K(ref_zsyr2k, DoubleComplex, doubleComplex, double)
+
 }  // extern "C"

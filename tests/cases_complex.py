@@ -151,3 +151,164 @@ def sweep_ctrsm_cases(prec):
             cases.append(ctrsm_case(prec, order, side, uplo, ta, diag, M, N, alpha=[1 + 0j, 2.5 - 1j, -0.5j][seed % 3],
                                     pad=(seed % 5, seed % 7), off=(seed % 3, seed % 11), seed=seed))
     return cases
+
+
+# ------------------------------------------------- complex SYRK / HERK / SYR2K / HER2K / SYMM / HEMM
+def _other_triangle(n, uplo):
+    return np.triu(np.ones((n, n), dtype=bool), 1) if uplo == Lower else np.tril(np.ones((n, n), dtype=bool), -1)
+
+
+def crank_case(kind, prec, order, uplo, trans, N, K, alpha, beta, pad=(0, 0, 0), off=(0, 0, 0), mode="int", seed=12345):
+    """kind: syrk | herk | syr2k | her2k.  trans: NoTrans, or Trans (symmetric kinds) / ConjTrans (Hermitian kinds)."""
+    ld = _min_ld(order, trans, N, K)
+    return dict(kind=kind, prec=prec, order=order, uplo=uplo, trans=trans, N=N, K=K, alpha=alpha, beta=beta,
+                lda=ld + pad[0], ldb=ld + pad[1], ldc=N + pad[2], offA=off[0], offB=off[1], offC=off[2], mode=mode, seed=seed)
+
+
+def crank_logical(c):
+    """op(A), op(B) (N x K) and C (N x N: NaN in the triangle that is not referenced; real diagonal for Hermitian kinds)."""
+    g = oracle.rng(c["seed"], 41)
+    opA = _draw(g, c["mode"], (c["N"], c["K"]), c["prec"])
+    opB = _draw(g, c["mode"], (c["N"], c["K"]), c["prec"])
+    C = _draw(g, c["mode"], (c["N"], c["N"]), c["prec"])
+    if c["kind"] in ("herk", "her2k"):
+        C[np.arange(c["N"]), np.arange(c["N"])] = C.diagonal().real
+    C[_other_triangle(c["N"], c["uplo"])] = CNAN
+    return opA, opB, C
+
+
+def crank_buffers(c, logical=None, tail=3):
+    opA, opB, C = logical if logical is not None else crank_logical(c)
+    herm = c["kind"] in ("herk", "her2k")
+    # the stored matrix X satisfies op(X) = opX: X = opX, opX^T, or conj(opX)^T when op is the conjugate transposition
+    sA = np.conj(opA) if (herm and c["trans"] != NoTrans) else opA
+    sB = np.conj(opB) if (herm and c["trans"] != NoTrans) else opB
+    return (oracle.pack(sA, c["order"], c["trans"], c["lda"], c["offA"], pad_value=CNAN, tail=tail),
+            oracle.pack(sB, c["order"], c["trans"], c["ldb"], c["offB"], pad_value=CNAN, tail=tail),
+            oracle.pack(C, c["order"], NoTrans, c["ldc"], c["offC"], pad_value=CNAN, tail=tail))
+
+
+def crank_exact(c, logical):
+    """complex128 value of the update on the whole matrix and the magnitude sum that scales the error bound."""
+    opA, opB, C = (x.astype(np.complex128) for x in logical)
+    C = np.nan_to_num(C)
+    a, b = c["alpha"], c["beta"]
+    k = c["kind"]
+    if k == "syrk":
+        want, mag = a * (opA @ opA.T) + b * C, abs(a) * (np.abs(opA) @ np.abs(opA).T) + abs(b) * np.abs(C)
+    elif k == "herk":
+        want, mag = a * (opA @ opA.conj().T) + b * C, abs(a) * (np.abs(opA) @ np.abs(opA).T) + abs(b) * np.abs(C)
+    elif k == "syr2k":
+        want = a * (opA @ opB.T + opB @ opA.T) + b * C
+        mag = abs(a) * (np.abs(opA) @ np.abs(opB).T + np.abs(opB) @ np.abs(opA).T) + abs(b) * np.abs(C)
+    else:
+        want = a * (opA @ opB.conj().T) + np.conj(a) * (opB @ opA.conj().T) + b * C
+        mag = abs(a) * (np.abs(opA) @ np.abs(opB).T + np.abs(opB) @ np.abs(opA).T) + abs(b) * np.abs(C)
+    if k in ("herk", "her2k"):
+        want = want.copy()
+        want[np.arange(c["N"]), np.arange(c["N"])] = want.diagonal().real
+    return want, mag
+
+
+def crank_scalars(kind, k):
+    if kind == "syrk":
+        return [1 + 0j, 2 - 1j, -1 + 3j][k % 3], [1 + 0j, 0j, 2 + 1j][k % 3]
+    if kind == "herk":
+        return [1.0, 2.0, -3.0][k % 3], [1.0, 0.0, 2.0][k % 3]
+    if kind == "syr2k":
+        return [1 + 0j, 2 - 1j, -1 + 3j][k % 3], [1 + 0j, 0j, 2 + 1j][k % 3]
+    return [1 + 0j, 2 - 1j, -1 + 3j][k % 3], [1.0, 0.0, 2.0][k % 3]
+
+
+def golden_crank_cases():
+    out = {}
+    k = 0
+    for kind in ("syrk", "herk", "syr2k", "her2k"):
+        t2 = Trans if kind in ("syrk", "syr2k") else ConjTrans
+        for prec in "cz":
+            for order, uplo, tr in itertools.product(ORDERS, (Upper, Lower), (NoTrans, t2)):
+                N, K = [(9, 5), (16, 17), (33, 12)][k % 3]
+                al, be = crank_scalars(kind, k)
+                out[f"c{kind}_{prec}_{order}{uplo}{tr}"] = crank_case(kind, prec, order, uplo, tr, N, K, al, be, pad=(2, 1, 3),
+                                                                    off=(1, 2, 4), mode=["int", "uniform"][k % 2], seed=1500 + k)
+                k += 1
+    return out
+
+
+def sweep_crank_cases(kind, prec, mode):
+    cases = []
+    seed = 16000
+    t2 = Trans if kind in ("syrk", "syr2k") else ConjTrans
+    for order, uplo, tr in itertools.product(ORDERS, (Upper, Lower), (NoTrans, t2)):
+        for (N, K) in ((8, 8), (17, 33), (128, 64), (257, 130), (300, 129)):
+            seed += 1
+            al, be = crank_scalars(kind, seed)
+            cases.append(crank_case(kind, prec, order, uplo, tr, N, K, al, be, pad=(seed % 5, seed % 3, seed % 7),
+                                    off=(seed % 3, seed % 5, seed % 11), mode=mode, seed=seed))
+    return cases
+
+
+def csymm_case(kind, prec, order, side, uplo, M, N, alpha, beta, pad=(0, 0, 0), off=(0, 0, 0), mode="int", seed=12345):
+    """kind: symm | hemm."""
+    n = M if side == Left else N
+    ldbc = _min_ld(order, NoTrans, M, N)
+    return dict(kind=kind, prec=prec, order=order, side=side, uplo=uplo, M=M, N=N, alpha=alpha, beta=beta,
+                lda=n + pad[0], ldb=ldbc + pad[1], ldc=ldbc + pad[2], offA=off[0], offB=off[1], offC=off[2], mode=mode, seed=seed)
+
+
+def csymm_logical(c):
+    """(stored A with NaN in the other triangle -- and, for HEMM, garbage imaginary parts on the diagonal, which must be
+    ignored -- the dense matrix it stands for, B, C)."""
+    g = oracle.rng(c["seed"], 43)
+    n = c["M"] if c["side"] == Left else c["N"]
+    R = _draw(g, c["mode"], (n, n), c["prec"])
+    if c["kind"] == "hemm":
+        full = np.tril(R, -1) + np.tril(R, -1).conj().T + np.diag(R.diagonal().real)
+    else:
+        full = np.tril(R) + np.tril(R, -1).T
+    full = full.astype(CDT[c["prec"]])
+    A = full.copy()
+    if c["kind"] == "hemm":
+        A[np.arange(n), np.arange(n)] = full.diagonal().real + 1j * 7.0
+    A[_other_triangle(n, c["uplo"])] = CNAN
+    return A, full, _draw(g, c["mode"], (c["M"], c["N"]), c["prec"]), _draw(g, c["mode"], (c["M"], c["N"]), c["prec"])
+
+
+def csymm_buffers(c, logical=None, tail=3):
+    A, _, B, C = logical if logical is not None else csymm_logical(c)
+    return (oracle.pack(A, c["order"], NoTrans, c["lda"], c["offA"], pad_value=CNAN, tail=tail),
+            oracle.pack(B, c["order"], NoTrans, c["ldb"], c["offB"], pad_value=CNAN, tail=tail),
+            oracle.pack(C, c["order"], NoTrans, c["ldc"], c["offC"], pad_value=CNAN, tail=tail))
+
+
+def csymm_exact(c, logical):
+    _, full, B, C = (x.astype(np.complex128) for x in logical)
+    a, b = c["alpha"], c["beta"]
+    if c["side"] == Left:
+        return a * (full @ B) + b * C, abs(a) * (np.abs(full) @ np.abs(B)) + abs(b) * np.abs(C)
+    return a * (B @ full) + b * C, abs(a) * (np.abs(B) @ np.abs(full)) + abs(b) * np.abs(C)
+
+
+def golden_csymm_cases():
+    out = {}
+    k = 0
+    for kind in ("symm", "hemm"):
+        for prec in "cz":
+            for order, side, uplo in itertools.product(ORDERS, (Left, Right), (Upper, Lower)):
+                M, N = [(9, 5), (16, 17), (12, 33)][k % 3]
+                out[f"c{kind}_{prec}_{order}{side}{uplo}"] = csymm_case(kind, prec, order, side, uplo, M, N, [1 + 0j, -2 + 1j, 0.5j][k % 3],
+                                                                      [0.5 + 0j, 0j, 3 - 1j][k % 3], pad=(2, 1, 3), off=(1, 2, 4),
+                                                                      mode=["int", "uniform"][k % 2], seed=1700 + k)
+                k += 1
+    return out
+
+
+def sweep_csymm_cases(kind, prec, mode):
+    cases = []
+    seed = 17000
+    for order, side, uplo in itertools.product(ORDERS, (Left, Right), (Upper, Lower)):
+        for (M, N) in ((8, 8), (17, 33), (128, 64), (257, 130), (130, 300)):
+            seed += 1
+            cases.append(csymm_case(kind, prec, order, side, uplo, M, N, [1 + 0j, 2 - 1j, -3j][seed % 3], [1 + 0j, 0j, 2 + 1j][seed % 3],
+                                    pad=(seed % 5, seed % 3, seed % 7), off=(seed % 3, seed % 5, seed % 11), mode=mode, seed=seed))
+    return cases

@@ -33,6 +33,39 @@ def symm_by_external_blas(c):
     return oracle.pack(np.ascontiguousarray(R), c["order"], NoTrans, c["ldc"], c["offC"], tail=3)
 
 
+def hermitian_update_by_external_blas(c):
+    """Logical N x N result of ?herk / ?her2k of the Netlib interface (scipy.linalg.blas) on the logical operands; the
+    triangle that is not referenced keeps the input's NaN."""
+    from scipy.linalg import blas
+    from oracle import Lower, NoTrans
+    opA, opB, C = cases_complex.crank_logical(c)
+    z = c["prec"] == "z"
+    C0 = np.nan_to_num(C)
+    lower = 1 if c["uplo"] == Lower else 0
+    # the operands are handed over as op(X) itself (trans = 0): what is tested downstream is the definition
+    if c["kind"] == "herk":
+        fn = blas.zherk if z else blas.cherk
+        R = fn(c["alpha"], np.asfortranarray(opA), beta=c["beta"], c=np.asfortranarray(C0), trans=0, lower=lower)
+    else:
+        fn = blas.zher2k if z else blas.cher2k
+        R = fn(c["alpha"], np.asfortranarray(opA), np.asfortranarray(opB), beta=c["beta"], c=np.asfortranarray(C0), trans=0,
+               lower=lower)
+    R = np.array(R)
+    R[cases_complex._other_triangle(c["N"], c["uplo"])] = cases_complex.CNAN
+    return R
+
+
+def complex_symm_by_external_blas(c):
+    from scipy.linalg import blas
+    from oracle import Left, Lower
+    A, full, B, C = cases_complex.csymm_logical(c)
+    z = c["prec"] == "z"
+    fn = {("symm", True): blas.zsymm, ("symm", False): blas.csymm, ("hemm", True): blas.zhemm, ("hemm", False): blas.chemm}[(c["kind"], z)]
+    stored = np.where(np.isnan(A), 0, A)
+    return np.array(fn(c["alpha"], np.asfortranarray(stored), np.asfortranarray(B), beta=c["beta"], c=np.asfortranarray(C),
+                       side=0 if c["side"] == Left else 1, lower=1 if c["uplo"] == Lower else 0))
+
+
 def main():
     oracle.build()
     assert oracle.have_ref(), "oracle/_ref/libnaive_ref.so missing: reference tree not present"
@@ -76,6 +109,21 @@ def main():
         oracle.ctrsm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A, c["offA"],
                      c["lda"], B, c["offB"], c["ldb"], impl="ref")
         out[name] = B
+    cc = cases_complex
+    for name, c in cc.golden_crank_cases().items():
+        if c["kind"] in ("syrk", "syr2k"):
+            A, B, C = cc.crank_buffers(c)
+            if c["kind"] == "syrk":
+                oracle.csyrk(c["order"], c["uplo"], c["trans"], c["N"], c["K"], c["alpha"], A, c["offA"], c["lda"], c["beta"],
+                             C, c["offC"], c["ldc"], impl="ref")
+            else:
+                oracle.csyr2k(c["order"], c["uplo"], c["trans"], c["N"], c["K"], c["alpha"], A, c["offA"], c["lda"], B, c["offB"],
+                              c["ldb"], c["beta"], C, c["offC"], c["ldc"], impl="ref")
+            out[name] = C
+        else:
+            out[name] = hermitian_update_by_external_blas(c)
+    for name, c in cc.golden_csymm_cases().items():
+        out[name] = complex_symm_by_external_blas(c)
     path = os.path.join(os.path.dirname(__file__), "level3_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} cases, {os.path.getsize(path)} bytes")
