@@ -109,7 +109,8 @@ def _load() -> ctypes.CDLL:
         f = getattr(lib, name)
         f.argtypes = [i, i, i, sz, sz, sz, ct, vp, sz, sz, vp, sz, sz, ct, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
-    for name, ct in (("clblasCtrsm", FloatComplex), ("clblasZtrsm", DoubleComplex)):
+    for name, ct in (("clblasCtrsm", FloatComplex), ("clblasZtrsm", DoubleComplex), ("clblasCtrmm", FloatComplex),
+                     ("clblasZtrmm", DoubleComplex)):
         f = getattr(lib, name)
         f.argtypes = [i, i, i, i, i, sz, sz, ct, vp, sz, sz, vp, sz, sz, u, pvp, u, pvp, pvp]
         f.restype = i
@@ -178,7 +179,7 @@ EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
            "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
-           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost", "clblasB200StrsmHost", "clblasB200DtrsmHost"] + MATRIX_HELPERS + COMPLEX_SYM
+           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost", "clblasB200StrsmHost", "clblasB200DtrsmHost"] + MATRIX_HELPERS + COMPLEX_SYM + ["clblasCtrmm", "clblasZtrmm"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -475,6 +476,21 @@ def clblasFillSubMatrix(order, element_size, A, offA, ldA, nrA, ncA, xA, yA, nx,
 
 def clblasFillMatrix(order, element_size, A, offA, ldA, nrA, ncA, pattern: bytes, queue=None) -> int:
     return lib.clblasFillMatrix(order, element_size, _ptr(A), offA, ldA, nrA, ncA, ctypes.c_char_p(pattern), _stream(queue), 0, None)
+
+
+def clblasCtrmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                queues=None, wait=None, events=None) -> int:
+    """complex64 triangular product, B overwritten; alpha is a Python complex number (src/clBLAS.h:7839)."""
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return lib.clblasCtrmm(order, side, uplo, transA, diag, M, N, _cplx(FloatComplex, alpha), _ptr(A), offA, lda,
+                           _ptr(B), offB, ldb, nq, q, nw, w, e)
+
+
+def clblasZtrmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                queues=None, wait=None, events=None) -> int:
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return lib.clblasZtrmm(order, side, uplo, transA, diag, M, N, _cplx(DoubleComplex, alpha), _ptr(A), offA, lda,
+                           _ptr(B), offB, ldb, nq, q, nw, w, e)
 
 
 def _complex_routine(name: str):

@@ -366,6 +366,40 @@ clblasStatus csymm_entry(bool herm, clblasOrder order, clblasSide side, clblasUp
     return record_out(s, events);
 }
 
+// Complex TRMM front end: the checks of trmm_entry on complex elements.
+template <typename R>
+clblasStatus ctrmm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, R ar, R ai, const void* A, size_t offA, size_t lda,
+                         void* B, size_t offB, size_t ldb,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u || (unsigned)transA > 2u || (unsigned)diag > 1u) return clblasInvalidValue;
+    const size_t msize = (side == clblasLeft) ? M : N;
+    const size_t tsize = 2 * sizeof(R);
+    if ((st = check_matrix_sizes(tsize, order, transA, msize, msize, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if ((st = check_matrix_sizes(tsize, order, clblasNoTrans, M, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = ctrmm_colmajor<R>(right, lower, (int)transA, diag == clblasUnit, M, N, ar, ai,
+                                      static_cast<const R*>(A) + 2 * offA, lda, static_cast<R*>(B) + 2 * offB, ldb, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(s, events);
+}
+
 template <typename T>
 clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
                         size_t M, size_t N, T alpha, const void* A, size_t offA, size_t lda,
@@ -908,6 +942,24 @@ clblasStatus clblasZhemm(clblasOrder order, clblasSide side, clblasUplo uplo, si
 {
     return csymm_entry<double>(true, order, side, uplo, M, N, alpha.s[0], alpha.s[1], A, offa, lda, B, offb, ldb,
                             beta.s[0], beta.s[1], C, offc, ldc, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasCtrmm(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, FloatComplex alpha, const clblasMem A, size_t offA, size_t lda,
+                         clblasMem B, size_t offB, size_t ldb,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return ctrmm_entry<float>(order, side, uplo, transA, diag, M, N, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb,
+                              nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasZtrmm(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                         size_t M, size_t N, DoubleComplex alpha, const clblasMem A, size_t offA, size_t lda,
+                         clblasMem B, size_t offB, size_t ldb,
+                         unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return ctrmm_entry<double>(order, side, uplo, transA, diag, M, N, alpha.s[0], alpha.s[1], A, offA, lda, B, offB, ldb,
+                               nq, queues, nev, wait, events);
 }
 
 clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA,

@@ -135,6 +135,14 @@ cudaError_t trsm_host_colmajor(bool right, bool lower, bool trans, bool unit, si
                                const T* hA, size_t lda, T* hB, size_t ldb, cudaStream_t user);
 void host_pipeline_release();
 
+// 2 x 2-block real form of the referenced triangle of a complex triangular matrix, blocks of 64 complex rows
+// strictly off the block diagonal only (trsm.cu); complex TRMM (trmm.cu), op as for ctrsm_colmajor.
+template <typename R>
+cudaError_t complex_expand_block_offdiag(const R* A, size_t lda, R* E, size_t lde, size_t n, bool lower, bool conj, cudaStream_t s);
+template <typename R>
+cudaError_t ctrmm_colmajor(bool right, bool lower, int op, bool unit, size_t M, size_t N, R ar, R ai,
+                           const R* A, size_t lda, R* B, size_t ldb, cudaStream_t s);
+
 // Blocked triangular solve on a column-major problem (B overwritten by X).
 template <typename T>
 cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,

@@ -160,6 +160,107 @@ cudaError_t trmm_colmajor(bool right, bool lower, bool trans, bool unit, size_t 
     return e != cudaSuccess ? e : e2;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Complex TRMM (clblasCtrmm / clblasZtrmm, src/clBLAS.h:7839, :7909; src/library/blas/xtrmm.c) on the real
+// recursion above, the way the complex TRSM uses the real solver: with every complex entry written as the
+// real block [[re, -im], [im, re]], alpha*op(A)*B on interleaved storage IS a real triangular product of twice
+// the order whose matrix is triangular by 128 x 128 blocks.  The off-diagonal blocks come from one expansion of
+// the referenced triangle, the dense diagonal blocks from a complex-aware copy; rep(A)^T = rep(A^H), so A^H is
+// the real recursion's transposition of rep(A) and A^T that of rep(conj A); alpha is applied to B first; a
+// Right-side product is the Left-side product of the transposed problem on a transposed copy of B.
+namespace {
+
+constexpr int CNB = NB / 2;
+
+template <typename R> struct Pair2;
+template <> struct Pair2<float> { using type = float2; };
+template <> struct Pair2<double> { using type = double2; };
+
+// tri[b] = 128 x 128 real form of the 64 x 64 complex diagonal block b: zeros outside the referenced triangle
+// and beyond the order n, (1, 0) on a unit diagonal, conjugated when asked.
+template <typename R>
+__global__ void __launch_bounds__(256) ctri_blocks_kernel(const R* __restrict__ A, size_t lda, size_t n, bool lower, bool unit,
+                                                           bool conj, R* __restrict__ tri)
+{
+    using R2 = typename Pair2<R>::type;
+    const size_t b = blockIdx.x, r0 = b * CNB;
+    const R* Ab = A + 2 * (r0 + r0 * lda);
+    R* out = tri + b * (size_t)(NB * NB);
+    for (int e = threadIdx.x; e < CNB * CNB; e += 256) {
+        const int i = e % CNB, j = e / CNB;
+        R2 v; v.x = R(0); v.y = R(0);
+        if (r0 + i < n && r0 + j < n) {
+            if (i == j) {
+                if (unit) v.x = R(1); else v = *reinterpret_cast<const R2*>(Ab + 2 * ((size_t)i + (size_t)j * lda));
+            } else if (lower ? i > j : i < j) {
+                v = *reinterpret_cast<const R2*>(Ab + 2 * ((size_t)i + (size_t)j * lda));
+            }
+        }
+        if (conj) v.y = -v.y;
+        R* o = out + 2 * i + (size_t)(2 * j) * NB;
+        o[0] = v.x; o[1] = v.y; o[NB] = -v.y; o[NB + 1] = v.x;
+    }
+}
+
+template <typename R>
+cudaError_t ctrmm_left(bool lower, int op, bool unit, size_t M, size_t N, const R* A, size_t lda, R* B, size_t ldb, cudaStream_t s)
+{
+    // op: 0 A, 1 A^T, 2 A^H, 3 conj(A)
+    const bool conj = (op == 1 || op == 3), rtrans = (op == 1 || op == 2);
+    TrmmCtx<R> c;
+    c.right = false; c.trans = rtrans; c.eff_lower = (lower != rtrans);
+    c.M = 2 * M; c.N = N; c.n = 2 * M; c.B = B; c.ldb = 2 * ldb; c.alpha = R(1); c.s = s;
+    const size_t nblk = (M + CNB - 1) / CNB;
+    const size_t tri_elems = nblk * (size_t)(NB * NB), tmp_elems = (size_t)NB * N;
+    constexpr size_t Q = 16 / sizeof(R);
+    const size_t lde = (2 * M + Q - 1) / Q * Q;
+    const size_t e_elems = nblk > 1 ? lde * 2 * M : 0;
+    R* ws = nullptr;
+    cudaError_t e = ws_alloc(reinterpret_cast<void**>(&ws), (tri_elems + tmp_elems + e_elems) * sizeof(R), s);
+    if (e != cudaSuccess) return e;
+    c.tri = ws;
+    c.tmp = ws + tri_elems;
+    R* E = ws + tri_elems + tmp_elems;
+    c.A = E; c.lda = lde;
+    ctri_blocks_kernel<R><<<(unsigned)nblk, 256, 0, s>>>(A, lda, M, lower, unit, conj, c.tri);
+    count_launch();
+    e = cudaGetLastError();
+    if (e == cudaSuccess && nblk > 1) e = complex_expand_block_offdiag<R>(A, lda, E, lde, M, lower, conj, s);
+    if (e == cudaSuccess) e = mul_range<R>(c, 0, nblk);
+    const cudaError_t e2 = ws_free(ws, s);
+    return e != cudaSuccess ? e : e2;
+}
+
+}  // namespace
+
+template <typename R>
+cudaError_t ctrmm_colmajor(bool right, bool lower, int op, bool unit, size_t M, size_t N, R ar, R ai,
+                           const R* A, size_t lda, R* B, size_t ldb, cudaStream_t s)
+{
+    if (M == 0 || N == 0) return cudaSuccess;
+    // B <- alpha*B first (alpha == 0: B <- 0 and A is not referenced), then the product with alpha = 1
+    cudaError_t e = complex_scale<R>(B, ldb, M, N, ar, ai, s);
+    if (e != cudaSuccess || (ar == R(0) && ai == R(0))) return e;
+    if (!right) return ctrmm_left<R>(lower, op, unit, M, N, A, lda, B, ldb, s);
+
+    // B op(A) = (op(A)^T B^T)^T: (A)^T -> A^T, (A^T)^T -> A, (A^H)^T -> conj(A)
+    constexpr size_t Q = 16 / sizeof(R);
+    const size_t ldt = (N + Q - 1) / Q * Q;
+    R* Bt = nullptr;
+    e = ws_alloc(reinterpret_cast<void**>(&Bt), 2 * ldt * M * sizeof(R), s);
+    if (e != cudaSuccess) return e;
+    e = complex_transpose<R>(Bt, ldt, B, ldb, M, N, s);
+    if (e == cudaSuccess) e = ctrmm_left<R>(lower, op == 0 ? 1 : op == 1 ? 0 : 3, unit, N, M, A, lda, Bt, ldt, s);
+    if (e == cudaSuccess) e = complex_transpose<R>(B, ldb, Bt, ldt, N, M, s);
+    const cudaError_t e2 = ws_free(Bt, s);
+    return e != cudaSuccess ? e : e2;
+}
+
+template cudaError_t ctrmm_colmajor<float>(bool, bool, int, bool, size_t, size_t, float, float, const float*, size_t, float*, size_t,
+                                           cudaStream_t);
+template cudaError_t ctrmm_colmajor<double>(bool, bool, int, bool, size_t, size_t, double, double, const double*, size_t, double*,
+                                            size_t, cudaStream_t);
+
 template cudaError_t trmm_colmajor<float>(bool, bool, bool, bool, size_t, size_t, float, const float*, size_t, float*, size_t, cudaStream_t);
 template cudaError_t trmm_colmajor<double>(bool, bool, bool, bool, size_t, size_t, double, const double*, size_t, double*, size_t, cudaStream_t);
 

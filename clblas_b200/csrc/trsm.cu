@@ -493,6 +493,17 @@ cudaError_t ctrsm_left(bool lower, int op, bool unit, size_t M, size_t N, const 
 }  // namespace
 
 template <typename R>
+cudaError_t complex_expand_block_offdiag(const R* A, size_t lda, R* E, size_t lde, size_t n, bool lower, bool conj, cudaStream_t s)
+{
+    const unsigned blocks = (unsigned)std::min<size_t>((n * n + 255) / 256, (size_t)sm_count() * 16);
+    expand_tri_kernel<R><<<blocks, 256, 0, s>>>(A, lda, E, lde, n, lower, conj);
+    count_launch();
+    return cudaGetLastError();
+}
+template cudaError_t complex_expand_block_offdiag<float>(const float*, size_t, float*, size_t, size_t, bool, bool, cudaStream_t);
+template cudaError_t complex_expand_block_offdiag<double>(const double*, size_t, double*, size_t, size_t, bool, bool, cudaStream_t);
+
+template <typename R>
 cudaError_t ctrsm_colmajor(bool right, bool lower, int op, bool unit, size_t M, size_t N, R ar, R ai,
                            const R* A, size_t lda, R* B, size_t ldb, cudaStream_t s)
 {

@@ -362,6 +362,27 @@ const char* clblasB200LastGemmKernel(void);
  * src/library/blas/impl.c:81-129).  Returns the previous value. */
 int clblasB200SetGemmPath(int path);
 
+/* ---- complex TRMM: replaces clblasCtrmm (src/clBLAS.h:7839) and clblasZtrmm (:7909); same checks as clblasStrmm.
+ *      B <- alpha*op(A)*B (Left) or alpha*B*op(A) (Right), A triangular, interleaved (re, im) matrices;
+ *      clblasConjTrans conjugates. */
+clblasStatus clblasCtrmm(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    FloatComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasZtrmm(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    DoubleComplex alpha,
+    const clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
 /* ---- complex symmetric / Hermitian level-3: replace clblasCsyrk / Zsyrk (src/clBLAS.h:8417, :8485), clblasCherk / Zherk
  *      (:9389, :9458; real alpha and beta), clblasCsyr2k / Zsyr2k (:8722, :8798), clblasCher2k / Zher2k (:9545, :9623;
  *      real beta), clblasCsymm / Zsymm (:9052, :9124) and clblasChemm / Zhemm (:9224, :9305); reference front ends

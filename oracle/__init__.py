@@ -91,6 +91,8 @@ def _lib(impl: str) -> ctypes.CDLL:
         getattr(lib, f"{prefix}{p}gemm").restype = None
         getattr(lib, f"{prefix}{p}trsm").argtypes = [i, i, i, i, i, sz, sz, ct, ct, ptr, sz, ptr, sz]
         getattr(lib, f"{prefix}{p}trsm").restype = None
+        getattr(lib, f"{prefix}{p}trmm").argtypes = [i, i, i, i, i, sz, sz, ct, ct, ptr, sz, ptr, sz]
+        getattr(lib, f"{prefix}{p}trmm").restype = None
         if prefix == "oracle_":      # herm flag after trans / uplo; the reference's naive BLAS has only the symmetric updates
             getattr(lib, f"{prefix}{p}syrk").argtypes = [i, i, i, i, sz, sz, ct, ct, ptr, sz, ct, ct, ptr, sz]
             getattr(lib, f"{prefix}{p}syr2k").argtypes = [i, i, i, i, sz, sz, ct, ct, ptr, sz, ptr, sz, ct, ct, ptr, sz]
@@ -158,6 +160,14 @@ def ctrsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, l
     p = "c" if B.dtype == np.complex64 else "z"
     alpha = complex(alpha)
     fn = getattr(lib, f"{lib._prefix}{p}trsm")
+    fn(order, side, uplo, transA, diag, M, N, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb)
+
+
+def ctrmm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, impl: str = "port") -> None:
+    """Complex triangular product in place on the flat complex buffer B; alpha a Python complex number."""
+    lib = _lib(impl)
+    alpha = complex(alpha)
+    fn = getattr(lib, f"{lib._prefix}{'c' if B.dtype == np.complex64 else 'z'}trmm")
     fn(order, side, uplo, transA, diag, M, N, alpha.real, alpha.imag, _p(A, offA), lda, _p(B, offB), ldb)
 
 

@@ -498,3 +498,49 @@ void NAME(int order, int side, int uplo, int herm, size_t M, size_t N, T alr, T 
 
 DEFINE_CSYMM(oracle_csymm, float)
 DEFINE_CSYMM(oracle_zsymm, double)
+
+/* Complex TRMM: NaiveBlas::trmm<FloatComplex / DoubleComplex> (naive_blas.cpp:580-630) with the complex
+ * operators written out; a ConjTrans accessor conjugates what it reads, also after the Right-side flip. */
+#define DEFINE_CTRMM(NAME, T)                                                                  \
+void NAME(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, T alr, T ali, \
+          const T* A, size_t lda, T* B, size_t ldb)                                            \
+{                                                                                              \
+    size_t rowsA = (side == OLeft) ? M : N;                                                    \
+    size_t colsB = (side == OLeft) ? N : M;                                                    \
+    acc_t ma = make_acc(order, transA, lda);                                                   \
+    acc_t mb = make_acc(order, ONoTrans, ldb);                                                 \
+    const int cj = (transA == OConjTrans);                                                     \
+    int revPass = (uplo == OLower) ^ (transA != ONoTrans);                                     \
+    size_t i;                                                                                  \
+    if (side == ORight) {                                                                      \
+        ma.tra = !ma.tra;                                                                      \
+        mb.tra = !mb.tra;                                                                      \
+        revPass = !revPass;                                                                    \
+    }                                                                                          \
+    for (i = 0; i < rowsA; i++) {                                                              \
+        size_t row = revPass ? (rowsA - i - 1) : i;                                            \
+        size_t boundK = revPass ? row : (rowsA - row - 1);                                     \
+        long long j;                                                                           \
+        _Pragma("omp parallel for schedule(static)")                                           \
+        for (j = 0; j < (long long)colsB; j++) {                                               \
+            T tr = (T)0.0, ti = (T)0.0;                                                        \
+            size_t k;                                                                          \
+            for (k = 0; k <= boundK; k++) {                                                    \
+                size_t col = revPass ? k : (rowsA - k - 1);                                    \
+                T ar = (T)1.0, ai = (T)0.0;                                                    \
+                const T* b = B + 2 * at(mb, col, (size_t)j);                                   \
+                if (!((k == boundK) && (diag == OUnit))) {                                     \
+                    const T* a = A + 2 * at(ma, row, col);                                     \
+                    ar = a[0]; ai = cj ? -a[1] : a[1];                                         \
+                }                                                                              \
+                tr = tr + (ar * b[0] - ai * b[1]);                                             \
+                ti = ti + (ar * b[1] + b[0] * ai);                                             \
+            }                                                                                  \
+            B[2 * at(mb, row, (size_t)j)] = tr * alr - ti * ali;                               \
+            B[2 * at(mb, row, (size_t)j) + 1] = tr * ali + alr * ti;                           \
+        }                                                                                      \
+    }                                                                                          \
+}
+
+DEFINE_CTRMM(oracle_ctrmm, float)
+DEFINE_CTRMM(oracle_ztrmm, double)

@@ -160,4 +160,16 @@ REF_CSYRK(ref_zsyrk, DoubleComplex, doubleComplex, double)
 REF_CSYR2K(ref_csyr2k, FloatComplex, floatComplex, float)
 REF_CSYR2K(ref_zsyr2k, DoubleComplex, doubleComplex, double)
 
+#define REF_CTRMM(NAME, CT, MK, T)                                                                                   \
+    void NAME(int order, int side, int uplo, int transA, int diag, size_t M, size_t N, T alr, T ali, const T* A,         \
+              size_t lda, T* B, size_t ldb)                                                                              \
+    {                                                                                                                    \
+        NaiveBlas::trmm<NaiveBlas::CT>((NaiveBlas::clblasOrder)order, (NaiveBlas::clblasSide)side,                       \
+                                       (NaiveBlas::clblasUplo)uplo, (NaiveBlas::clblasTranspose)transA,                  \
+                                       (NaiveBlas::clblasDiag)diag, M, N, NaiveBlas::MK(alr, ali),                       \
+                                       reinterpret_cast<const NaiveBlas::CT*>(A), lda, reinterpret_cast<NaiveBlas::CT*>(B), ldb); \
+    }
+REF_CTRMM(ref_ctrmm, FloatComplex, floatComplex, float)
+REF_CTRMM(ref_ztrmm, DoubleComplex, doubleComplex, double)
+
 }  // extern "C"

@@ -312,3 +312,60 @@ def sweep_csymm_cases(kind, prec, mode):
             cases.append(csymm_case(kind, prec, order, side, uplo, M, N, [1 + 0j, 2 - 1j, -3j][seed % 3], [1 + 0j, 0j, 2 + 1j][seed % 3],
                                     pad=(seed % 5, seed % 3, seed % 7), off=(seed % 3, seed % 5, seed % 11), mode=mode, seed=seed))
     return cases
+
+
+# ------------------------------------------------------------------------------------- complex TRMM
+def ctrmm_case(prec, order, side, uplo, transA, diag, M, N, alpha=1 + 0j, pad=(0, 0), off=(0, 0), mode="int", seed=12345):
+    n = M if side == Left else N
+    return dict(kind="ctrmm", prec=prec, order=order, side=side, uplo=uplo, transA=transA, diag=diag, M=M, N=N, alpha=alpha,
+                lda=n + pad[0], ldb=_min_ld(order, NoTrans, M, N) + pad[1], offA=off[0], offB=off[1], mode=mode, seed=seed)
+
+
+def ctrmm_logical(c):
+    """Stored triangular A (NaN outside the referenced triangle and on a unit diagonal) and B."""
+    g = oracle.rng(c["seed"], 47)
+    n = c["M"] if c["side"] == Left else c["N"]
+    A = _draw(g, c["mode"], (n, n), c["prec"])
+    A[_other_triangle(n, c["uplo"])] = CNAN
+    if c["diag"] == Unit:
+        A[np.arange(n), np.arange(n)] = CNAN
+    return A, _draw(g, c["mode"], (c["M"], c["N"]), c["prec"])
+
+
+def ctrmm_buffers(c, logical=None, tail=3):
+    A, B = logical if logical is not None else ctrmm_logical(c)
+    return (oracle.pack(A, c["order"], NoTrans, c["lda"], c["offA"], pad_value=CNAN, tail=tail),
+            oracle.pack(B, c["order"], NoTrans, c["ldb"], c["offB"], pad_value=CNAN, tail=tail))
+
+
+def ctrmm_exact(c, logical):
+    A, B = logical
+    T = ctrsm_op_triangle(c, A).astype(np.complex128)
+    B = B.astype(np.complex128)
+    if c["side"] == Left:
+        return c["alpha"] * (T @ B), abs(c["alpha"]) * (np.abs(T) @ np.abs(B)), T
+    return c["alpha"] * (B @ T), abs(c["alpha"]) * (np.abs(B) @ np.abs(T)), T
+
+
+def golden_ctrmm_cases():
+    out = {}
+    k = 0
+    for prec in "cz":
+        for order, side, uplo, ta, diag in itertools.product(ORDERS, (Left, Right), (Upper, Lower), ALL_TRANS, (Unit, NonUnit)):
+            M, N = [(9, 5), (16, 17), (7, 12)][k % 3]
+            out[f"ctrmm_{prec}_{order}{side}{uplo}{ta}{diag}"] = ctrmm_case(prec, order, side, uplo, ta, diag, M, N,
+                                                                           alpha=[1 + 0j, -2 + 1j, 0.5j][k % 3], pad=(2, 3), off=(1, 4),
+                                                                           mode=["int", "uniform"][k % 2], seed=1900 + k)
+            k += 1
+    return out
+
+
+def sweep_ctrmm_cases(prec, mode):
+    cases = []
+    seed = 19000
+    for order, side, uplo, ta, diag in itertools.product(ORDERS, (Left, Right), (Upper, Lower), ALL_TRANS, (Unit, NonUnit)):
+        for (M, N) in ((8, 8), (17, 33), (64, 64), (130, 257), (300, 129)):
+            seed += 1
+            cases.append(ctrmm_case(prec, order, side, uplo, ta, diag, M, N, alpha=[1 + 0j, 2 - 1j, -3j][seed % 3],
+                                    pad=(seed % 5, seed % 7), off=(seed % 3, seed % 11), mode=mode, seed=seed))
+    return cases

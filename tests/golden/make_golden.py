@@ -124,6 +124,11 @@ def main():
             out[name] = hermitian_update_by_external_blas(c)
     for name, c in cc.golden_csymm_cases().items():
         out[name] = complex_symm_by_external_blas(c)
+    for name, c in cc.golden_ctrmm_cases().items():
+        A, B = cc.ctrmm_buffers(c)
+        oracle.ctrmm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A, c["offA"], c["lda"],
+                     B, c["offB"], c["ldb"], impl="ref")
+        out[name] = B
     path = os.path.join(os.path.dirname(__file__), "level3_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} cases, {os.path.getsize(path)} bytes")

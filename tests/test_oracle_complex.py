@@ -84,3 +84,39 @@ def test_trsm_solves_the_system(built_oracle):
         X = oracle.view(run_trsm(c, "port", logical), c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
         assert np.all(np.isfinite(X)), c
         assert cc.ctrsm_backward_ratio(c, X, cc.ctrsm_op_triangle(c, logical[0]), logical[1]) <= 1.0, c
+
+
+# ------------------------------------------------------------------------------------- complex TRMM
+def run_trmm(c, impl, logical=None):
+    A, B = cc.ctrmm_buffers(c, logical)
+    oracle.ctrmm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], A, c["offA"], c["lda"],
+                 B, c["offB"], c["ldb"], impl=impl)
+    return B
+
+
+def test_trmm_port_matches_golden(built_oracle):
+    """Golden outputs made with NaiveBlas::trmm<FloatComplex/DoubleComplex> (naive_blas.cpp:580-630)."""
+    g = np.load(GOLDEN)
+    items = list(cc.golden_ctrmm_cases().items())
+    assert len(items) == 96
+    for name, c in items:
+        assert same_bits(run_trmm(c, "port"), g[name]), name
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference's own naive_blas.cpp was not compiled here")
+def test_trmm_port_matches_reference_code(built_oracle):
+    for prec in "cz":
+        for c in cc.sweep_ctrmm_cases(prec, "uniform")[::7]:
+            if max(c["M"], c["N"]) > 140:
+                continue
+            assert same_bits(run_trmm(c, "port"), run_trmm(c, "ref")), c
+
+
+def test_trmm_integer_inputs_are_exact_and_poison_is_not_read(built_oracle):
+    for c in cc.sweep_ctrmm_cases("z", "int")[::5]:
+        if max(c["M"], c["N"]) > 140:
+            continue
+        logical = cc.ctrmm_logical(c)
+        X = oracle.view(run_trmm(c, "port", logical), c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
+        want, _, _ = cc.ctrmm_exact(c, logical)
+        assert np.array_equal(X, want), c
