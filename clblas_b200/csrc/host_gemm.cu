@@ -99,7 +99,14 @@ cudaError_t gemm_host_colmajor(bool ta, bool tb, size_t M, size_t N, size_t K, T
     size_t ns = !product ? 1 : K >= 8192 ? 4 : K >= 2048 ? 2 : 1;
     if (const char* v = getenv("CLBLAS_B200_HOST_W")) { const size_t x = strtoull(v, nullptr, 10); if (x) w = std::min(round_up(x, 128), round_up(N, 128)); }
     if (const char* v = getenv("CLBLAS_B200_HOST_NS")) { const size_t x = strtoull(v, nullptr, 10); if (x && product) ns = x; }
-    const size_t nb = (N + w - 1) / w;
+    // Block boundaries.  The first block is half as wide again as the others: its products are the ones that
+    // wait for the slabs of A, so they should last as long as those uploads; what is left at the end makes a
+    // narrower last block, which shortens the download that nothing overlaps.
+    std::vector<size_t> bounds;
+    bounds.push_back(0);
+    if (N > 2 * w && getenv("CLBLAS_B200_HOST_W") == nullptr) bounds.push_back(w + w / 2);
+    while (bounds.back() < N) bounds.push_back(std::min(N, bounds.back() + w));
+    const size_t nb = bounds.size() - 1;
     const size_t kslab = round_up((K + ns - 1) / ns, 64);
 
     // One block and one slab leave nothing to overlap: everything goes on the caller's stream, without events.
@@ -130,7 +137,7 @@ cudaError_t gemm_host_colmajor(bool ta, bool tb, size_t M, size_t N, size_t K, T
     }
 
     for (size_t j = 0; j < nb; j++) {
-        const size_t j0 = j * w, wj = std::min(w, N - j0);
+        const size_t j0 = bounds[j], wj = bounds[j + 1] - j0;
         for (size_t s = 0; s < ns; s++) {
             const size_t k0 = std::min(s * kslab, K), kw = std::min(kslab, K - k0);
             if (product && kw == 0) continue;
