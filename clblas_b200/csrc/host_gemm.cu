@@ -205,7 +205,20 @@ cudaError_t trsm_host_colmajor(bool right, bool lower, bool trans, bool unit, si
     const bool solve = alpha != T(0);
     const size_t nbt = std::min<size_t>(8, std::max<size_t>(1, other / 4096));
     const size_t w = round_up((other + nbt - 1) / nbt, 128);
-    const size_t nb = (other + w - 1) / w;
+    // Block boundaries: a first block of w/4 (the solve can start as soon as A and that little piece of B have
+    // landed), full blocks of w, and a tail of two shrinking blocks (the last download overlaps nothing).
+    std::vector<size_t> bounds;
+    bounds.push_back(0);
+    if (other > 2 * w) {
+        bounds.push_back(std::max<size_t>(512, round_up(w / 4, 128)));
+        while (other - bounds.back() > w + w / 2) bounds.push_back(bounds.back() + w);
+        const size_t rem = other - bounds.back();
+        if (rem >= 1024) bounds.push_back(bounds.back() + round_up(rem * 2 / 3, 128));
+        bounds.push_back(other);
+    } else {
+        while (bounds.back() < other) bounds.push_back(std::min(other, bounds.back() + w));
+    }
+    const size_t nb = bounds.size() - 1;
     const bool single = nb == 1;
 
     HostPipe* pp = nullptr;
@@ -241,7 +254,7 @@ cudaError_t trsm_host_colmajor(bool right, bool lower, bool trans, bool unit, si
         }
     }
     for (size_t j = 0; j < nb; j++) {
-        const size_t j0 = j * w, wj = std::min(w, other - j0);
+        const size_t j0 = bounds[j], wj = bounds[j + 1] - j0;
         // block j of B: columns j0.. (Left) or rows j0.. (Right)
         T* db = right ? dB + j0 : dB + j0 * dldb;
         T* hb = right ? hB + j0 : hB + j0 * ldb;
