@@ -88,6 +88,9 @@ struct ScopedNoAlloc {
     ~ScopedNoAlloc();
 };
 
+// False while a ScopedNoAlloc is alive on the calling thread or a kernel family is forced.
+bool gemm_may_allocate();
+
 // Dispatcher keyed on precision, transposes, shape and alignment.
 template <typename T>
 cudaError_t gemm_colmajor(const GemmProblem<T>& p, cudaStream_t s);

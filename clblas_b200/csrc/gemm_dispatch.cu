@@ -136,6 +136,8 @@ cudaError_t gemm_any(const GemmProblem<T>& p, cudaStream_t s)
 
 }  // namespace
 
+bool gemm_may_allocate() { return t_forbid_alloc == 0 && forced_gemm_path() == PATH_AUTO; }
+
 ScopedNoAlloc::ScopedNoAlloc() { ++t_forbid_alloc; }
 ScopedNoAlloc::~ScopedNoAlloc() { --t_forbid_alloc; }
 

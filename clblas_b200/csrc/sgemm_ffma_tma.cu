@@ -31,6 +31,7 @@
 #include "common.h"
 #include "tma_pipeline.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 
 namespace cb200 {
@@ -69,7 +70,7 @@ template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS, bool TRI>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                      unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg)
+                      unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg, unsigned splits, size_t split_stride)
 {
     int tri = TRI ? tri_arg : TRI_FULL;
     constexpr int STAGE_BYTES = stage_bytes(BN);
@@ -97,7 +98,13 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         if (tri_tile_outside(tri, m0, BM, n0, BN)) return;      // triangular update: nothing of this tile is referenced
         if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
     }
-    const int nk = (int)((K + BK - 1) / BK);
+    // Split-K launches (gridDim.y = splits): this CTA owns K slabs [kt0, kt0 + nk) and writes its partial tile
+    // into plane blockIdx.y of a workspace; a reduction kernel sums the planes in a fixed order.
+    const int nk_total = (int)((K + BK - 1) / BK);
+    const int nk_per = (nk_total + (int)splits - 1) / (int)splits;
+    const int kt0 = (int)blockIdx.y * nk_per;
+    const int nk = max(0, min(nk_per, nk_total - kt0));
+    C += (size_t)blockIdx.y * split_stride;
     // Every other wave of CTAs walks K backwards: it starts on the K range the wave before it
     // finished on, which is what L2 still holds, instead of re-streaming those panels from DRAM.
     const bool reverse_k = wave != 0 && ((blockIdx.x / wave) & 1);
@@ -117,7 +124,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         unsigned char* sa = smem + s * STAGE_BYTES;
         unsigned char* sb = sa + A_BYTES;
         mbar_expect_tx(&full[s], STAGE_BYTES);
-        const int k0 = (reverse_k ? nk - 1 - kt : kt) * BK;
+        const int k0 = (kt0 + (reverse_k ? nk - 1 - kt : kt)) * BK;
         if (TA) tma_load_2d(sa, &mapA, k0, (int)m0, &full[s]); else tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
         if (TB) tma_load_2d(sb, &mapB, (int)n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, (int)n0, &full[s]);
     };
@@ -274,8 +281,24 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     }
 }
 
+// C <- alpha * (plane 0 + plane 1 + ...) + beta * C, planes summed in index order (deterministic).
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ W, size_t ldw, size_t stride, unsigned splits,
+                                                            float* __restrict__ C, size_t ldc, size_t M, size_t N, float alpha, float beta)
+{
+    const size_t total = M * N;
+    for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < total; e += (size_t)gridDim.x * 256) {
+        const size_t i = e % M, j = e / M;
+        float acc = W[i + j * ldw];
+        for (unsigned sp = 1; sp < splits; sp++) acc += W[sp * stride + i + j * ldw];
+        float* c = C + i + j * ldc;
+        float r = alpha * acc;
+        if (beta != 0.f) r = fmaf(beta, *c, r);
+        *c = r;
+    }
+}
+
 template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS, bool TRI>
-cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
+cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s, unsigned splits = 1)
 {
     void* enc = get_tensor_map_encoder();
     CUtensorMap mapA, mapB;
@@ -298,8 +321,28 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s)
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
+    if (splits > 1) {
+        // partial products into `splits` planes of a workspace, then one deterministic reduction into C
+        const size_t ldw = (p.M + 3) / 4 * 4, stride = ldw * p.N;
+        float* W = nullptr;
+        cudaError_t e = ws_alloc(reinterpret_cast<void**>(&W), splits * stride * sizeof(float), s);
+        if (e != cudaSuccess) return e;
+        sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI><<<dim3((unsigned)(tilesM * tilesN), splits), THREADS, SMEM, s>>>(
+            mapA, mapB, W, ldw, p.M, p.N, p.K, 1.f, 0.f, (unsigned)tilesM, (unsigned)tilesN, 0u, TRI_FULL, splits, stride);
+        count_launch();
+        e = cudaGetLastError();
+        if (e == cudaSuccess) {
+            const unsigned blocks = (unsigned)std::min<size_t>((p.M * p.N + 255) / 256, (size_t)sm_count() * 8);
+            splitk_reduce_kernel<<<blocks, 256, 0, s>>>(W, ldw, stride, splits, p.C, p.ldc, p.M, p.N, p.alpha, p.beta);
+            count_launch();
+            e = cudaGetLastError();
+        }
+        const cudaError_t e2 = ws_free(W, s);
+        return e != cudaSuccess ? e : e2;
+    }
     sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
-        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * MIN_CTAS), p.tri);
+        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * MIN_CTAS), p.tri,
+        1u, (size_t)0);
     count_launch();
     return cudaGetLastError();
 }
@@ -491,8 +534,14 @@ cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s)
 }
 
 template <int BN, int STAGES, int MIN_CTAS>
-cudaError_t launch_any(const GemmProblem<float>& p, cudaStream_t s)
+cudaError_t launch_any(const GemmProblem<float>& p, cudaStream_t s, unsigned splits = 1)
 {
+    if (splits > 1) {
+        if (!p.ta && !p.tb) return launch<false, false, BN, STAGES, MIN_CTAS, false>(p, s, splits);
+        if (!p.ta && p.tb) return launch<false, true, BN, STAGES, MIN_CTAS, false>(p, s, splits);
+        if (p.ta && !p.tb) return launch<true, false, BN, STAGES, MIN_CTAS, false>(p, s, splits);
+        return launch<true, true, BN, STAGES, MIN_CTAS, false>(p, s, splits);
+    }
     if (p.tri != TRI_FULL) {
         if (!p.ta && !p.tb) return launch<false, false, BN, STAGES, MIN_CTAS, true>(p, s);
         if (!p.ta && p.tb) return launch<false, true, BN, STAGES, MIN_CTAS, true>(p, s);
@@ -521,8 +570,18 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     // Fewer 128-wide tiles than SMs: halve the tile width so that twice as many CTAs share the work
     // (three of them fit an SM).  With A K-contiguous the 4-k fragments need the one-CTA register budget.
     if (min_bn < 128 && tiles128 < 120) {
-        if (p.ta) return launch_any<64, 5, 1>(p, s);
-        return launch_any<64, 3, 2>(p, s);
+        // Tiles for less than a third of the SMs' CTA slots and a long K loop: split K over 2-4 CTAs per tile (partial
+        // tiles in a workspace, summed in a fixed order by a second kernel).  Measured N/N: 768 x 768 x 2048 18.6 -> 34.2,
+        // 512^3 7.2 -> 10.5 TFLOP/s; with more tiles than that the second kernel costs more than the split gains
+        // (1024^3, 128 tiles: 31.3 -> 29.9), so those stay unsplit.
+        const size_t tiles64 = tilesM * ((p.N + 63) / 64);
+        const size_t slots = (size_t)sm_count() * (p.ta ? 1 : 2);
+        unsigned splits = 1;
+        if (p.tri == TRI_FULL && tiles64 * 3 <= slots && gemm_may_allocate() && p.C != p.A && p.C != p.B &&
+            getenv("CLBLAS_B200_NO_SPLITK") == nullptr)
+            splits = (unsigned)std::max<size_t>(1, std::min<size_t>(std::min<size_t>(4, slots / tiles64), p.K / 256));
+        if (p.ta) return launch_any<64, 5, 1>(p, s, splits);
+        return launch_any<64, 3, 2>(p, s, splits);
     }
     // A K-contiguous operand is fetched 4 k at a time (32 fragment registers on top of the
     // accumulators), which the two-CTA budget of 128 registers holds only for B; measured at 8192^3
