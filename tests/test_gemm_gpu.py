@@ -200,6 +200,20 @@ def test_tma_paths_real_valued(lib, prec):
     assert lib.device_fault() == 0
 
 
+def test_sgemm_split_k_exact(lib):
+    """Few tiles and a long K: the SGEMM path splits K over several CTAs per tile (partial tiles in a workspace, ordered
+    reduction).  Integer inputs must still equal the oracle, for all transposes, ragged sizes and beta = 0."""
+    seed = 22000
+    for ta in (NoTrans, Trans):
+        for tb in (NoTrans, Trans):
+            for M, N, K in ((512, 512, 512), (768, 300, 2048), (130, 257, 1100), (64, 64, 4097)):
+                seed += 1
+                check_exact(lib, _aligned_case("s", ColumnMajor, ta, tb, M, N, K, seed))
+                assert lib.last_gemm_kernel() == "sgemm_ffma_tma"
+                check_exact(lib, _aligned_case("s", RowMajor, ta, tb, M, N, K, seed, beta=0.0))
+    assert lib.device_fault() == 0
+
+
 def test_config2_shape_family_dgemm_tn(lib):
     """DGEMM column-major T/N, normal(0,1), alpha = beta = 1, tight leading dimensions (BASELINE
     config 2) at 1024^3, where the float64 host check is cheap; the 8192^3 run is checked through
