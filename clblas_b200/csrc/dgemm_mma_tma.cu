@@ -23,6 +23,9 @@
 //    i.e. rows of 132 (68, 36) doubles of which 128 (64, 32) are used: the 4 extra elements make the
 //    row pitch = 32 (mod 128) bytes, which is what separates the four k rows of a fragment.
 #include "common.h"
+
+#include <algorithm>
+#include <cstdlib>
 #include "tma_pipeline.cuh"
 
 namespace cb200 {
@@ -189,6 +192,217 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tail of the grid, shared between all SMs ("stream-K" for the last partial wave).
+//
+// With one CTA per tile, a grid of T tiles on S SMs runs ceil(T / S) waves; the last one keeps only T mod S SMs
+// busy (DGEMM 2048^3: 256 tiles = 1.73 waves, two waves of time).  The main kernel therefore takes the first
+// floor(T / S) * S tiles and this kernel the R = T mod S remaining ones: their R * nk K-slabs are cut into equal
+// consecutive shares, one per CTA, so a CTA computes part of one tile (sometimes the end of one and the start of
+// the next).  A CTA that owns a whole tile writes C directly.  Otherwise it stores its partial tile into its slot of
+// a workspace and takes a ticket from the tile's counter; the CTA that draws the last ticket adds the slots in slot
+// order -- a fixed order, so the result does not depend on which CTA finishes last -- and writes C.  Nobody waits
+// for anybody: there is no spin loop in this kernel besides the bounded mbarrier waits of the TMA ring.
+constexpr int SK_MIN_SLABS = 8;          // smallest share of a CTA, in K slabs of 16
+
+__device__ __forceinline__ void tile_coords(unsigned tile, unsigned tilesM, unsigned tilesN, unsigned& tm, unsigned& tn)
+{
+    const unsigned per_group = GROUP_M * tilesN;
+    const unsigned g = tile / per_group;
+    const unsigned first = g * GROUP_M;
+    const unsigned rows = min((unsigned)GROUP_M, tilesM - first);
+    const unsigned r = tile - g * per_group;
+    tm = first + r % rows;
+    tn = r / rows;
+}
+
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(THREADS, 1)
+dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                     double* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, double alpha, double beta,
+                     unsigned tilesM, unsigned tilesN, unsigned tile0, unsigned units, unsigned upc, unsigned maxc,
+                     double* __restrict__ ws, unsigned* __restrict__ counters)
+{
+    constexpr int BN = 128;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int STAGE_BYTES = stage_bytes(BN);
+    constexpr int PITCH_B = BN + 4;
+    constexpr int WN = BN / 4, NI = WN / 8;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    unsigned* s_ticket = reinterpret_cast<unsigned*>(empty + STAGES);
+
+    const unsigned nk = (unsigned)((K + BK - 1) / BK);
+    const unsigned u0 = blockIdx.x * upc, u1 = min(u0 + upc, units);
+    if (u0 >= u1) return;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CONSUMER_WARPS);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == CONSUMER_WARPS) {
+        // ------------------------------- producer -------------------------------
+        if (lane == 0) {
+            tma_prefetch_descriptor(&mapA);
+            tma_prefetch_descriptor(&mapB);
+            unsigned t = u0 / nk, kt = u0 % nk, tm, tn;
+            tile_coords(tile0 + t, tilesM, tilesN, tm, tn);
+            for (unsigned u = u0; u < u1; u++) {
+                const unsigned i = u - u0;
+                const int s = (int)(i % STAGES);
+                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1)) break;
+                unsigned char* sa = smem + s * STAGE_BYTES;
+                unsigned char* sb = sa + A_BYTES;
+                const uint32_t bytes = (TA ? BK * BM : MC_PITCH * BK) * 8 + (TB ? PITCH_B * BK : BK * BN) * 8;
+                mbar_expect_tx(&full[s], bytes);
+                const int k0 = (int)(kt * BK), m0 = (int)(tm * BM), n0 = (int)(tn * BN);
+                if (TA) tma_load_2d(sa, &mapA, k0, m0, &full[s]); else tma_load_2d(sa, &mapA, m0, k0, &full[s]);
+                if (TB) tma_load_2d(sb, &mapB, n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, n0, &full[s]);
+                if (++kt == nk) { kt = 0; t++; if (u + 1 < u1) tile_coords(tile0 + t, tilesM, tilesN, tm, tn); }
+            }
+        }
+        return;
+    }
+
+    // --------------------------------- consumers ---------------------------------
+    const int wm = warp % 2, wn = warp / 2;
+    const int g = lane / 4, kk = lane % 4;
+    const int pg = perm8(g);
+    const int ctid = threadIdx.x;                    // 0..255: the consumer warps are warps 0..7
+    int offA, offB;
+    if (TA) offA = (wm * 64 + pg) * 128 + ((((kk >> 1) ^ (pg & 1))) << 4) + (kk & 1) * 8;
+    else    offA = kk * (MC_PITCH * 8) + (wm * 64 + g) * 8;
+    if (!TB) offB = (wn * WN + pg) * 128 + ((((kk >> 1) ^ (pg & 1))) << 4) + (kk & 1) * 8;
+    else     offB = kk * (PITCH_B * 8) + (wn * WN + g) * 8;
+    const int xr = (pg & 6) << 4;
+
+    double acc[8][NI][2];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < NI; j++) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+    // C = alpha*acc + beta*C for the tile at (m0, n0); beta == 0 never reads C
+    auto epilogue = [&](size_t m0, size_t n0) {
+        const bool useC = (beta != 0.0);
+#pragma unroll
+        for (int ni = 0; ni < NI; ni++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int j = 2 * kk + e;
+                const size_t col = n0 + wn * WN + ni * 8 + (!TB ? perm8(j) : j);
+                if (col >= N) continue;
+                double* cc = C + col * ldc;
+#pragma unroll
+                for (int mi = 0; mi < 8; mi++) {
+                    const size_t row = m0 + wm * 64 + mi * 8 + (TA ? pg : g);
+                    if (row >= M) continue;
+                    double r = alpha * acc[mi][ni][e];
+                    if (useC) r = fma(beta, cc[row], r);
+                    cc[row] = r;
+                }
+            }
+    };
+
+    // Outer loop over this CTA's segments (one per tile it touches), inner loop over the K slabs of a segment: the
+    // inner loop is the main kernel's, so it keeps that kernel's register allocation.
+    unsigned u = u0;
+    while (u < u1) {
+        const unsigned t = u / nk, seg_first = u - t * nk;
+        const unsigned seg_end = min(u1, (t + 1) * nk);          // one past the last unit of this segment
+        for (unsigned i = u - u0; i < seg_end - u0; i++) {
+            const int s = (int)(i % STAGES);
+            if (!mbar_wait(&full[s], (i / STAGES) & 1)) return;   // flagged; C of this tile stays unwritten
+            const unsigned char* sa = smem + s * STAGE_BYTES;
+            const unsigned char* sb = sa + A_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < BK / 4; ks++) {
+                double a[8], b[NI];
+#pragma unroll
+                for (int mi = 0; mi < 8; mi++) {
+                    const int o = TA ? offA + mi * 1024 + (((ks * 32) ^ xr)) : offA + ks * 4 * (MC_PITCH * 8) + mi * 64;
+                    a[mi] = *reinterpret_cast<const double*>(sa + o);
+                }
+#pragma unroll
+                for (int ni = 0; ni < NI; ni++) {
+                    const int o = !TB ? offB + ni * 1024 + (((ks * 32) ^ xr)) : offB + ks * 4 * (PITCH_B * 8) + ni * 64;
+                    b[ni] = *reinterpret_cast<const double*>(sb + o);
+                }
+#pragma unroll
+                for (int mi = 0; mi < 8; mi++)
+#pragma unroll
+                    for (int ni = 0; ni < NI; ni++) dmma(acc[mi][ni][0], acc[mi][ni][1], a[mi], b[ni]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+
+        // ---- end of this CTA's segment [seg_first, seg_last] of tile t
+        const unsigned seg_last = seg_end - 1 - t * nk;
+        unsigned tm, tn;
+        tile_coords(tile0 + t, tilesM, tilesN, tm, tn);
+        const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
+        if (seg_first == 0 && seg_last == nk - 1) {
+            epilogue(m0, n0);
+        } else {
+            const unsigned first_cta = (t * nk) / upc;
+            const unsigned idx = blockIdx.x - first_cta;
+            const unsigned count = ((t + 1) * nk - 1) / upc - first_cta + 1;
+            double* slot = ws + ((size_t)t * maxc + idx) * (size_t)(BM * BN);
+#pragma unroll
+            for (int mi = 0; mi < 8; mi++)
+#pragma unroll
+                for (int ni = 0; ni < NI; ni++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) __stcg(slot + ((mi * NI + ni) * 2 + e) * 256 + ctid, acc[mi][ni][e]);
+            __threadfence();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (ctid == 0) *s_ticket = atomicAdd(&counters[t], 1u);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (*s_ticket == count - 1) {
+                __threadfence();
+                // slot by slot (the 64 loads of a slot are independent and overlap; a loop over the slots inside each
+                // element would be a chain of dependent L2 latencies), always in slot order
+                const double* base = ws + (size_t)t * maxc * (size_t)(BM * BN) + ctid;
+#pragma unroll
+                for (int mi = 0; mi < 8; mi++)
+#pragma unroll
+                    for (int ni = 0; ni < NI; ni++) acc[mi][ni][0] = acc[mi][ni][1] = 0.0;
+                for (unsigned c = 0; c < count; c++) {
+                    const double* sl = base + (size_t)c * (BM * BN);
+                    double v[8][NI][2];
+#pragma unroll
+                    for (int mi = 0; mi < 8; mi++)
+#pragma unroll
+                        for (int ni = 0; ni < NI; ni++)
+#pragma unroll
+                            for (int e = 0; e < 2; e++) v[mi][ni][e] = __ldcg(sl + ((mi * NI + ni) * 2 + e) * 256);
+#pragma unroll
+                    for (int mi = 0; mi < 8; mi++)
+#pragma unroll
+                        for (int ni = 0; ni < NI; ni++)
+#pragma unroll
+                            for (int e = 0; e < 2; e++) acc[mi][ni][e] += v[mi][ni][e];
+                }
+                epilogue(m0, n0);
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");      // s_ticket is reused by the next segment
+        }
+#pragma unroll
+        for (int mi = 0; mi < 8; mi++)
+#pragma unroll
+            for (int ni = 0; ni < NI; ni++) acc[mi][ni][0] = acc[mi][ni][1] = 0.0;
+        u = seg_end;
+    }
+}
+
 template <bool TA, bool TB, int BN, bool TRI>
 cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
 {
@@ -211,7 +425,45 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
-    dgemm_mma_tma_kernel<TA, TB, BN, TRI><<<(unsigned)(tilesM * tilesN), THREADS, smem_bytes(BN), s>>>(
+    size_t main_tiles = tilesM * tilesN;
+    if (BN == 128 && !TRI) {
+        // Whole waves go to the kernel above, the last partial wave to the stream-K kernel.
+        const size_t T = tilesM * tilesN, S = (size_t)sm_count(), R = T % S, nk = (p.K + BK - 1) / BK;
+        if (T > S && R != 0 && R * 20 <= S * 17 && nk >= 2 * SK_MIN_SLABS && nk < (1u << 20) && gemm_may_allocate() &&
+            p.C != p.A && p.C != p.B && getenv("CLBLAS_B200_NO_STREAMK") == nullptr) {
+            const size_t units = R * nk;
+            const size_t ctas = std::max<size_t>(1, std::min<size_t>(S, units / SK_MIN_SLABS));
+            const size_t upc = (units + ctas - 1) / ctas;
+            const size_t maxc = (nk + upc - 1) / upc + 1;
+            const size_t ws_doubles = R * maxc * (size_t)(BM * 128);
+            double* ws = nullptr;
+            cudaError_t e = ws_alloc(reinterpret_cast<void**>(&ws), ws_doubles * sizeof(double) + R * sizeof(unsigned) + 256, s);
+            if (e == cudaSuccess) {
+                unsigned* counters = reinterpret_cast<unsigned*>(ws + ws_doubles);
+                e = cudaMemsetAsync(counters, 0, R * sizeof(unsigned), s);
+                static bool sk_attr_done[64] = {};
+                if (e == cudaSuccess && (dev < 0 || dev >= 64 || !sk_attr_done[dev])) {
+                    e = cudaFuncSetAttribute(dgemm_streamk_kernel<TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128));
+                    if (e == cudaSuccess && dev >= 0 && dev < 64) sk_attr_done[dev] = true;
+                }
+                if (e == cudaSuccess) {
+                    main_tiles = T - R;
+                    dgemm_mma_tma_kernel<TA, TB, BN, TRI><<<(unsigned)main_tiles, THREADS, smem_bytes(BN), s>>>(
+                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)S, p.tri);
+                    count_launch();
+                    dgemm_streamk_kernel<TA, TB><<<(unsigned)((units + upc - 1) / upc), THREADS, smem_bytes(128), s>>>(
+                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)main_tiles,
+                        (unsigned)units, (unsigned)upc, (unsigned)maxc, ws, counters);
+                    count_launch();
+                    e = cudaGetLastError();
+                }
+                const cudaError_t e2 = ws_free(ws, s);
+                return e != cudaSuccess ? e : e2;
+            }
+            cudaGetLastError();        // no workspace: one CTA per tile as usual
+        }
+    }
+    dgemm_mma_tma_kernel<TA, TB, BN, TRI><<<(unsigned)main_tiles, THREADS, smem_bytes(BN), s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 1), p.tri);
     count_launch();
     return cudaGetLastError();

@@ -214,6 +214,26 @@ def test_sgemm_split_k_exact(lib):
     assert lib.device_fault() == 0
 
 
+def test_dgemm_stream_k_tail_exact(lib):
+    """More than one wave of tiles and a partial last wave: the DGEMM path gives the last tiles to the kernel that shares
+    their K range between CTAs (partial tiles in a workspace, the last arrival sums them in slot order).  Integer inputs
+    must equal the oracle for all transposes, ragged edges included, and twice the same call must agree bit for bit."""
+    seed = 23000
+    for ta in (NoTrans, Trans):
+        for tb in (NoTrans, Trans):
+            for M, N, K in ((2048, 2048, 512), (1990, 2300, 700), (1280, 3000, 1030), (2560, 1920, 256)):
+                seed += 1
+                check_exact(lib, _aligned_case("d", ColumnMajor, ta, tb, M, N, K, seed))
+                assert lib.last_gemm_kernel() == "dgemm_mma_tma"
+    check_exact(lib, _aligned_case("d", RowMajor, Trans, NoTrans, 2100, 2100, 900, 23099, beta=0.0))
+    c = _aligned_case("d", ColumnMajor, NoTrans, Trans, 2304, 2176, 1111, 23100, mode="uniform", alpha=1.5, beta=0.5)
+    bufs = cases.gemm_buffers(c)
+    _, first = run_gemm_gpu(lib, c, bufs)
+    _, second = run_gemm_gpu(lib, c, bufs)
+    assert same_bits(first, second)
+    assert lib.device_fault() == 0
+
+
 def test_config2_shape_family_dgemm_tn(lib):
     """DGEMM column-major T/N, normal(0,1), alpha = beta = 1, tight leading dimensions (BASELINE
     config 2) at 1024^3, where the float64 host check is cheap; the 8192^3 run is checked through
