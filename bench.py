@@ -35,11 +35,11 @@ NOMINAL = {"fp32": 148 * 128 * 2 * 1.965e9 / 1e12, "fp64": 148 * 64 * 2 * 1.965e
 # None where no capture of that workload exists (cfg4 is 127 launches of different shapes; cfg5 runs 1.2 s).
 NCU_TRAFFIC_BYTES = {
     "cfg1": int(12.63e6),                          # sgemm_ffma_tma N/N 1024^3 (operands L2 resident, C not written back yet)
-    "cfg2": int(6.34e9 + 528.82e6),                # dgemm_mma_tma T/N 8192^3
+    "cfg2": int(6.107e9 + 509.2e6 + 620.1e6 + 12.4e6),   # dgemm_mma_tma T/N 8192^3: main kernel (3996 tiles) + stream-K tail (100 tiles)
     "cfg3": int(94.89e6 + 18.84e6),                # sgemm_ffma_tma on the repacked operands of config 3
     "cfg4": None,
     "cfg5": None,
-    "sgemm8192": int(3.06e9 + 269.16e6),           # sgemm_ffma_tma N/T 8192^3
+    "sgemm8192": int(3.257e9 + 263.6e6),           # sgemm_nt_16x8 N/T 8192^3
 }
 NCU_TRAFFIC_BYTES_3XTF32 = {"sgemm8192": int(2.70e9 + 256.35e6)}
 
