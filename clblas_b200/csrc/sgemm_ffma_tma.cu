@@ -42,6 +42,7 @@ constexpr int BM = 128, BK = 32;
 constexpr int A_BYTES = BM * BK * 4;                // 16 KB
 constexpr int THREADS = 256;
 constexpr int GROUP_M = 16;
+constexpr int REFILL_KC = 6;                         // eighth of the slab (0..7) in which the freed slot is refilled
 
 constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 4; }
 constexpr int smem_bytes(int stages, int bn) { return stages * stage_bytes(bn) + 1024 + 256; }
@@ -161,10 +162,10 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         const unsigned char* sb = sa + A_BYTES;
 #pragma unroll
         for (int kc = 0; kc < BK / 4; kc++) {
-            // Refill the slot consumed during the previous slab with the slab STAGES-1 ahead.  Done a
-            // quarter of the way into this slab: by then the other warps have released that slot,
-            // so the producer thread rarely waits.
-            if (kc == 2 && threadIdx.x == 0 && kt + STAGES - 1 < nk) {
+            // Refill the slot consumed during the previous slab with the slab STAGES-1 ahead.  Done late in
+            // this slab (by then even a lagging warp has released that slot) and by a different warp every
+            // slab, so that a wait, when there is one, does not always hold back the same warp.
+            if (kc == REFILL_KC && threadIdx.x == 32 * (kt & 7) && kt + STAGES - 1 < nk) {
                 if (kt >= 1) alive = mbar_wait(&empty[(kt - 1) % STAGES], ((kt - 1) / STAGES) & 1);
                 if (alive) issue(kt + STAGES - 1);
             }
