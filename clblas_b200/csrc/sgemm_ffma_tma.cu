@@ -8,8 +8,9 @@
 //
 // CTA = 128 x BN tile of C (BN = 128, or 64 for problems too small to give every SM a 128-wide
 // tile), K in slabs of 32, 256 threads (16 x 16, an 8 x BN/16 register tile each).
-// Thread 0 doubles as the producer: part-way through every slab it refills the ring slot that was
-// consumed one slab earlier (two TMA bulk-tensor loads; full/empty mbarriers, bounded waits).
+// There is no producer warp: late in every slab one thread (lane 0 of a different warp each slab) refills
+// the ring slot that was consumed one slab earlier (two TMA bulk-tensor loads; full/empty mbarriers, bounded
+// waits).
 // Configurations of the same code:
 //   * 3-stage ring, at most 128 registers per thread, TWO CTAs per SM: four warps per SM
 //     sub-partition hide each other's shared-memory latency and barrier waits;
