@@ -73,11 +73,15 @@ trtri_diag_kernel(const T* __restrict__ A, size_t lda, size_t n, bool lower, boo
 #pragma unroll 1
         for (int kk = 0; kk < 16; kk++) {
             const int k = kb * 16 + kk;
+            // Row k of X is zero beyond column k, so only the column groups jj <= k / 32 = kb / 2 take part
+            // (a compile-time bound: kb is an unrolled index).
+            const int jmax = kb >> 1;
             T* rb = rowbuf + (k & 1) * NB;
             if (tr == kk) {
                 const T rd = T(1) / Ls[k * NB + k];
 #pragma unroll
                 for (int jj = 0; jj < 4; jj++) {
+                    if (jj > jmax) continue;
                     x[kb][jj] = x[kb][jj] * rd;
                     rb[tc + 32 * jj] = x[kb][jj];
                 }
@@ -85,14 +89,17 @@ trtri_diag_kernel(const T* __restrict__ A, size_t lda, size_t n, bool lower, boo
             __syncthreads();
             T xr[4];
 #pragma unroll
-            for (int jj = 0; jj < 4; jj++) xr[jj] = rb[tc + 32 * jj];
+            for (int jj = 0; jj < 4; jj++) xr[jj] = (jj > jmax) ? T(0) : rb[tc + 32 * jj];
 #pragma unroll
             for (int ii = 0; ii < 8; ii++) {
                 if (ii < kb) continue;                       // rows above the current block row are final
                 if (ii == kb && tr <= kk) continue;          // rows up to k inside the block row are final
                 const T l = Ls[k * NB + tr + 16 * ii];
 #pragma unroll
-                for (int jj = 0; jj < 4; jj++) x[ii][jj] = fma(-l, xr[jj], x[ii][jj]);
+                for (int jj = 0; jj < 4; jj++) {
+                    if (jj > jmax) continue;
+                    x[ii][jj] = fma(-l, xr[jj], x[ii][jj]);
+                }
             }
         }
     }
