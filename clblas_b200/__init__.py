@@ -170,6 +170,30 @@ def _load() -> ctypes.CDLL:
     lib.clblasB200LastGemmKernel.restype = ctypes.c_char_p
     lib.clblasB200SetGemmPath.argtypes = [i]
     lib.clblasB200SetGemmPath.restype = i
+    lib.clblasB200LastGemmVariant.argtypes = []
+    lib.clblasB200LastGemmVariant.restype = ctypes.c_char_p
+    lib.clblasB200WorkspaceAllocCount.argtypes = []
+    lib.clblasB200WorkspaceAllocCount.restype = ctypes.c_ulonglong
+    lib.clblasB200NoAllocLimits.argtypes = [psz, psz]
+    lib.clblasB200NoAllocLimits.restype = None
+    # communicator and sharded forms
+    lib.clblasB200CommGetUniqueId.argtypes = [vp]
+    lib.clblasB200CommInitRank.argtypes = [pvp, vp, i, i]
+    lib.clblasB200CommInitAll.argtypes = [pvp, i, pint]
+    lib.clblasB200CommDestroy.argtypes = [vp]
+    lib.clblasB200CommInfo.argtypes = [vp, pint, pint]
+    lib.clblasB200PanelPlan.argtypes = [sz, sz, u, psz, ctypes.POINTER(u)]
+    for name in ("clblasB200CommGetUniqueId", "clblasB200CommInitRank", "clblasB200CommInitAll", "clblasB200CommDestroy",
+                 "clblasB200CommInfo", "clblasB200PanelPlan"):
+        getattr(lib, name).restype = i
+    for name, ft in (("clblasB200SgemmSharded", ctypes.c_float), ("clblasB200DgemmSharded", ctypes.c_double)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, sz, sz, sz, ft, vp, sz, sz, vp, sz, sz, ft, vp, sz, sz, vp, i, u, pvp, u, pvp, pvp]
+        f.restype = i
+    for name, ft in (("clblasB200StrsmSharded", ctypes.c_float), ("clblasB200DtrsmSharded", ctypes.c_double)):
+        f = getattr(lib, name)
+        f.argtypes = [i, i, i, i, i, sz, sz, ft, vp, sz, sz, vp, sz, sz, vp, i, u, pvp, u, pvp, pvp]
+        f.restype = i
     return lib
 
 
@@ -179,7 +203,10 @@ EXPORTS = ["clblasSetup", "clblasTeardown", "clblasGetVersion", "clblasSgemm", "
            "clblasDtrsm", "clblasB200PlanShards", "clblasB200LaunchCount", "clblasB200LastGemmKernel",
            "clblasB200SetGemmPath", "clblasB200DeviceFault", "clblasB200ProbePeak", "clblasB200DtrsmNoAlloc",
            "clblasStrmm", "clblasDtrmm", "clblasSsyrk", "clblasDsyrk", "clblasSsyr2k", "clblasDsyr2k",
-           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost", "clblasB200StrsmHost", "clblasB200DtrsmHost"] + MATRIX_HELPERS + COMPLEX_SYM + ["clblasCtrmm", "clblasZtrmm"]
+           "clblasSsymm", "clblasDsymm", "clblasCgemm", "clblasZgemm", "clblasCtrsm", "clblasZtrsm", "clblasB200SgemmHost", "clblasB200DgemmHost", "clblasB200StrsmHost", "clblasB200DtrsmHost"] + MATRIX_HELPERS + COMPLEX_SYM + ["clblasCtrmm", "clblasZtrmm"] + [
+    "clblasB200LastGemmVariant", "clblasB200WorkspaceAllocCount", "clblasB200NoAllocLimits", "clblasB200CommGetUniqueId",
+    "clblasB200CommInitRank", "clblasB200CommInitAll", "clblasB200CommDestroy", "clblasB200CommInfo", "clblasB200PanelPlan",
+    "clblasB200SgemmSharded", "clblasB200DgemmSharded", "clblasB200StrsmSharded", "clblasB200DtrsmSharded"]
 
 
 def _ptr(x) -> Optional[int]:
@@ -527,7 +554,13 @@ for _n in COMPLEX_SYM:
     globals()[_n] = _complex_routine(_n)
 
 
-NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = 4096, 8192
+def _noalloc_limits():
+    a, b = ctypes.c_size_t(), ctypes.c_size_t()
+    lib.clblasB200NoAllocLimits(ctypes.byref(a), ctypes.byref(b))
+    return a.value, b.value
+
+
+NOALLOC_MAX_ORDER, NOALLOC_MAX_OTHER = _noalloc_limits()      # as compiled into the library
 
 
 def clblasB200DtrsmNoAlloc(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
@@ -567,3 +600,95 @@ def last_gemm_kernel() -> str:
 
 def set_gemm_path(path: int) -> int:
     return lib.clblasB200SetGemmPath(path)
+
+
+def last_gemm_variant() -> str:
+    """Instantiation and mode of the kernel the calling thread's last GEMM ran (clblasB200LastGemmVariant)."""
+    return lib.clblasB200LastGemmVariant().decode()
+
+
+def workspace_alloc_count() -> int:
+    """Workspace allocations made by the level-3 routines so far (clblasB200WorkspaceAllocCount)."""
+    return int(lib.clblasB200WorkspaceAllocCount())
+
+
+def panel_plan(columns: int, min_columns: int = 128, max_panels: int = 12):
+    """Boundaries of the broadcast panels the sharded calls use (clblasB200PanelPlan)."""
+    out = (ctypes.c_size_t * (max_panels + 1))()
+    n = ctypes.c_uint()
+    check(lib.clblasB200PanelPlan(columns, min_columns, max_panels, out, ctypes.byref(n)), "clblasB200PanelPlan")
+    return list(out)[: n.value + 1]
+
+
+# ---- one process per GPU: communicator and sharded forms -------------------------------------------------
+UNIQUE_ID_BYTES = 128
+
+
+def comm_get_unique_id() -> bytes:
+    """128 bytes that identify a communicator about to be created; one rank makes them, all ranks use them."""
+    buf = ctypes.create_string_buffer(UNIQUE_ID_BYTES)
+    check(lib.clblasB200CommGetUniqueId(buf), "clblasB200CommGetUniqueId")
+    return buf.raw
+
+
+def comm_init_rank(unique_id: Optional[bytes], nranks: int, rank: int) -> int:
+    """Joins the communicator (collective; the rank's device must be current).  Returns the handle."""
+    h = ctypes.c_void_p()
+    buf = ctypes.create_string_buffer(unique_id, UNIQUE_ID_BYTES) if unique_id is not None else None
+    check(lib.clblasB200CommInitRank(ctypes.byref(h), buf, nranks, rank), "clblasB200CommInitRank")
+    return h.value
+
+
+def comm_destroy(comm) -> None:
+    lib.clblasB200CommDestroy(comm)
+
+
+def comm_from_process_group(group=None) -> int:
+    """A communicator with one rank per rank of a torch.distributed process group: rank 0 draws the id, the
+    group carries it to the others (the only use made of the group)."""
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if world == 1:
+        return comm_init_rank(None, 1, 0)
+    box = [comm_get_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    return comm_init_rank(box[0], world, rank)
+
+
+def _gemm_sharded(fn, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc, comm, root,
+                  queues, wait, events):
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return fn(order, transA, transB, M, N, K, alpha, _ptr(A), offA, lda, _ptr(B), offB, ldb, beta, _ptr(C), offC, ldc,
+              comm, root, nq, q, nw, w, e)
+
+
+def clblasB200SgemmSharded(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                           comm, root=0, queues=None, wait=None, events=None) -> int:
+    """clblasSgemm on this rank's column block of op(B) and C (column-major; row-major: row block of op(A) and C);
+    the other operand is broadcast from `root` in panels while the panel products run."""
+    return _gemm_sharded(lib.clblasB200SgemmSharded, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb,
+                         beta, C, offC, ldc, comm, root, queues, wait, events)
+
+
+def clblasB200DgemmSharded(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                           comm, root=0, queues=None, wait=None, events=None) -> int:
+    return _gemm_sharded(lib.clblasB200DgemmSharded, order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb,
+                         beta, C, offC, ldc, comm, root, queues, wait, events)
+
+
+def _trsm_sharded(fn, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, comm, root, queues, wait, events):
+    nq, q, nw, w, e = _queues_events(queues, wait, events)
+    return fn(order, side, uplo, transA, diag, M, N, alpha, _ptr(A), offA, lda, _ptr(B), offB, ldb, comm, root, nq, q, nw, w, e)
+
+
+def clblasB200StrsmSharded(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, comm, root=0,
+                           queues=None, wait=None, events=None) -> int:
+    """clblasStrsm on this rank's block of right-hand sides; A is broadcast from `root` in panels the solve waits for."""
+    return _trsm_sharded(lib.clblasB200StrsmSharded, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                         comm, root, queues, wait, events)
+
+
+def clblasB200DtrsmSharded(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, comm, root=0,
+                           queues=None, wait=None, events=None) -> int:
+    return _trsm_sharded(lib.clblasB200DtrsmSharded, order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb,
+                         comm, root, queues, wait, events)

@@ -5,6 +5,7 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace cb200 {
@@ -15,6 +16,7 @@ std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_forced_path{0};
 std::atomic<int> g_initialized{0};
 thread_local const char* t_last_kernel = "none";
+thread_local char t_last_variant[96] = "none";
 
 // cuMemGetAddressRange through the runtime's driver entry point query: the extent of the CUDA
 // allocation that holds a pointer stands in for clGetMemObjectInfo(CL_MEM_SIZE) of the
@@ -118,13 +120,61 @@ clblasStatus wait_all(cudaStream_t s, unsigned n, const clblasEvent* ev)
     return clblasSuccess;
 }
 
-clblasStatus record_out(cudaStream_t s, clblasEvent* events)
+// Completion events.  events[0] is recorded on the queue that did the work; a caller that passed several
+// queues gets events[q] recorded on queue q once the work is done (the reference hands out one event per
+// queue, src/library/blas/xgemm.cc:606-610, src/library/blas/generic/solution_seq_make.c:402-404).
+clblasStatus record_out(unsigned nq, clblasQueue* queues, clblasEvent* events)
 {
-    if (events != nullptr && events[0] != nullptr) {
-        cudaError_t e = cudaEventRecord(reinterpret_cast<cudaEvent_t>(events[0]), s);
-        if (e != cudaSuccess) { cudaGetLastError(); return clblasInvalidValue; }
+    if (events == nullptr) return clblasSuccess;
+    cudaStream_t s0 = reinterpret_cast<cudaStream_t>(queues[0]);
+    cudaEvent_t done = reinterpret_cast<cudaEvent_t>(events[0]);
+    if (done != nullptr && cudaEventRecord(done, s0) != cudaSuccess) { cudaGetLastError(); return clblasInvalidValue; }
+    bool others = false;
+    for (unsigned q = 1; q < nq; q++) others = others || events[q] != nullptr;
+    if (!others) return clblasSuccess;
+    cudaEvent_t tmp = nullptr;
+    if (done == nullptr) {
+        if (cudaEventCreateWithFlags(&tmp, cudaEventDisableTiming) != cudaSuccess || cudaEventRecord(tmp, s0) != cudaSuccess) {
+            cudaGetLastError();
+            return clblasOutOfResources;
+        }
+        done = tmp;
     }
-    return clblasSuccess;
+    clblasStatus st = clblasSuccess;
+    for (unsigned q = 1; q < nq && st == clblasSuccess; q++) {
+        if (events[q] == nullptr) continue;
+        cudaStream_t sq = reinterpret_cast<cudaStream_t>(queues[q]);
+        if (cudaStreamWaitEvent(sq, done, 0) != cudaSuccess || cudaEventRecord(reinterpret_cast<cudaEvent_t>(events[q]), sq) != cudaSuccess) {
+            cudaGetLastError();
+            st = clblasInvalidValue;
+        }
+    }
+    if (tmp) cudaEventDestroy(tmp);
+    return st;
+}
+
+// Column-major form of a GEMM call.  Row-major C (M x N) is column-major C^T (N x M) = op(B)^T * op(A)^T: the
+// operands, their transposition flags and M with N are exchanged (the reference's force_gemm_column_major,
+// src/library/blas/xgemm.cc:40-61).  ConjTrans means Trans for real types.
+template <typename T>
+GemmProblem<T> normalise_gemm(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                              T alpha, const void* A, size_t offA, size_t lda, const void* B, size_t offB, size_t ldb,
+                              T beta, void* C, size_t offC, size_t ldc)
+{
+    GemmProblem<T> p;
+    p.alpha = alpha; p.beta = beta; p.K = K;
+    p.C = static_cast<T*>(C) + offC; p.ldc = ldc;
+    const bool ta = transA != clblasNoTrans, tb = transB != clblasNoTrans;
+    if (order == clblasColumnMajor) {
+        p.ta = ta; p.tb = tb; p.M = M; p.N = N;
+        p.A = static_cast<const T*>(A) + offA; p.lda = lda;
+        p.B = static_cast<const T*>(B) + offB; p.ldb = ldb;
+    } else {
+        p.ta = tb; p.tb = ta; p.M = N; p.N = M;
+        p.A = static_cast<const T*>(B) + offB; p.lda = ldb;
+        p.B = static_cast<const T*>(A) + offA; p.ldb = lda;
+    }
+    return p;
 }
 
 template <typename T>
@@ -150,26 +200,97 @@ clblasStatus gemm_entry(clblasOrder order, clblasTranspose transA, clblasTranspo
     if ((st = check_events(nev, wait)) != clblasSuccess) return st;
 
     cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
-    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    for (unsigned q = 0; q < nq; q++)
+        if ((st = wait_all(reinterpret_cast<cudaStream_t>(queues[q]), nev, wait)) != clblasSuccess) return st;
 
-    GemmProblem<T> p;
-    p.alpha = alpha; p.beta = beta; p.K = K;
-    p.C = static_cast<T*>(C) + offC; p.ldc = ldc;
-    const bool ta = transA != clblasNoTrans, tb = transB != clblasNoTrans;   // ConjTrans == Trans for reals
-    if (order == clblasColumnMajor) {
-        p.ta = ta; p.tb = tb; p.M = M; p.N = N;
-        p.A = static_cast<const T*>(A) + offA; p.lda = lda;
-        p.B = static_cast<const T*>(B) + offB; p.ldb = ldb;
-    } else {
-        // Row-major C (MxN) is column-major C^T (NxM) = op(B)^T * op(A)^T: swap the operands, their
-        // transposition flags and M with N (the reference's force_gemm_column_major, xgemm.cc:40-61).
-        p.ta = tb; p.tb = ta; p.M = N; p.N = M;
-        p.A = static_cast<const T*>(B) + offB; p.lda = ldb;
-        p.B = static_cast<const T*>(A) + offA; p.ldb = lda;
+    const GemmProblem<T> p = normalise_gemm<T>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc);
+    if (nq > 1) {
+        // Several queues: stripes of N, one per queue, as the reference's multi-queue GEMM does.
+        cudaError_t e = gemm_multi_queue<T>(p, nq, reinterpret_cast<cudaStream_t*>(queues), reinterpret_cast<cudaEvent_t*>(events));
+        if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+        return clblasSuccess;
     }
     cudaError_t e = gemm_colmajor<T>(p, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
+}
+
+// The GEMM front end on one rank's shard (clblasB200{S,D}gemmSharded): the checks of gemm_entry, except that a
+// rank may own no columns at all (its part of the split is empty) and still takes part in the broadcasts.
+template <typename T>
+clblasStatus gemm_sharded_entry(clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+                                size_t M, size_t N, size_t K, T alpha,
+                                void* A, size_t offA, size_t lda, void* B, size_t offB, size_t ldb,
+                                T beta, void* C, size_t offC, size_t ldc, clblasB200Comm comm, int root,
+                                unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (C == nullptr) return clblasInvalidMatC;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)transA > 2u || (unsigned)transB > 2u) return clblasInvalidValue;
+    int nranks = 1, rank = 0;
+    if (comm != nullptr) clblasB200CommInfo(comm, &nranks, &rank);
+    if (root < 0 || root >= nranks) return clblasInvalidValue;
+    // The sharded dimension is N for a column-major call and M for a row-major one (the columns of the
+    // column-major view of C either way); the operand that is broadcast is the other one's partner: A for
+    // column-major, B for row-major.
+    const bool col = order == clblasColumnMajor;
+    const size_t local = col ? N : M;
+    clblasStatus st;
+    if (K != 0) {
+        if (col || local != 0)
+            if ((st = check_matrix_sizes(sizeof(T), order, transA, M, K, A, offA, lda, SET_A)) != clblasSuccess) return st;
+        if (!col || local != 0)
+            if ((st = check_matrix_sizes(sizeof(T), order, transB, K, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+    }
+    if (local != 0 && (st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, M, N, C, offC, ldc, SET_C)) != clblasSuccess) return st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    const GemmProblem<T> p = normalise_gemm<T>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc);
+    cudaError_t e = gemm_sharded_colmajor<T>(static_cast<ShardComm*>(comm), root, p, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(nq, queues, events);
+}
+
+// The TRSM front end on one rank's shard (clblasB200{S,D}trsmSharded): checks of trsm_entry; the dimension of B
+// that is not the order of A is the sharded one and may be zero on a rank.
+template <typename T>
+clblasStatus trsm_sharded_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                                size_t M, size_t N, T alpha, void* A, size_t offA, size_t lda, void* B, size_t offB, size_t ldb,
+                                clblasB200Comm comm, int root,
+                                unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    clblasStatus st;
+    if ((st = check_queues(nq, queues)) != clblasSuccess) return st;
+    if ((st = check_events(nev, wait)) != clblasSuccess) return st;
+    if (!g_initialized.load()) return clblasNotInitialized;
+    if (A == nullptr) return clblasInvalidMatA;
+    if (B == nullptr) return clblasInvalidMatB;
+    if (order != clblasRowMajor && order != clblasColumnMajor) return clblasInvalidValue;
+    if ((unsigned)side > 1u || (unsigned)uplo > 1u || (unsigned)transA > 2u || (unsigned)diag > 1u) return clblasInvalidValue;
+    int nranks = 1, rank = 0;
+    if (comm != nullptr) clblasB200CommInfo(comm, &nranks, &rank);
+    if (root < 0 || root >= nranks) return clblasInvalidValue;
+    const size_t msize = (side == clblasLeft) ? M : N, other = (side == clblasLeft) ? N : M;
+    if ((st = check_matrix_sizes(sizeof(T), order, transA, msize, msize, A, offA, lda, SET_A)) != clblasSuccess) return st;
+    if (other != 0 && (st = check_matrix_sizes(sizeof(T), order, clblasNoTrans, M, N, B, offB, ldb, SET_B)) != clblasSuccess) return st;
+
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(queues[0]);
+    if ((st = wait_all(s, nev, wait)) != clblasSuccess) return st;
+    bool right = (side == clblasRight), lower = (uplo == clblasLower);
+    if (order == clblasRowMajor) {
+        size_t t = M; M = N; N = t;
+        right = !right;
+        lower = !lower;
+    }
+    cudaError_t e = trsm_sharded_colmajor<T>(static_cast<ShardComm*>(comm), root, right, lower, transA != clblasNoTrans,
+                                             diag == clblasUnit, M, N, alpha, static_cast<T*>(A) + offA, lda,
+                                             static_cast<T*>(B) + offB, ldb, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
+    return record_out(nq, queues, events);
 }
 
 // Complex GEMM front end: the checks of gemm_entry on complex elements (2 * sizeof(R) bytes each).
@@ -207,7 +328,7 @@ clblasStatus cgemm_entry(clblasOrder order, clblasTranspose transA, clblasTransp
     else    // row-major C is column-major C^T = op(B)^T * op(A)^T; a conjugation stays with its operand
         e = cgemm_colmajor<R>((int)transB, (int)transA, N, M, K, ar, ai, b, ldb, a, lda, br, bi, c, ldc, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 // Leading-dimension check of checkMatrixSizes for a matrix in host memory (no allocation extent to compare with).
@@ -251,7 +372,7 @@ clblasStatus gemm_host_entry(clblasOrder order, clblasTranspose transA, clblasTr
     if (order == clblasColumnMajor) e = gemm_host_colmajor<T>(ta, tb, M, N, K, alpha, a, lda, b, ldb, beta, c, ldc, s);
     else                            e = gemm_host_colmajor<T>(tb, ta, N, M, K, alpha, b, ldb, a, lda, beta, c, ldc, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 // TRSM on host matrices: the checks of trsm_entry in the same order (without memory extents).
@@ -283,7 +404,7 @@ clblasStatus trsm_host_entry(clblasOrder order, clblasSide side, clblasUplo uplo
     cudaError_t e = trsm_host_colmajor<T>(right, lower, transA != clblasNoTrans, diag == clblasUnit, M, N, alpha,
                                           static_cast<const T*>(A) + offA, lda, static_cast<T*>(B) + offB, ldb, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 // Complex SYRK / HERK, SYR2K / HER2K, SYMM / HEMM front ends.  Checks in the order of the reference's doSyrk /
@@ -328,7 +449,7 @@ clblasStatus csyrk_entry(bool herm, bool two, clblasOrder order, clblasUplo uplo
     if (two) e = csyr2k_colmajor<R>(herm, lower, op, N, K, ar, ai, a, lda, static_cast<const R*>(B) + 2 * offB, ldb, br, bi, c, ldc, s);
     else     e = csyrk_colmajor<R>(herm, lower, op, N, K, ar, ai, a, lda, br, bi, c, ldc, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 template <typename R>
@@ -363,7 +484,7 @@ clblasStatus csymm_entry(bool herm, clblasOrder order, clblasSide side, clblasUp
     cudaError_t e = csymm_colmajor<R>(herm, right, lower, M, N, ar, ai, static_cast<const R*>(A) + 2 * offA, lda,
                                       static_cast<const R*>(B) + 2 * offB, ldb, br, bi, static_cast<R*>(C) + 2 * offC, ldc, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 // Complex TRMM front end: the checks of trmm_entry on complex elements.
@@ -397,7 +518,7 @@ clblasStatus ctrmm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, cl
     cudaError_t e = ctrmm_colmajor<R>(right, lower, (int)transA, diag == clblasUnit, M, N, ar, ai,
                                       static_cast<const R*>(A) + 2 * offA, lda, static_cast<R*>(B) + 2 * offB, ldb, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 template <typename T>
@@ -433,7 +554,7 @@ clblasStatus trsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clb
     cudaError_t e = trsm_colmajor<T>(right, lower, transA != clblasNoTrans, diag == clblasUnit, M, N, alpha,
                                      static_cast<const T*>(A) + offA, lda, static_cast<T*>(B) + offB, ldb, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 // clblasStrmm / clblasDtrmm: checks of the reference's doTrmm (src/library/blas/xtrmm.c:52-70):
@@ -470,7 +591,7 @@ clblasStatus ctrsm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, cl
     cudaError_t e = ctrsm_colmajor<R>(right, lower, (int)transA, diag == clblasUnit, M, N, ar, ai,
                                       static_cast<const R*>(A) + 2 * offA, lda, static_cast<R*>(B) + 2 * offB, ldb, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 template <typename T>
@@ -502,7 +623,7 @@ clblasStatus trmm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, clb
     cudaError_t e = trmm_colmajor<T>(right, lower, transA != clblasNoTrans, diag == clblasUnit, M, N, alpha,
                                      static_cast<const T*>(A) + offA, lda, static_cast<T*>(B) + offB, ldb, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 // clblasSsyrk / clblasDsyrk: checks of the reference's doSyrk (src/library/blas/xsyrk.c:48-70): initialised,
@@ -534,7 +655,7 @@ clblasStatus syrk_entry(clblasOrder order, clblasUplo uplo, clblasTranspose tran
     cudaError_t e = syrk_colmajor<T>(lower, trans, N, K, alpha, static_cast<const T*>(A) + offA, lda, beta,
                                      static_cast<T*>(C) + offC, ldc, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 // SYR2K front end.  Check order of the reference's doSyr2k (src/library/blas/xsyr2k.c:52-78).
@@ -567,7 +688,7 @@ clblasStatus syr2k_entry(clblasOrder order, clblasUplo uplo, clblasTranspose tra
     cudaError_t e = syr2k_colmajor<T>(lower, trans, N, K, alpha, static_cast<const T*>(A) + offA, lda,
                                       static_cast<const T*>(B) + offB, ldb, beta, static_cast<T*>(C) + offC, ldc, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 // SYMM front end.  Check order of the reference's doSymm (src/library/blas/xsymm.c): memory objects and
@@ -604,13 +725,18 @@ clblasStatus symm_entry(clblasOrder order, clblasSide side, clblasUplo uplo, siz
     cudaError_t e = symm_colmajor<T>(right, lower, M, N, alpha, static_cast<const T*>(A) + offA, lda,
                                      static_cast<const T*>(B) + offB, ldb, beta, static_cast<T*>(C) + offC, ldc, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 }  // namespace
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
-void set_last_kernel(const char* name) { t_last_kernel = name; }
+void set_last_kernel(const char* name) { t_last_kernel = name; set_last_variant(name); }
+void set_last_variant(const char* name)
+{
+    std::strncpy(t_last_variant, name, sizeof(t_last_variant) - 1);
+    t_last_variant[sizeof(t_last_variant) - 1] = 0;
+}
 int forced_gemm_path() { return g_forced_path.load(std::memory_order_relaxed); }
 
 int sm_count()
@@ -993,7 +1119,7 @@ clblasStatus clblasB200DtrsmNoAlloc(clblasOrder order, clblasSide side, clblasUp
     cudaError_t e = dtrsm_colmajor_noalloc(right, lower, transA != clblasNoTrans, diag == clblasUnit, M, N, alpha,
                                            static_cast<const double*>(A) + offA, lda, static_cast<double*>(B) + offB, ldb, s);
     if (e != cudaSuccess) { cudaGetLastError(); return from_cuda(e); }
-    return record_out(s, events);
+    return record_out(nq, queues, events);
 }
 
 clblasStatus clblasB200PlanShards(size_t total, unsigned parts, size_t align, size_t* bounds)
@@ -1020,6 +1146,49 @@ unsigned clblasB200DeviceFault(void)
     return dgemm_tma_fault_flag() | sgemm_tma_fault_flag() | sgemm_3xtf32_fault_flag();
 }
 const char* clblasB200LastGemmKernel(void) { return t_last_kernel; }
+const char* clblasB200LastGemmVariant(void) { return t_last_variant; }
+unsigned long long clblasB200WorkspaceAllocCount(void) { return ws_alloc_count(); }
+void clblasB200NoAllocLimits(size_t* max_order, size_t* max_other)
+{
+    if (max_order) *max_order = CLBLAS_B200_NOALLOC_MAX_ORDER;
+    if (max_other) *max_other = CLBLAS_B200_NOALLOC_MAX_OTHER;
+}
+
+clblasStatus clblasB200SgemmSharded(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                                    float alpha, clblasMem A, size_t offA, size_t lda, clblasMem B, size_t offB, size_t ldb,
+                                    float beta, clblasMem C, size_t offC, size_t ldc, clblasB200Comm comm, int root,
+                                    unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return gemm_sharded_entry<float>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                                     comm, root, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasB200DgemmSharded(clblasOrder order, clblasTranspose transA, clblasTranspose transB, size_t M, size_t N, size_t K,
+                                    double alpha, clblasMem A, size_t offA, size_t lda, clblasMem B, size_t offB, size_t ldb,
+                                    double beta, clblasMem C, size_t offC, size_t ldc, clblasB200Comm comm, int root,
+                                    unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return gemm_sharded_entry<double>(order, transA, transB, M, N, K, alpha, A, offA, lda, B, offB, ldb, beta, C, offC, ldc,
+                                      comm, root, nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasB200StrsmSharded(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                                    size_t M, size_t N, float alpha, clblasMem A, size_t offA, size_t lda, clblasMem B, size_t offB,
+                                    size_t ldb, clblasB200Comm comm, int root,
+                                    unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return trsm_sharded_entry<float>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, comm, root,
+                                     nq, queues, nev, wait, events);
+}
+
+clblasStatus clblasB200DtrsmSharded(clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+                                    size_t M, size_t N, double alpha, clblasMem A, size_t offA, size_t lda, clblasMem B, size_t offB,
+                                    size_t ldb, clblasB200Comm comm, int root,
+                                    unsigned nq, clblasQueue* queues, unsigned nev, const clblasEvent* wait, clblasEvent* events)
+{
+    return trsm_sharded_entry<double>(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, offB, ldb, comm, root,
+                                      nq, queues, nev, wait, events);
+}
 int clblasB200SetGemmPath(int path) { return g_forced_path.exchange(path); }
 
 }  // extern "C"

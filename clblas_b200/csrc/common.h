@@ -2,8 +2,11 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
+#include <functional>
+#include <vector>
 
 #include "../../include/clblas_b200.h"
 
@@ -61,6 +64,8 @@ unsigned sgemm_3xtf32_fault_flag();
 
 void count_launch(unsigned n = 1);
 void set_last_kernel(const char* name);
+// Instantiation and mode of the kernel a GEMM ran (reported by clblasB200LastGemmVariant); the string is copied.
+void set_last_variant(const char* name);
 int forced_gemm_path();
 
 // Scales C by beta (beta == 0 stores zeros without reading C).  Used for K == 0 and alpha == 0.
@@ -146,10 +151,22 @@ template <typename R>
 cudaError_t ctrmm_colmajor(bool right, bool lower, int op, bool unit, size_t M, size_t N, R ar, R ai,
                            const R* A, size_t lda, R* B, size_t ldb, cudaStream_t s);
 
-// Blocked triangular solve on a column-major problem (B overwritten by X).
+// Columns of the stored triangular matrix that arrive while the solve is already running (a broadcast
+// in column panels): panel p = columns [bounds[p], bounds[p+1]), complete once ready[p] has fired.  Every
+// step of the solve waits, on its stream, for the panels it reads and has not waited for yet; the
+// diagonal blocks of a panel are inverted when the panel is first needed.  Boundaries other than the
+// last one are multiples of 128 (the order of the inverted blocks).
+struct TrsmPanelGate {
+    std::vector<size_t> bounds;
+    std::vector<cudaEvent_t> ready;
+    std::vector<char> waited;
+};
+
+// Blocked triangular solve on a column-major problem (B overwritten by X).  gate == nullptr: all of A is
+// in place when the call is made.
 template <typename T>
 cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
-                          const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
+                          const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s, TrsmPanelGate* gate = nullptr);
 void trsm_release_workspaces();
 
 // Triangular matrix multiply on a column-major problem (B overwritten by alpha*op(A)*B or alpha*B*op(A)).
@@ -174,15 +191,53 @@ template <typename T>
 cudaError_t symm_colmajor(bool right, bool lower, size_t M, size_t N, T alpha, const T* A, size_t lda, const T* B, size_t ldb,
                           T beta, T* C, size_t ldc, cudaStream_t s);
 
+// Multi-GPU forms (sharded.cu).  ShardComm: one rank's end of a communicator (clblasB200Comm).
+struct ShardComm;
+template <typename T>
+cudaError_t gemm_sharded_colmajor(ShardComm* c, int root, const GemmProblem<T>& p, cudaStream_t s);
+template <typename T>
+cudaError_t trsm_sharded_colmajor(ShardComm* c, int root, bool right, bool lower, bool trans, bool unit, size_t M, size_t N,
+                                  T alpha, T* A, size_t lda, T* B, size_t ldb, cudaStream_t s);
+// One process, several queues (possibly on several devices): stripe q of N runs on queues[q]; done[q], when
+// given, is recorded on queues[q] after its stripe.
+template <typename T>
+cudaError_t gemm_multi_queue(const GemmProblem<T>& p, unsigned nq, cudaStream_t* queues, cudaEvent_t* done);
+
 // Stream-ordered workspace from the library's own per-device pool (workspace.cu).
 cudaError_t ws_alloc(void** ptr, size_t bytes, cudaStream_t s);
 cudaError_t ws_free(void* ptr, cudaStream_t s);
 void ws_release_all();
+// Number of ws_alloc calls made by the process so far (every workspace a level-3 routine takes goes
+// through ws_alloc, so a call during which this does not move allocated nothing).
+unsigned long long ws_alloc_count();
+
+// One-time, per-device set-up step (a kernel's opt-in to large dynamic shared memory) that several host
+// threads may reach at once: the step is idempotent, the flag is atomic.
+struct DeviceOnce {
+    std::atomic<unsigned char> done[64];
+    template <typename F>
+    cudaError_t run(F&& step)
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const bool tracked = dev >= 0 && dev < 64;
+        if (tracked && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+        const cudaError_t e = step();
+        if (e != cudaSuccess) return e;
+        if (tracked) done[dev].store(1, std::memory_order_release);
+        return cudaSuccess;
+    }
+};
 
 // DTRSM on the fixed device-resident scratch array (no allocation); cudaErrorMemoryAllocation
 // when the problem exceeds the array.
 cudaError_t dtrsm_colmajor_noalloc(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, double alpha,
                                    const double* A, size_t lda, double* B, size_t ldb, cudaStream_t s);
+
+// First-use work of every FP64 GEMM kernel a triangular solve can reach without allocating, done ahead of
+// time on the current device: shared-memory opt-ins and module loads.
+cudaError_t dgemm_prepare_all_kernels();
+cudaError_t gemm_simt_load_double_kernels();
 
 // Sticky per-translation-unit flags set when a bounded mbarrier wait inside a kernel ran out.
 unsigned dgemm_tma_fault_flag();

@@ -25,6 +25,7 @@
 #include "common.h"
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include "tma_pipeline.cuh"
 
@@ -403,6 +404,33 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
 }
 
+// One-time per-device opt-in to the kernels' dynamic shared memory.
+template <bool TA, bool TB, int BN, bool TRI>
+cudaError_t prepare_main()
+{
+    static DeviceOnce once;
+    return once.run([] {
+        return cudaFuncSetAttribute(dgemm_mma_tma_kernel<TA, TB, BN, TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN));
+    });
+}
+template <bool TA, bool TB>
+cudaError_t prepare_streamk()
+{
+    static DeviceOnce once;
+    return once.run([] {
+        return cudaFuncSetAttribute(dgemm_streamk_kernel<TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128));
+    });
+}
+
+// "dgemm_mma_tma<T,N,128>" (+ "+tri", "+streamk_tail"): the instantiation a call ran, for the tests.
+const char* variant_name(bool ta, bool tb, int bn, bool tri, bool streamk)
+{
+    static thread_local char buf[64];
+    snprintf(buf, sizeof(buf), "dgemm_mma_tma<%c,%c,%d>%s%s", ta ? 'T' : 'N', tb ? 'T' : 'N', bn, tri ? "+tri" : "",
+             streamk ? "+streamk_tail" : "");
+    return buf;
+}
+
 template <bool TA, bool TB, int BN, bool TRI>
 cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
 {
@@ -416,14 +444,8 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
     else    ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.B, p.K, p.N, p.ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorNotSupported;
 
-    static bool attr_done[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(dgemm_mma_tma_kernel<TA, TB, BN, TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN));
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) attr_done[dev] = true;
-    }
+    cudaError_t e0 = prepare_main<TA, TB, BN, TRI>();
+    if (e0 != cudaSuccess) return e0;
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
     size_t main_tiles = tilesM * tilesN;
     if (BN == 128 && !TRI) {
@@ -441,13 +463,10 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
             if (e == cudaSuccess) {
                 unsigned* counters = reinterpret_cast<unsigned*>(ws + ws_doubles);
                 e = cudaMemsetAsync(counters, 0, R * sizeof(unsigned), s);
-                static bool sk_attr_done[64] = {};
-                if (e == cudaSuccess && (dev < 0 || dev >= 64 || !sk_attr_done[dev])) {
-                    e = cudaFuncSetAttribute(dgemm_streamk_kernel<TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128));
-                    if (e == cudaSuccess && dev >= 0 && dev < 64) sk_attr_done[dev] = true;
-                }
+                if (e == cudaSuccess) e = prepare_streamk<TA, TB>();
                 if (e == cudaSuccess) {
                     main_tiles = T - R;
+                    set_last_variant(variant_name(TA, TB, BN, TRI, true));
                     dgemm_mma_tma_kernel<TA, TB, BN, TRI><<<(unsigned)main_tiles, THREADS, smem_bytes(BN), s>>>(
                         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)S, p.tri);
                     count_launch();
@@ -463,10 +482,26 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
             cudaGetLastError();        // no workspace: one CTA per tile as usual
         }
     }
+    set_last_variant(variant_name(TA, TB, BN, TRI, false));
     dgemm_mma_tma_kernel<TA, TB, BN, TRI><<<(unsigned)main_tiles, THREADS, smem_bytes(BN), s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 1), p.tri);
     count_launch();
     return cudaGetLastError();
+}
+
+// Shared-memory opt-in and module load of every instantiation without the triangular mode (what a
+// triangular solve can dispatch to when it may not allocate).
+template <bool TA, bool TB>
+cudaError_t prepare_transposition()
+{
+    cudaFuncAttributes fa;
+    cudaError_t e;
+    if ((e = prepare_main<TA, TB, 128, false>()) != cudaSuccess) return e;
+    if ((e = cudaFuncGetAttributes(&fa, dgemm_mma_tma_kernel<TA, TB, 128, false>)) != cudaSuccess) return e;
+    if ((e = prepare_main<TA, TB, 64, false>()) != cudaSuccess) return e;
+    if ((e = cudaFuncGetAttributes(&fa, dgemm_mma_tma_kernel<TA, TB, 64, false>)) != cudaSuccess) return e;
+    if ((e = prepare_main<TA, TB, 32, false>()) != cudaSuccess) return e;
+    return cudaFuncGetAttributes(&fa, dgemm_mma_tma_kernel<TA, TB, 32, false>);
 }
 
 template <int BN>
@@ -499,6 +534,17 @@ cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s, i
     if (min_bn >= 128 || tilesM * ((p.N + 127) / 128) >= 120) return launch_t<128>(p, s);
     if (tilesM * ((p.N + 63) / 64) >= 120) return launch_t<64>(p, s);
     return launch_t<32>(p, s);
+}
+
+cudaError_t dgemm_prepare_all_kernels()
+{
+    cudaError_t e;
+    if ((e = prepare_transposition<false, false>()) != cudaSuccess) return e;
+    if ((e = prepare_transposition<false, true>()) != cudaSuccess) return e;
+    if ((e = prepare_transposition<true, false>()) != cudaSuccess) return e;
+    if ((e = prepare_transposition<true, true>()) != cudaSuccess) return e;
+    if (get_tensor_map_encoder() == nullptr) return cudaErrorNotSupported;
+    return gemm_simt_load_double_kernels();
 }
 
 unsigned dgemm_tma_fault_flag() { return read_wait_timeout_flag(); }

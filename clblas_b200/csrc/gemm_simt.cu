@@ -219,6 +219,17 @@ cudaError_t launch_gemm_simt<double>(const GemmProblem<double>& p, cudaStream_t 
     return launch_cfg<double, 64, 64, 8, 4, 4>(p, s);
 }
 
+cudaError_t gemm_simt_load_double_kernels()
+{
+    cudaFuncAttributes fa;
+    cudaError_t e;
+    if ((e = cudaFuncGetAttributes(&fa, gemm_simt_kernel<double, 64, 64, 8, 4, 4, false, false, false>)) != cudaSuccess) return e;
+    if ((e = cudaFuncGetAttributes(&fa, gemm_simt_kernel<double, 64, 64, 8, 4, 4, false, true, false>)) != cudaSuccess) return e;
+    if ((e = cudaFuncGetAttributes(&fa, gemm_simt_kernel<double, 64, 64, 8, 4, 4, true, false, false>)) != cudaSuccess) return e;
+    if ((e = cudaFuncGetAttributes(&fa, gemm_simt_kernel<double, 64, 64, 8, 4, 4, true, true, false>)) != cudaSuccess) return e;
+    return cudaFuncGetAttributes(&fa, scale_kernel<double>);
+}
+
 template cudaError_t launch_scale<float>(size_t, size_t, float, float*, size_t, cudaStream_t);
 template cudaError_t launch_scale<double>(size_t, size_t, double, double*, size_t, cudaStream_t);
 

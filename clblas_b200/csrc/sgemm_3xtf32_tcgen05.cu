@@ -367,13 +367,8 @@ cudaError_t launch_sgemm_3xtf32(const GemmProblem<float>& p, cudaStream_t s)
                   make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, p.K, p.N, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_64B);
         if (!ok) e = cudaErrorNotSupported;
         if (e == cudaSuccess) {
-            static bool attr_done[64] = {};
-            int dev = 0;
-            cudaGetDevice(&dev);
-            if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-                e = cudaFuncSetAttribute(sgemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-                if (e == cudaSuccess && dev >= 0 && dev < 64) attr_done[dev] = true;
-            }
+            static DeviceOnce once;
+            e = once.run([] { return cudaFuncSetAttribute(sgemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
         }
         if (e == cudaSuccess) {
             const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;

@@ -33,7 +33,9 @@
 #include "tma_pipeline.cuh"
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 namespace cb200 {
 
@@ -313,22 +315,25 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s, unsigned splits 
     if (!ok) return cudaErrorNotSupported;
 
     constexpr int SMEM = smem_bytes(STAGES, BN);
-    static bool attr_done[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) attr_done[dev] = true;
-    }
+    static DeviceOnce once;
+    cudaError_t e = once.run([] {
+        return cudaFuncSetAttribute(sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    });
+    if (e != cudaSuccess) return e;
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
+    char name[64];
+    snprintf(name, sizeof(name), "sgemm_ffma_tma<%c,%c,%d,%d,%d>%s", TA ? 'T' : 'N', TB ? 'T' : 'N', BN, STAGES, MIN_CTAS, TRI ? "+tri" : "");
+    float* W = nullptr;
+    const size_t ldw = (p.M + 3) / 4 * 4, stride = ldw * p.N;
+    if (splits > 1 && ws_alloc(reinterpret_cast<void**>(&W), splits * stride * sizeof(float), s) != cudaSuccess) {
+        cudaGetLastError();          // no workspace: the same kernel, unsplit, needs none
+        splits = 1;
+    }
     if (splits > 1) {
         // partial products into `splits` planes of a workspace, then one deterministic reduction into C
-        const size_t ldw = (p.M + 3) / 4 * 4, stride = ldw * p.N;
-        float* W = nullptr;
-        cudaError_t e = ws_alloc(reinterpret_cast<void**>(&W), splits * stride * sizeof(float), s);
-        if (e != cudaSuccess) return e;
+        snprintf(name + strlen(name), sizeof(name) - strlen(name), "+splitk%u", splits);
+        set_last_variant(name);
         sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI><<<dim3((unsigned)(tilesM * tilesN), splits), THREADS, SMEM, s>>>(
             mapA, mapB, W, ldw, p.M, p.N, p.K, 1.f, 0.f, (unsigned)tilesM, (unsigned)tilesN, 0u, TRI_FULL, splits, stride);
         count_launch();
@@ -342,6 +347,7 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s, unsigned splits 
         const cudaError_t e2 = ws_free(W, s);
         return e != cudaSuccess ? e : e2;
     }
+    set_last_variant(name);
     sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * MIN_CTAS), p.tri,
         1u, (size_t)0);
@@ -520,14 +526,12 @@ cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s)
         return cudaErrorNotSupported;
     if (!make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.N, p.K, p.ldb, 128, BK, CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorNotSupported;
-    static bool attr_done[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(sgemm_nt_16x8_kernel<TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, T16_SMEM);
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) attr_done[dev] = true;
-    }
+    static DeviceOnce once;
+    const cudaError_t e = once.run([] {
+        return cudaFuncSetAttribute(sgemm_nt_16x8_kernel<TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, T16_SMEM);
+    });
+    if (e != cudaSuccess) return e;
+    set_last_variant(TRI ? "sgemm_nt_16x8+tri" : "sgemm_nt_16x8");
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128;
     sgemm_nt_16x8_kernel<TRI><<<(unsigned)(tilesM * tilesN), T16_THREADS, T16_SMEM, s>>>(
         mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 2), p.tri);

@@ -23,9 +23,9 @@ namespace {
 constexpr int NB = 128;           // order of the inverted diagonal blocks
 constexpr int TRTRI_THREADS = 512;
 
-// Inverts every NB x NB diagonal block of the triangular matrix A (order n) into
-// inv[b] (dense NB x NB, column-major, ld = NB, zeros outside the triangle).  Rows/columns of the
-// last block beyond n are completed with the identity.
+// Inverts the NB x NB diagonal blocks b_first, b_first + 1, ... (one per CTA) of the triangular matrix A
+// (order n) into inv[b] (dense NB x NB, column-major, ld = NB, zeros outside the triangle).  Rows/columns
+// of the last block beyond n are completed with the identity.
 //
 // The block is held in shared memory as a lower-triangular L (an upper-triangular block is loaded
 // transposed and the result stored transposed).  X = L^-1 lives in registers, 32 entries per
@@ -34,13 +34,13 @@ constexpr int TRTRI_THREADS = 512;
 // one barrier per k; row k travels through a double-buffered shared row.
 template <typename T>
 __global__ void __launch_bounds__(TRTRI_THREADS)
-trtri_diag_kernel(const T* __restrict__ A, size_t lda, size_t n, bool lower, bool unit, T* __restrict__ inv)
+trtri_diag_kernel(const T* __restrict__ A, size_t lda, size_t n, bool lower, bool unit, T* __restrict__ inv, unsigned b_first)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* Ls = reinterpret_cast<T*>(smem_raw);                 // Ls[k*NB + i] = L[i][k]
     T* rowbuf = Ls + NB * NB;                               // 2 x NB
 
-    const size_t b = blockIdx.x;
+    const size_t b = (size_t)b_first + blockIdx.x;
     const size_t r0 = b * NB;
     const int nv = (n - r0 < (size_t)NB) ? (int)(n - r0) : NB;   // valid order of this block
     const T* Ab = A + r0 + r0 * lda;
@@ -117,13 +117,57 @@ trtri_diag_kernel(const T* __restrict__ A, size_t lda, size_t n, bool lower, boo
 template <typename T>
 struct TrsmCtx {
     bool right, lower, trans, eff_lower;
+    bool unit = false;
     size_t M, N, n;              // n = order of A
     const T* A; size_t lda;
     T* B; size_t ldb;
     T* inv;                      // NB*NB per diagonal block
     T* tmp;                      // staging panel for one leaf
     cudaStream_t s;
+    TrsmPanelGate* gate = nullptr;   // set when columns of A are still arriving (see common.h)
 };
+
+constexpr size_t trtri_smem(size_t elem) { return (size_t)(NB * NB + 2 * NB) * elem; }
+
+template <typename T>
+cudaError_t trtri_prepare()
+{
+    // The opt-in to more than 48 KB of dynamic shared memory is a per-device function attribute.
+    static DeviceOnce once[2];
+    return once[sizeof(T) == 8].run([] {
+        return cudaFuncSetAttribute(trtri_diag_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)trtri_smem(sizeof(T)));
+    });
+}
+
+// Inverts the diagonal blocks [b0, b1) of c.A into c.inv.
+template <typename T>
+cudaError_t invert_blocks(const TrsmCtx<T>& c, size_t b0, size_t b1)
+{
+    if (b1 <= b0) return cudaSuccess;
+    trtri_diag_kernel<T><<<(unsigned)(b1 - b0), TRTRI_THREADS, trtri_smem(sizeof(T)), c.s>>>(c.A, c.lda, c.n, c.lower, c.unit, c.inv,
+                                                                                              (unsigned)b0);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// Before an operation that reads columns [c0, c1) of the stored A: with a gate, orders the stream after
+// the arrival of every panel that holds one of them and has not been waited for yet, and inverts the
+// diagonal blocks of those panels.  Without a gate everything is in place already.
+template <typename T>
+cudaError_t need_columns(const TrsmCtx<T>& c, size_t c0, size_t c1)
+{
+    TrsmPanelGate* g = c.gate;
+    if (g == nullptr) return cudaSuccess;
+    for (size_t p = 0; p + 1 < g->bounds.size(); p++) {
+        const size_t p0 = g->bounds[p], p1 = g->bounds[p + 1];
+        if (p1 <= c0 || p0 >= c1 || g->waited[p]) continue;
+        cudaError_t e = cudaStreamWaitEvent(c.s, g->ready[p], 0);
+        if (e != cudaSuccess) return e;
+        g->waited[p] = 1;
+        if ((e = invert_blocks(c, p0 / NB, (p1 + NB - 1) / NB)) != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
 
 template <typename T>
 cudaError_t gemm_call(bool ta, bool tb, size_t M, size_t N, size_t K, T alpha, const T* A, size_t lda,
@@ -154,6 +198,7 @@ cudaError_t solve_leaf(const TrsmCtx<T>& c, size_t b, T alpha)
     const size_t r = b * NB, nv = std::min<size_t>(NB, c.n - r);
     const T* invb = c.inv + b * (size_t)(NB * NB);
     cudaError_t e;
+    if ((e = need_columns(c, r, r + nv)) != cudaSuccess) return e;
     // In place when the TMA kernels can take the panel: their CTA tile is 128 rows (Left) or 128
     // columns (Right) = the whole block, so each CTA reads exactly the part of B it later overwrites,
     // and reads all of it (every K slab) before its epilogue stores; beta = 0 never reads C.
@@ -197,10 +242,12 @@ cudaError_t solve_range(const TrsmCtx<T>& c, size_t b0, size_t b1, T alpha)
         if (!c.right) {
             // B2 = alpha*B2 - op(A)[2,1] * X1 ; op(A)[2,1] is A[2,1] or A[1,2]^T
             const T* A21 = c.trans ? c.A + r0 + r1 * c.lda : c.A + r1 + r0 * c.lda;
+            if ((e = c.trans ? need_columns(c, r1, r2) : need_columns(c, r0, r1)) != cudaSuccess) return e;
             e = gemm_call<T>(c.trans, false, n2, c.N, n1, T(-1), A21, c.lda, c.B + r0, c.ldb, alpha, c.B + r1, c.ldb, c.s);
         } else {
             // X op(A) = alpha B with op(A) upper: B2 = alpha*B2 - X1 * op(A)[1,2]
             const T* A12 = c.trans ? c.A + r1 + r0 * c.lda : c.A + r0 + r1 * c.lda;
+            if ((e = c.trans ? need_columns(c, r0, r1) : need_columns(c, r1, r2)) != cudaSuccess) return e;
             e = gemm_call<T>(false, c.trans, c.M, n2, n1, T(-1), c.B + r0 * c.ldb, c.ldb, A12, c.lda, alpha,
                              c.B + r1 * c.ldb, c.ldb, c.s);
         }
@@ -211,10 +258,12 @@ cudaError_t solve_range(const TrsmCtx<T>& c, size_t b0, size_t b1, T alpha)
     if (!c.right) {
         // op(A) upper: B1 = alpha*B1 - op(A)[1,2] * X2
         const T* A12 = c.trans ? c.A + r1 + r0 * c.lda : c.A + r0 + r1 * c.lda;
+        if ((e = c.trans ? need_columns(c, r0, r1) : need_columns(c, r1, r2)) != cudaSuccess) return e;
         e = gemm_call<T>(c.trans, false, n1, c.N, n2, T(-1), A12, c.lda, c.B + r1, c.ldb, alpha, c.B + r0, c.ldb, c.s);
     } else {
         // X op(A) = alpha B with op(A) lower: B1 = alpha*B1 - X2 * op(A)[2,1]
         const T* A21 = c.trans ? c.A + r0 + r1 * c.lda : c.A + r1 + r0 * c.lda;
+        if ((e = c.trans ? need_columns(c, r1, r2) : need_columns(c, r0, r1)) != cudaSuccess) return e;
         e = gemm_call<T>(false, c.trans, c.M, n1, n2, T(-1), c.B + r1 * c.ldb, c.ldb, A21, c.lda, alpha,
                          c.B + r0 * c.ldb, c.ldb, c.s);
     }
@@ -226,38 +275,27 @@ cudaError_t solve_range(const TrsmCtx<T>& c, size_t b0, size_t b1, T alpha)
 
 template <typename T>
 cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t M, size_t N, T alpha,
-                          const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s)
+                          const T* A, size_t lda, T* B, size_t ldb, cudaStream_t s, TrsmPanelGate* gate)
 {
     if (M == 0 || N == 0) return cudaSuccess;
     if (alpha == T(0)) return launch_scale<T>(M, N, T(0), B, ldb, s);   // BLAS: B <- 0, A not referenced
 
     TrsmCtx<T> c;
-    c.right = right; c.lower = lower; c.trans = trans; c.eff_lower = (lower != trans);
-    c.M = M; c.N = N; c.n = right ? N : M; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.s = s;
+    c.right = right; c.lower = lower; c.trans = trans; c.eff_lower = (lower != trans); c.unit = unit;
+    c.M = M; c.N = N; c.n = right ? N : M; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.s = s; c.gate = gate;
     const size_t nblk = (c.n + NB - 1) / NB;
     const size_t inv_elems = nblk * (size_t)(NB * NB);
     const size_t tmp_elems = (size_t)NB * (right ? M : N);
 
+    cudaError_t e = trtri_prepare<T>();
+    if (e != cudaSuccess) return e;
     T* ws = nullptr;
-    cudaError_t e = ws_alloc(reinterpret_cast<void**>(&ws), (inv_elems + tmp_elems) * sizeof(T), s);
+    e = ws_alloc(reinterpret_cast<void**>(&ws), (inv_elems + tmp_elems) * sizeof(T), s);
     if (e != cudaSuccess) return e;
     c.inv = ws;
     c.tmp = ws + inv_elems;
 
-    const size_t smem = (size_t)(NB * NB + 2 * NB) * sizeof(T);
-    // The opt-in to more than 48 KB of dynamic shared memory is a per-device function attribute.
-    static bool attr_done[2][64] = {};
-    const int ti = sizeof(T) == 8;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_done[ti][dev]) {
-        e = cudaFuncSetAttribute(trtri_diag_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { ws_free(ws, s); return e; }
-        if (dev >= 0 && dev < 64) attr_done[ti][dev] = true;
-    }
-    trtri_diag_kernel<T><<<(unsigned)nblk, TRTRI_THREADS, smem, s>>>(A, lda, c.n, lower, unit, c.inv);
-    count_launch();
-    e = cudaGetLastError();
+    if (gate == nullptr) e = invert_blocks(c, 0, nblk);    // with a gate: panel by panel, as the panels arrive
     if (e == cudaSuccess) e = solve_range<T>(c, 0, nblk, alpha);
     cudaError_t e2 = ws_free(ws, s);
     return e != cudaSuccess ? e : e2;
@@ -301,9 +339,14 @@ static cudaError_t noalloc_scratch_address(double** out)
         double* p = nullptr;
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_dtrsm_noalloc_scratch);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(trtri_diag_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)((size_t)(NB * NB + 2 * NB) * sizeof(double)));
-        if (e != cudaSuccess) return e;
+        // Everything else a solve can need for the first time on this device is done here as well: the
+        // shared-memory opt-in of the inversion kernel and of every GEMM kernel the dispatcher can choose
+        // without allocating, each of them loaded (cudaFuncGetAttributes) -- so that no later call, whatever its
+        // transposition, width or alignment, has any first-time work left.
+        if ((e = trtri_prepare<double>()) != cudaSuccess) return e;
+        cudaFuncAttributes fa;
+        if ((e = cudaFuncGetAttributes(&fa, trtri_diag_kernel<double>)) != cudaSuccess) return e;
+        if ((e = dgemm_prepare_all_kernels()) != cudaSuccess) return e;
         addr[dev] = p;
     }
     *out = addr[dev];
@@ -324,16 +367,12 @@ cudaError_t dtrsm_colmajor_noalloc(bool right, bool lower, bool trans, bool unit
     ScopedNoAlloc no_alloc;          // the GEMM dispatcher must not repack operands into a workspace here
 
     TrsmCtx<double> c;
-    c.right = right; c.lower = lower; c.trans = trans; c.eff_lower = (lower != trans);
+    c.right = right; c.lower = lower; c.trans = trans; c.eff_lower = (lower != trans); c.unit = unit;
     c.M = M; c.N = N; c.n = n; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.s = s;
     c.inv = ws;
     c.tmp = ws + NOALLOC_INV_ELEMS;
     const size_t nblk = (n + NB - 1) / NB;
-    const size_t smem = (size_t)(NB * NB + 2 * NB) * sizeof(double);
-    trtri_diag_kernel<double><<<(unsigned)nblk, TRTRI_THREADS, smem, s>>>(A, lda, n, lower, unit, c.inv);
-    count_launch();
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
+    if ((e = invert_blocks(c, 0, nblk)) != cudaSuccess) return e;
     return solve_range<double>(c, 0, nblk, alpha);
 }
 
@@ -474,15 +513,11 @@ cudaError_t ctrsm_left(bool lower, int op, bool unit, size_t M, size_t N, const 
     c.A = E; c.lda = lde;
 
     const size_t smem = (size_t)(2 * CNB * CNB + CNB) * 2 * sizeof(R);
-    static bool attr_done[2][64] = {};
-    const int ti = sizeof(R) == 8;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_done[ti][dev]) {
-        e = cudaFuncSetAttribute(ctrtri_diag_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { ws_free(ws, s); return e; }
-        if (dev >= 0 && dev < 64) attr_done[ti][dev] = true;
-    }
+    static DeviceOnce once[2];
+    e = once[sizeof(R) == 8].run([smem] {
+        return cudaFuncSetAttribute(ctrtri_diag_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    });
+    if (e != cudaSuccess) { ws_free(ws, s); return e; }
     ctrtri_diag_kernel<R><<<(unsigned)nblk, CNB, smem, s>>>(A, lda, M, lower, unit, conj, c.inv);
     count_launch();
     e = cudaGetLastError();
@@ -539,8 +574,8 @@ template cudaError_t ctrsm_colmajor<double>(bool, bool, int, bool, size_t, size_
                                             double*, size_t, cudaStream_t);
 
 template cudaError_t trsm_colmajor<float>(bool, bool, bool, bool, size_t, size_t, float, const float*, size_t,
-                                          float*, size_t, cudaStream_t);
+                                          float*, size_t, cudaStream_t, TrsmPanelGate*);
 template cudaError_t trsm_colmajor<double>(bool, bool, bool, bool, size_t, size_t, double, const double*, size_t,
-                                           double*, size_t, cudaStream_t);
+                                           double*, size_t, cudaStream_t, TrsmPanelGate*);
 
 }  // namespace cb200

@@ -6,12 +6,14 @@
 // (src/library/blas/xtrsm.cc:1183-1207, :1499-1500).
 #include "common.h"
 
+#include <atomic>
 #include <mutex>
 
 namespace cb200 {
 
 namespace {
 std::mutex g_mu;
+std::atomic<unsigned long long> g_allocs{0};
 cudaMemPool_t g_pool[64] = {};
 
 cudaError_t pool_for_current_device(cudaMemPool_t* out)
@@ -41,11 +43,14 @@ cudaError_t pool_for_current_device(cudaMemPool_t* out)
 
 cudaError_t ws_alloc(void** ptr, size_t bytes, cudaStream_t s)
 {
+    g_allocs.fetch_add(1, std::memory_order_relaxed);
     cudaMemPool_t pool;
     cudaError_t e = pool_for_current_device(&pool);
     if (e != cudaSuccess) return e;
     return cudaMallocFromPoolAsync(ptr, bytes, pool, s);
 }
+
+unsigned long long ws_alloc_count() { return g_allocs.load(std::memory_order_relaxed); }
 
 cudaError_t ws_free(void* ptr, cudaStream_t s) { return cudaFreeAsync(ptr, s); }
 

@@ -100,9 +100,17 @@ void clblasTeardown(void);
  *      NULL A/B/C -> InvalidMat{A,B,C}; if K != 0: A then B sizes; always C sizes;
  *      M == 0 or N == 0 -> InvalidDim; short ld -> InvalidLeadDim{A,B,C}; matrix extent beyond
  *      the CUDA allocation holding the pointer -> InsufficientMemMat{A,B,C}.
- *      numCommandQueues >= 1; only commandQueues[0] is used (one call = one device).
+ *      numCommandQueues >= 1.  With one queue the whole product runs on it.  With several, N is cut into
+ *      one stripe per queue, boundaries multiples of 128, and stripe q runs on commandQueues[q] -- what the
+ *      reference's multi-queue GEMM does (xgemm.cc:603-658; stripes of
+ *      src/library/blas/generic/solution_seq_make.c:764-866).  The matrices live on the device of
+ *      commandQueues[0]; a queue on another device of the same process is given copies of A and of its
+ *      stripes of B and C, and its stripe of C is copied back before its event is recorded (OpenCL queues
+ *      of one context share their buffers, GPUs do not).  Every other level-3 routine of this library does
+ *      its work on commandQueues[0], as the reference's TRSM does (src/library/blas/xtrsm.cc:1626-1629).
  *      The call is asynchronous: work is ordered after every event of eventWaitList and, when
- *      events != NULL, events[0] must be a created cudaEvent_t that is recorded on completion. */
+ *      events != NULL, every non-NULL events[q] (q < numCommandQueues) must be a created cudaEvent_t; it
+ *      is recorded on commandQueues[q] when the work that queue has to wait for is complete. */
 clblasStatus clblasSgemm(
     clblasOrder order, clblasTranspose transA, clblasTranspose transB,
     size_t M, size_t N, size_t K,
@@ -310,8 +318,10 @@ clblasStatus clblasDsymm(
  *      Limits: order of A (M for Left, N for Right) <= CLBLAS_B200_NOALLOC_MAX_ORDER and the other
  *      dimension of B <= CLBLAS_B200_NOALLOC_MAX_OTHER; larger problems return
  *      clblasOutOfResources and touch nothing.
- *      The first call on each device looks up the array's device address and sets a kernel
- *      attribute; make that first call before starting any stream capture.
+ *      The first call on each device does all the one-time work the entry point can ever need there: it
+ *      looks up the array's device address, and it sets the shared-memory attribute of, and loads, every
+ *      kernel a later call may dispatch to, whatever that call's transposition, width or alignment.  Make that
+ *      first call before starting any stream capture.
  *      Every call on a device uses the same array: calls that may overlap on the GPU (streams with
  *      no ordering between them) race and give wrong results -- order them on one stream or with
  *      events.  What an earlier call left in the array never influences a later one. */
@@ -334,6 +344,100 @@ clblasStatus clblasB200DtrsmNoAlloc(
  *      `bounds` (bounds[0] = 0, bounds[parts] = total).  Pure host arithmetic; no CUDA call. */
 clblasStatus clblasB200PlanShards(size_t total, unsigned parts, size_t align, size_t* bounds);
 
+/* ---- one process (or thread) per GPU: the sharded forms.  They replace, for GPUs that do not share
+ *      buffers, the reference's "one SolutionStep per command queue" execution
+ *      (src/library/blas/generic/solution_seq_make.c:371-419, stripes :764-866) and the round-robin
+ *      queue use of its GEMM (src/library/blas/xgemm.cc:603-658).
+ *
+ *      A communicator joins `nranks` GPUs of one box.  NCCL carries the traffic and is loaded at run
+ *      time (dlopen of libnccl.so.2; a copy already mapped by the process is preferred; the environment
+ *      variable CLBLAS_B200_NCCL_LIB names another); without it these calls return clblasNotImplemented.
+ *      clblasB200CommGetUniqueId: one rank obtains 128 bytes and hands them to the others by any means.
+ *      clblasB200CommInitRank: collective; call it with the rank's device current.  nranks == 1 needs no id.
+ *      clblasB200CommInitAll: all ranks of one process at once (devices == NULL: devices 0..ndev-1), for a
+ *      program that drives each GPU from its own thread.
+ *      clblasB200CommDestroy: collective in effect (every rank destroys its end). */
+#define CLBLAS_B200_UNIQUE_ID_BYTES 128
+typedef void* clblasB200Comm;
+clblasStatus clblasB200CommGetUniqueId(void* id128);
+clblasStatus clblasB200CommInitRank(clblasB200Comm* comm, const void* id128, int nranks, int rank);
+clblasStatus clblasB200CommInitAll(clblasB200Comm* comms, int ndev, const int* devices);
+clblasStatus clblasB200CommDestroy(clblasB200Comm comm);
+clblasStatus clblasB200CommInfo(clblasB200Comm comm, int* nranks, int* rank);
+
+/*      clblasB200{S,D}gemmSharded: the argument list of clblasSgemm / clblasDgemm on ONE RANK'S SHARD, plus
+ *      the communicator and the root rank.  Column-major: N is the number of columns of op(B) and C this rank
+ *      owns (B and C point at the rank's own column block; boundaries as clblasB200PlanShards gives them;
+ *      N == 0 is legal); A is the whole matrix on the root and a buffer of the same extent
+ *      (same lda) on every other rank, which the call fills: A is broadcast in column panels of the matrix
+ *      as stored, on a second stream, and the product of panel p starts when panel p has arrived, so the
+ *      transfer of later panels overlaps the products (transA == NoTrans: K slabs accumulated with beta on
+ *      the first and 1 afterwards, the reference's K split,
+ *      src/library/blas/specialCases/GemmSpecialCases.cpp:127-191; otherwise blocks of rows of C).
+ *      Row-major: the roles swap with the operands (src/library/blas/xgemm.cc:40-61): M counts the rank's
+ *      rows of op(A) and C, and B is the broadcast matrix.
+ *      M, K, alpha, the transpositions, the layout of the broadcast matrix and `root` must agree on all
+ *      ranks; every rank of the communicator must make the call.  comm == NULL or a communicator of one
+ *      rank: a plain GEMM.  Checks and status codes as clblasSgemm.  Work is issued on commandQueues[0]
+ *      (and the communicator's own stream); the call is asynchronous like every other one. */
+clblasStatus clblasB200SgemmSharded(
+    clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+    size_t M, size_t N, size_t K,
+    float alpha,
+    clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    float beta,
+    clblasMem C, size_t offC, size_t ldc,
+    clblasB200Comm comm, int root,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasB200DgemmSharded(
+    clblasOrder order, clblasTranspose transA, clblasTranspose transB,
+    size_t M, size_t N, size_t K,
+    double alpha,
+    clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    double beta,
+    clblasMem C, size_t offC, size_t ldc,
+    clblasB200Comm comm, int root,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+/*      clblasB200{S,D}trsmSharded: the argument list of clblasStrsm / clblasDtrsm on one rank's shard of the
+ *      right-hand sides: the dimension of B that is not the order of A (N for Left, M for Right) counts what
+ *      this rank owns (zero is legal) and B points at the rank's own block.  A is the whole triangular matrix
+ *      on the root and a buffer of the same extent elsewhere; it is broadcast in column panels in the order
+ *      the substitution reaches them, small panels first, and each step of the blocked solve waits only for
+ *      the panels it reads, so the solve starts after the first panel and the rest of the transfer is hidden
+ *      behind it.  No other exchange takes place: right-hand sides are independent
+ *      (the reference's split, src/library/blas/generic/solution_seq_make.c:785-866). */
+clblasStatus clblasB200StrsmSharded(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    float alpha,
+    clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    clblasB200Comm comm, int root,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+clblasStatus clblasB200DtrsmSharded(
+    clblasOrder order, clblasSide side, clblasUplo uplo, clblasTranspose transA, clblasDiag diag,
+    size_t M, size_t N,
+    double alpha,
+    clblasMem A, size_t offA, size_t lda,
+    clblasMem B, size_t offB, size_t ldb,
+    clblasB200Comm comm, int root,
+    unsigned numCommandQueues, clblasQueue* commandQueues,
+    unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
+
+/*      The panel plan the sharded calls use for a matrix of `columns` stored columns: a first panel of about
+ *      1/32 of the columns (at least min_columns), each next one twice as wide, boundaries multiples of 128,
+ *      at most max_panels panels.  Writes count+1 boundaries (bounds needs max_panels+1 entries).  Pure host
+ *      arithmetic, exported for the tests. */
+clblasStatus clblasB200PanelPlan(size_t columns, size_t min_columns, unsigned max_panels, size_t* bounds, unsigned* count);
+
 /* ---- introspection used by the benchmark client and the tests (no reference counterpart
  *      beyond the AUTOGEMM_PRINT_DEBUG kernel-name print of xgemm.cc:437-445) ------------- */
 
@@ -351,6 +455,16 @@ double clblasB200ProbePeak(int kind, double seconds);
 /* Name of the kernel family the most recent GEMM of the calling thread dispatched to
  * ("dgemm_mma_tma", "sgemm_ffma_tma", "gemm_simt_ldg", ...).  Static storage; never NULL. */
 const char* clblasB200LastGemmKernel(void);
+/* The instantiation and mode behind that name, e.g. "dgemm_mma_tma<T,N,128>+streamk_tail",
+ * "sgemm_ffma_tma<N,N,64,3,2>+splitk2", "sgemm_nt_16x8+tri": lets a test assert which variant it exercised.
+ * Thread-local storage, overwritten by the thread's next GEMM; never NULL. */
+const char* clblasB200LastGemmVariant(void);
+/* Number of workspace allocations the level-3 routines of this library have made in the calling process so far
+ * (operand repacking, split-K and stream-K partial tiles, TRSM's inverted blocks ...).  A call across which the
+ * number does not change allocated nothing. */
+unsigned long long clblasB200WorkspaceAllocCount(void);
+/* The two size limits of clblasB200DtrsmNoAlloc as the built library has them (= the macros above). */
+void clblasB200NoAllocLimits(size_t* max_order, size_t* max_other);
 /* Forces a kernel family for GEMM calls of the whole process: 0 = automatic dispatch,
  * 1 = always the alignment-free LDG path, 2 / 3 = SGEMM TMA path with one / two CTAs per SM
  * (tuning aid; operands the TMA path cannot address still take the LDG path),
