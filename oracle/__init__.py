@@ -394,3 +394,53 @@ def trsm_backward_ratio(X, alpha, T, B_in, side, dtype):
 
 def op(mat, trans):
     return mat if trans == NoTrans else mat.T
+
+
+def trsm_delta(side, uplo, transA, diag, A, B, alpha, dtype):
+    """The reference's element-wise acceptance bound for TRSM, trsmDelta
+    (src/tests/correctness/trsm-delta.h:44-240), on logical matrices: A the stored triangular matrix
+    (only its diagonal is read), B the right-hand sides BEFORE the solve.  Returns delta (M x N): the
+    reference accepts a result when |X_blas - X_library| <= delta entry by entry
+    (compareMatrices, src/tests/include/matrix.h:301-329).
+
+    delta = (error of plain substitution) + (extra error of the reference's blocked algorithm):
+    with e[i, k] = |B[i, k] / A[i, i]| * DELTA_0 * |alpha| (DELTA_0 = 2^-20 for float, 2^-50 for double; the
+    division only for a non-unit diagonal), the first term is the running sum of e along the direction of
+    substitution, the second one bsize (32) times a weighted sum of that running sum at the same offset inside
+    each block of 32, the weights counting how many later blocks a block's error propagates into.
+    The Right / lower-triangular branch of the reference stops its block loop at (k + 31) / 32, so it adds
+    at most the term of k's own block; that is restated as it stands."""
+    d0 = 2.0 ** -20 if np.dtype(dtype) == np.float32 else 2.0 ** -50
+    bs = 32
+    B64 = np.abs(np.asarray(B, dtype=np.float64))
+    M, N = B64.shape
+    is_upper = (uplo == Upper) == (transA == NoTrans)
+    dd = np.abs(np.diagonal(np.asarray(A, dtype=np.float64))) if diag == NonUnit else None
+    amod = abs(alpha)
+    block = np.zeros((M, N))
+    if side == Left:
+        e = (B64 / dd[:, None] if dd is not None else B64) * d0 * amod
+        gauss = np.cumsum(e[::-1], axis=0)[::-1] if is_upper else np.cumsum(e, axis=0)
+        nblk = (M + bs - 1) // bs
+        for i in range(M):
+            if is_upper:
+                js, zs = range(i // bs, nblk), range(1, nblk - i // bs + 1)
+            else:
+                js, zs = range(0, i // bs + 1), range(i // bs + 1, 0, -1)
+            for j, z in zip(js, zs):
+                idx = j * bs + i % bs
+                if idx < M:
+                    block[i] += z * gauss[idx]
+    else:
+        e = (B64 / dd[None, :] if dd is not None else B64) * d0 * amod
+        gauss = np.cumsum(e, axis=1) if is_upper else np.cumsum(e[:, ::-1], axis=1)[:, ::-1]
+        for k in range(N):
+            if is_upper:
+                js, zs = range(0, k // bs + 1), range(k // bs + 1, 0, -1)
+            else:
+                js, zs = range(k // bs, (k + bs - 1) // bs), range(1, bs + 2)
+            for j, z in zip(js, zs):
+                idx = j * bs + k % bs
+                if idx < N:
+                    block[:, k] += z * gauss[:, idx]
+    return gauss + block * bs

@@ -1,0 +1,217 @@
+"""The reference suite's large cases and one test per kernel instantiation, through the C ABI.
+
+* TRSM over order x side x uplo x trans x diag at order 1100 (nine 128-blocks, odd splits at every level of the
+  recursion) and one pass at the reference's "Big" size 2801 x 2903
+  (src/tests/correctness/test-correctness.cpp:831-853, :994-1016); accepted by the backward-error bound AND by the
+  reference's own element-wise rule (trsmDelta, src/tests/correctness/trsm-delta.h:44-240) against the oracle.
+* GEMM "SelectedBig" shapes 5777 x 5333 x 3000 T/N and 6777 x 3333 x 3000 T/ConjTrans (:675-700), integer-valued
+  inputs whose partial sums are exact, so any correct summation order gives the same bits: the expected result is a
+  float64 host product of the same integers.
+* Products sized so that each variant of the kernels is the one that runs -- asserted through
+  clblasB200LastGemmVariant -- the 16 x 8 register-tile SGEMM and its triangular instantiation (SSYRK, CHERK),
+  the DGEMM stream-K tail, SGEMM split-K.
+* Several command queues on one device (the reference's MultipleQueues cases, :3006-3042: sizes 513 and 1025).
+* A conditioning sweep of the inverse-based TRSM.
+"""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import ColumnMajor, ConjTrans, Left, Lower, NonUnit, NoTrans, Right, RowMajor, Trans, Unit, Upper
+from tests import cases
+from tests.gpu_util import dev, outside_untouched, run_gemm_gpu, run_trsm_gpu, run_trsm_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _check_trsm(cb, c, with_oracle=True):
+    logical = cases.trsm_logical(c)
+    bufs = cases.trsm_buffers(c, logical)
+    st, got = run_trsm_gpu(cb, c, bufs)
+    assert st == cb.clblasSuccess, (cb.STATUS_NAME.get(st, st), c)
+    assert outside_untouched(bufs[1], got, c), c
+    dt = cases.DT[c["prec"]]
+    X = oracle.view(got, c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
+    assert np.all(np.isfinite(X)), c
+    A, B = logical
+    T = cases.trsm_op_triangle(c, A)
+    ratio = oracle.trsm_backward_ratio(X, c["alpha"], T, B, c["side"], dt)
+    assert ratio <= 1.0, (ratio, c)
+    if with_oracle:
+        want = run_trsm_oracle(c, bufs)
+        Xo = oracle.view(want, c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
+        delta = oracle.trsm_delta(c["side"], c["uplo"], c["transA"], c["diag"], oracle.clean_triangle(A, c["uplo"], c["diag"]),
+                                  B, c["alpha"], dt)
+        worst = float(np.max(np.abs(X.astype(np.float64) - Xo.astype(np.float64)) / delta))
+        assert worst <= 1.0, (worst, c)            # the reference's own acceptance rule
+
+
+@pytest.mark.parametrize("prec", ["s", "d"])
+def test_trsm_order_1100_all_variants(lib, prec):
+    seed = 7000
+    for order, side, uplo, ta, diag in itertools.product((ColumnMajor, RowMajor), (Left, Right), (Upper, Lower),
+                                                         (NoTrans, Trans, ConjTrans), (Unit, NonUnit)):
+        seed += 1
+        M, N = (1100, 200) if side == Left else (200, 1100)
+        _check_trsm(lib, cases.trsm_case(prec, order, side, uplo, ta, diag, M, N, alpha=[1.0, 2.5, -0.5][seed % 3],
+                                         pad=(seed % 5, seed % 7), off=(seed % 3, seed % 11), seed=seed))
+    assert lib.device_fault() == 0
+
+
+@pytest.mark.parametrize("prec,order,side,uplo,ta", [("d", ColumnMajor, Left, Lower, NoTrans), ("s", RowMajor, Right, Upper, Trans)])
+def test_trsm_reference_big_size(lib, prec, order, side, uplo, ta):
+    _check_trsm(lib, cases.trsm_case(prec, order, side, uplo, ta, NonUnit, 2801, 2903, alpha=1.5, seed=7100), with_oracle=False)
+
+
+def _exact_gemm(cb, prec, order, ta, tb, M, N, K, alpha=2.0, beta=3.0, pad=(0, 0, 0), off=(0, 0, 0), seed=8000, queues=None):
+    """Integer-valued inputs (bounds of the reference's generator, src/tests/include/blas-random.h:29-94): the
+    device result must equal the float64 host product of the same integers bit for bit."""
+    c = cases.gemm_case(prec, order, ta, tb, M, N, K, alpha=alpha, beta=beta, pad=pad, off=off, mode="int", seed=seed)
+    opA, opB, C = cases.gemm_logical(c)
+    bufs = cases.gemm_buffers(c, (opA, opB, C))
+    if queues is None:
+        st, got = run_gemm_gpu(cb, c, bufs)
+    else:
+        dA, dB, dC = (dev(b) for b in bufs)
+        fn = cb.clblasSgemm if prec == "s" else cb.clblasDgemm
+        events = [torch.cuda.Event() for _ in queues]
+        for e, q in zip(events, queues):
+            e.record(q)
+        torch.cuda.synchronize()
+        st = fn(c["order"], c["transA"], c["transB"], M, N, K, alpha, dA, c["offA"], c["lda"], dB, c["offB"], c["ldb"], beta,
+                dC, c["offC"], c["ldc"], queues=queues, events=events)
+        for e in events:
+            e.synchronize()                        # the caller's only way to know: every queue's event
+        got = dC.cpu().numpy()
+    assert st == cb.clblasSuccess, cb.STATUS_NAME.get(st, st)
+    exact = alpha * (opA.astype(np.float64) @ opB.astype(np.float64)) + beta * C.astype(np.float64)
+    want = oracle.pack(exact.astype(cases.DT[prec]), order, NoTrans, c["ldc"], c["offC"], tail=3)
+    assert outside_untouched(bufs[2], got, c), c
+    mask = ~oracle.outside_mask(got.size, order, NoTrans, M, N, c["ldc"], c["offC"])
+    # equal as numbers: where the exact result is zero its sign depends on the order of two exact operations
+    # (alpha * 0 against beta * c + alpha * 0), which is not part of the reference's rule either (it compares values)
+    assert np.array_equal(got[mask], want[mask]), (c, float(np.max(np.abs(got[mask] - want[mask]))))
+    return cb.last_gemm_variant()
+
+
+@pytest.mark.parametrize("order", [ColumnMajor, RowMajor])
+def test_gemm_reference_big_shapes(lib, order):
+    _exact_gemm(lib, "d", order, Trans, NoTrans, 5777, 5333, 3000, seed=8001)
+    _exact_gemm(lib, "s", order, Trans, ConjTrans, 6777, 3333, 3000, seed=8002)
+    _exact_gemm(lib, "d", order, NoTrans, NoTrans, 2801, 2903, 3005, seed=8003)
+    assert lib.device_fault() == 0
+
+
+def test_sgemm_16x8_register_tile_kernel_is_exact(lib):
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3200, 3200, 1024, seed=8010)
+    assert v == "sgemm_nt_16x8", v
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3200 - 37, 3200 + 5, 1024 + 19, alpha=-1.0, beta=0.0, seed=8011)
+    assert v == "sgemm_nt_16x8", v               # ragged edges in M, N and K
+
+
+def test_dgemm_streamk_tail_and_sgemm_splitk_are_exact(lib):
+    v = _exact_gemm(lib, "d", ColumnMajor, Trans, NoTrans, 2048, 2048, 2048, seed=8020)
+    assert v.endswith("+streamk_tail"), v
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, NoTrans, 768, 768, 2048, seed=8021)
+    assert "+splitk" in v, v
+    v = _exact_gemm(lib, "d", ColumnMajor, NoTrans, Trans, 128, 1000, 128, seed=8022)
+    assert v.startswith("dgemm_mma_tma<N,T,") and not v.startswith("dgemm_mma_tma<N,T,128>"), v     # a narrow-tile variant
+
+
+def test_triangular_16x8_kernel_through_ssyrk_and_cherk(lib):
+    """Rank-k updates large enough (676 tiles, K = 1024) for the triangular instantiation of the 16 x 8 kernel."""
+    n, k = 3328, 1024
+    g = oracle.rng(8030, 0)
+    A = g.integers(-3, 4, (n, k)).astype(np.float32)
+    C = np.tril(g.integers(-3, 4, (n, n))).astype(np.float32)
+    Cb = np.asfortranarray(C + np.triu(np.full((n, n), np.nan, np.float32), 1))      # the other triangle must not be touched
+    dA, dC = dev(np.asfortranarray(A).ravel(order="F").copy()), dev(Cb.ravel(order="F").copy())
+    st = lib.clblasSsyrk(ColumnMajor, Lower, NoTrans, n, k, 2.0, dA, 0, n, 3.0, dC, 0, n)
+    torch.cuda.synchronize()
+    assert st == lib.clblasSuccess and lib.last_gemm_variant() == "sgemm_nt_16x8+tri", lib.last_gemm_variant()
+    got = dC.cpu().numpy().reshape(n, n).T
+    want = 2.0 * (A.astype(np.float64) @ A.astype(np.float64).T) + 3.0 * C
+    assert np.array_equal(np.tril(got), np.tril(want).astype(np.float32))
+    assert np.all(np.isnan(got[np.triu_indices(n, 1)]))
+
+    # CHERK: C <- alpha*A*A^H + beta*C, complex64, lower triangle; integer parts, exact
+    n, k = 1792, 640
+    Ar, Ai = g.integers(-3, 4, (n, k)).astype(np.float64), g.integers(-3, 4, (n, k)).astype(np.float64)
+    Az = (Ar + 1j * Ai)
+    Cz = np.tril(g.integers(-3, 4, (n, n)) + 1j * g.integers(-3, 4, (n, n)))
+    Cz[np.diag_indices(n)] = Cz[np.diag_indices(n)].real
+    store = np.asfortranarray(Cz.astype(np.complex64))
+    store[np.triu_indices(n, 1)] = np.nan + 1j * np.nan
+    dA = dev(np.asfortranarray(Az.astype(np.complex64)).ravel(order="F").copy().view(np.float32))
+    dC = dev(store.ravel(order="F").copy().view(np.float32))
+    st = lib.clblasCherk(ColumnMajor, Lower, NoTrans, n, k, 2.0, dA, 0, n, -1.0, dC, 0, n)
+    torch.cuda.synchronize()
+    assert st == lib.clblasSuccess and "+tri" in lib.last_gemm_variant(), lib.last_gemm_variant()
+    got = dC.cpu().numpy().view(np.complex64).reshape(n, n).T
+    want = 2.0 * (Az @ Az.conj().T) - Cz
+    lo = np.tril_indices(n)
+    assert np.array_equal(got[lo], want[lo].astype(np.complex64))
+    assert lib.device_fault() == 0
+
+
+@pytest.mark.parametrize("nq", [2, 3, 7])
+def test_gemm_over_several_queues_of_one_device(lib, nq):
+    """numCommandQueues > 1: one stripe of N per queue, every queue's event recorded when its stripe is done."""
+    queues = [torch.cuda.Stream() for _ in range(nq)]
+    seed = 8100 + nq
+    for size, (ta, tb) in zip((513, 1025), ((NoTrans, NoTrans), (Trans, ConjTrans))):
+        for order in (ColumnMajor, RowMajor):
+            for prec in ("s", "d"):
+                seed += 1
+                _exact_gemm(lib, prec, order, ta, tb, size, size, size, pad=(3, 1, 2), off=(1, 2, 3), seed=seed, queues=queues)
+    assert lib.device_fault() == 0
+
+
+def test_other_routines_record_every_queue_event(lib):
+    """TRSM does its work on the first queue (as the reference's, src/library/blas/xtrsm.cc:1626-1629) and still
+    completes the event of every queue it was given."""
+    c = cases.trsm_case("d", ColumnMajor, Left, Lower, NoTrans, NonUnit, 300, 130, seed=8200)
+    logical = cases.trsm_logical(c)
+    A, B = cases.trsm_buffers(c, logical)
+    dA, dB = dev(A), dev(B)
+    queues = [torch.cuda.Stream() for _ in range(3)]
+    events = [torch.cuda.Event() for _ in queues]
+    for e, q in zip(events, queues):
+        e.record(q)
+    torch.cuda.synchronize()
+    st = lib.clblasDtrsm(c["order"], c["side"], c["uplo"], c["transA"], c["diag"], c["M"], c["N"], c["alpha"], dA, c["offA"], c["lda"],
+                         dB, c["offB"], c["ldb"], queues=queues, events=events)
+    assert st == lib.clblasSuccess
+    events[2].synchronize()                       # ordered after the solve although queue 2 did no work
+    X = oracle.view(dB.cpu().numpy(), c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
+    assert oracle.trsm_backward_ratio(X, c["alpha"], cases.trsm_op_triangle(c, logical[0]), logical[1], Left, np.float64) <= 1.0
+
+
+def test_trsm_backward_error_against_conditioning(lib):
+    """The solve multiplies by explicit inverses of the 128 x 128 diagonal blocks, so its backward error grows with
+    their condition number where substitution's does not.  Unit lower triangles with off-diagonal entries of growing
+    size give diagonal blocks with kappa from about 1e0 to beyond 1e10; the 4*M*u bound must hold while
+    kappa <= 1e6 (measured: 3 % of the bound there) and the error may grow at most in proportion to kappa beyond."""
+    n, nrhs = 512, 64
+    g = oracle.rng(8300, 0)
+    rows = []
+    for s in (0.02, 0.05, 0.08, 0.11, 0.14, 0.18, 0.22, 0.27, 0.33, 0.4):
+        L = np.tril(g.uniform(-1, 1, (n, n)), -1) * s * np.sign(g.uniform(-1, 1, (n, n))) + np.eye(n)
+        L = np.tril(np.abs(L), -1) * -1.0 + np.eye(n)         # same-sign entries: the inverse grows fastest
+        kappa = max(np.linalg.cond(L[b:b + 128, b:b + 128]) for b in range(0, n, 128))
+        B = g.standard_normal((n, nrhs))
+        dA, dB = dev(np.asfortranarray(L).ravel(order="F").copy()), dev(np.asfortranarray(B).ravel(order="F").copy())
+        st = lib.clblasDtrsm(ColumnMajor, Left, Lower, NoTrans, NonUnit, n, nrhs, 1.0, dA, 0, n, dB, 0, n)
+        torch.cuda.synchronize()
+        assert st == lib.clblasSuccess
+        X = dB.cpu().numpy().reshape(nrhs, n).T
+        ratio = oracle.trsm_backward_ratio(X, 1.0, L, B, Left, np.float64)
+        rows.append((kappa, ratio))
+    print("kappa of the worst diagonal block -> backward error / (4*M*u):", [(f"{k:.1e}", f"{r:.3g}") for k, r in rows])
+    for kappa, ratio in rows:
+        if kappa <= 1e6:
+            assert ratio <= 1.0, (kappa, ratio)
+        assert ratio <= max(1.0, kappa * 1e-6), (kappa, ratio)

@@ -65,3 +65,63 @@ def test_rejects_problems_beyond_the_scratch_array(lib):
     assert st == lib.clblasOutOfResources
     torch.cuda.synchronize()
     assert torch.equal(B, before)
+
+
+def _big_lower_system(n, nrhs, offA, lda, offB, ldb, seed):
+    """Left/Lower/NoTrans system generated on the device: diagonal in [1, 2], strict lower part U[-1, 1] / n, NaN above
+    the diagonal and in every element of both buffers that does not belong to a matrix."""
+    import torch
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    A = torch.full((offA + lda * n,), float("nan"), dtype=torch.float64, device="cuda")
+    Am = A[offA:].view(n, lda)[:, :n]                                  # Am[j, i] = A(i, j)
+    Am.copy_(torch.empty(n, n, dtype=torch.float64, device="cuda").uniform_(-1.0, 1.0, generator=g) / n)
+    Am.diagonal().uniform_(1.0, 2.0, generator=g)
+    iu = torch.triu_indices(n, n, offset=1, device="cuda")
+    Am[iu[1], iu[0]] = float("nan")
+    B = torch.full((offB + ldb * nrhs,), float("nan"), dtype=torch.float64, device="cuda")
+    B[offB:].view(nrhs, ldb)[:, :n].normal_(generator=g)
+    return A, B
+
+
+@pytest.mark.parametrize("n,nrhs,offA,pad_a,offB,pad_b", [
+    (4096, 8192, 3, 1, 5, 3),        # exactly the limits; odd offsets and leading dimensions: the update products cannot use TMA
+    (4096, 8192, 0, 0, 0, 0),        # exactly the limits, aligned: leaf products in place, updates with a partial last wave
+    (2432, 8192, 0, 0, 0, 0),        # 19 diagonal blocks: odd splits, update grids of 5 x 64 ... 10 x 64 tiles (partial waves)
+])
+def test_allocates_nothing_up_to_the_limits(lib, n, nrhs, offA, pad_a, offB, pad_b):
+    """The entry point is for callers who may not allocate, so the claim itself is checked: across a call the
+    library's workspace-allocation counter must not move, for problems large enough that the ordinary DTRSM
+    does allocate (inverted blocks; repacked operands for the unaligned case; stream-K partial tiles for update
+    products with a partial last wave), and the result must be the ordinary DTRSM's."""
+    import torch
+    assert n <= lib.NOALLOC_MAX_ORDER and nrhs <= lib.NOALLOC_MAX_OTHER
+    lda, ldb = n + pad_a, n + pad_b
+    A, B0 = _big_lower_system(n, nrhs, offA, lda, offB, ldb, seed=41)
+    args = (ColumnMajor, Left, Lower, NoTrans, NonUnit, n, nrhs, 1.0, A, offA, lda)
+    lib.clblasB200DtrsmNoAlloc(ColumnMajor, Left, Lower, NoTrans, NonUnit, 8, 8, 1.0, A, offA, lda, B0.clone(), offB, ldb)   # one-time set-up
+    torch.cuda.synchronize()
+    X = B0.clone()
+    before = lib.workspace_alloc_count()
+    st = lib.clblasB200DtrsmNoAlloc(*args, X, offB, ldb)
+    torch.cuda.synchronize()
+    assert st == lib.clblasSuccess, lib.STATUS_NAME.get(st, st)
+    assert lib.workspace_alloc_count() == before, "clblasB200DtrsmNoAlloc took a workspace"
+    Y = B0.clone()
+    st = lib.clblasDtrsm(*args, Y, offB, ldb)
+    torch.cuda.synchronize()
+    assert st == lib.clblasSuccess and lib.workspace_alloc_count() > before       # the ordinary entry point does allocate
+    Xm, Ym = X[offB:].view(nrhs, ldb)[:, :n], Y[offB:].view(nrhs, ldb)[:, :n]
+    assert bool(torch.isfinite(Xm).all())
+    assert float((Xm - Ym).abs().max()) <= 64 * n * 2.0 ** -53 * float(Ym.abs().max())
+    # padding and offset head untouched (NaN before and after)
+    outside = torch.ones_like(X, dtype=torch.bool)
+    outside[offB:].view(nrhs, ldb)[:, :n] = False
+    assert bool(torch.isnan(X[outside]).all())
+    # backward error of sampled columns on the host
+    cols = np.unique(np.concatenate([np.random.Generator(np.random.Philox(key=[9, 1])).choice(nrhs, 20, replace=False), [0, nrhs - 1]]))
+    ci = torch.from_numpy(cols).cuda()
+    Xs, Bs = Xm[ci].cpu().numpy().T, B0[offB:].view(nrhs, ldb)[:, :n][ci].cpu().numpy().T
+    T = np.tril(np.nan_to_num(A[offA:].view(n, lda)[:, :n].cpu().numpy().T, nan=0.0))
+    assert oracle.trsm_backward_ratio(Xs, 1.0, T, Bs, Left, np.float64) <= 1.0
+    assert lib.device_fault() == 0
