@@ -5,11 +5,12 @@
 // src/library/blas/AutoGemm/KernelOpenCL.py:13-459; hand-tuned 48x48 kernel
 // src/library/blas/AutoGemm/UserGemmKernelSources/dgemm_Col_TN_B1_MX048_NX048_KX08_src.cpp).
 //
-// CTA = 128 x BN tile of C (BN = 128; 64 or 32 for problems too narrow to fill the SMs with 128-wide
+// CTA = 128 x BN tile of C (BN = 128; 64, 32 or 16 for problems too narrow to fill the SMs with 128-wide
 // tiles, e.g. the panel products of TRSM), K in slabs of 16.  Warp 8 is the producer: one lane issues two TMA
 // bulk-tensor loads per slab (A and B) into a STAGES-deep ring in shared memory; full/empty
 // mbarriers carry the hand-over, all waits are bounded.  Warps 0-7 are consumers (2 x 4 grid,
-// 64 x BN/4 of C each, up to 128 accumulator registers per thread) issuing mma.sync.m8n8k4.f64.
+// 64 x BN/4 of C each, up to 128 accumulator registers per thread; 8 x 1 grid, 16 x 16 each, for BN = 16)
+// issuing mma.sync.m8n8k4.f64.
 // TMA zero-fills whatever lies beyond M, N or K, so ragged shapes need no separate edge launches
 // (the reference runs tile + row + column + corner kernels, src/library/blas/xgemm.cc:603-658);
 // only the epilogue is predicated.
@@ -68,9 +69,13 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int STAGE_BYTES = stage_bytes(BN);
     constexpr int PITCH_B = BN + 4;                 // doubles per k row of B, N-contiguous layout
-    constexpr int WN = BN / 4, NI = WN / 8;         // warp tile width, 8-wide sub-tiles per warp
+    constexpr int WARPS_M = BN >= 32 ? 2 : 8;       // consumer warps along M and along N
+    constexpr int WARPS_N = CONSUMER_WARPS / WARPS_M;
+    constexpr int WM = BM / WARPS_M, MI = WM / 8;   // warp tile height, 8-high sub-tiles per warp
+    constexpr int WN = BN / WARPS_N, NI = WN / 8;   // warp tile width, 8-wide sub-tiles per warp
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
+    pdl_launch_dependents();
 
     // grouped rasterisation: consecutive CTAs share A row-panels and B column-panels in L2
     unsigned tm, tn;
@@ -102,6 +107,7 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();               // everything below reads or writes global memory
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------- producer -------------------------------
@@ -124,22 +130,22 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
 
     // --------------------------------- consumers ---------------------------------
-    const int wm = warp % 2, wn = warp / 2;          // 2 x 4 warps, 64 x WN each
+    const int wm = warp % WARPS_M, wn = warp / WARPS_M;          // WARPS_M x WARPS_N warps, WM x WN each
     const int g = lane / 4, kk = lane % 4;
     const int pg = perm8(g);
 
     // byte offsets of this lane's fragment element inside an operand buffer, for k-step 0 and
     // sub-tile 0; sub-tiles and k-steps add compile-time constants (and one XOR for the swizzle).
     int offA, offB;
-    if (TA) offA = (wm * 64 + pg) * 128 + ((((kk >> 1) ^ (pg & 1))) << 4) + (kk & 1) * 8;
-    else    offA = kk * (MC_PITCH * 8) + (wm * 64 + g) * 8;
+    if (TA) offA = (wm * WM + pg) * 128 + ((((kk >> 1) ^ (pg & 1))) << 4) + (kk & 1) * 8;
+    else    offA = kk * (MC_PITCH * 8) + (wm * WM + g) * 8;
     if (!TB) offB = (wn * WN + pg) * 128 + ((((kk >> 1) ^ (pg & 1))) << 4) + (kk & 1) * 8;
     else     offB = kk * (PITCH_B * 8) + (wn * WN + g) * 8;
     const int xr = (pg & 6) << 4;                    // swizzle XOR applied to the 32-byte chunk of a k-step
 
-    double acc[8][NI][2];
+    double acc[MI][NI][2];
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < MI; i++)
 #pragma unroll
         for (int j = 0; j < NI; j++) acc[i][j][0] = acc[i][j][1] = 0.0;
 
@@ -150,9 +156,9 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         const unsigned char* sb = sa + A_BYTES;
 #pragma unroll
         for (int ks = 0; ks < BK / 4; ks++) {
-            double a[8], b[NI];
+            double a[MI], b[NI];
 #pragma unroll
-            for (int mi = 0; mi < 8; mi++) {
+            for (int mi = 0; mi < MI; mi++) {
                 const int o = TA ? offA + mi * 1024 + (((ks * 32) ^ xr))
                                  : offA + ks * 4 * (MC_PITCH * 8) + mi * 64;
                 a[mi] = *reinterpret_cast<const double*>(sa + o);
@@ -164,7 +170,7 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
                 b[ni] = *reinterpret_cast<const double*>(sb + o);
             }
 #pragma unroll
-            for (int mi = 0; mi < 8; mi++)
+            for (int mi = 0; mi < MI; mi++)
 #pragma unroll
                 for (int ni = 0; ni < NI; ni++) dmma(acc[mi][ni][0], acc[mi][ni][1], a[mi], b[ni]);
         }
@@ -183,8 +189,8 @@ dgemm_mma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
             if (col >= N) continue;
             double* cc = C + col * ldc;
 #pragma unroll
-            for (int mi = 0; mi < 8; mi++) {
-                const size_t row = m0 + wm * 64 + mi * 8 + (TA ? pg : g);
+            for (int mi = 0; mi < MI; mi++) {
+                const size_t row = m0 + wm * WM + mi * 8 + (TA ? pg : g);
                 if (row >= M || (TRI && tri_masked(tri, row, col))) continue;
                 double r = alpha * acc[mi][ni][e];
                 if (useC) r = fma(beta, cc[row], r);
@@ -234,6 +240,7 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     uint64_t* empty = full + STAGES;
     unsigned* s_ticket = reinterpret_cast<unsigned*>(empty + STAGES);
 
+    pdl_launch_dependents();
     const unsigned nk = (unsigned)((K + BK - 1) / BK);
     const unsigned u0 = blockIdx.x * upc, u1 = min(u0 + upc, units);
     if (u0 >= u1) return;
@@ -247,6 +254,7 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------- producer -------------------------------
@@ -467,14 +475,15 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
                 if (e == cudaSuccess) {
                     main_tiles = T - R;
                     set_last_variant(variant_name(TA, TB, BN, TRI, true));
-                    dgemm_mma_tma_kernel<TA, TB, BN, TRI><<<(unsigned)main_tiles, THREADS, smem_bytes(BN), s>>>(
-                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)S, p.tri);
+                    e = launch_pdl(dgemm_mma_tma_kernel<TA, TB, BN, TRI>, dim3((unsigned)main_tiles), dim3(THREADS), smem_bytes(BN), s,
+                                   mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)S, p.tri);
                     count_launch();
-                    dgemm_streamk_kernel<TA, TB><<<(unsigned)((units + upc - 1) / upc), THREADS, smem_bytes(128), s>>>(
-                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)main_tiles,
-                        (unsigned)units, (unsigned)upc, (unsigned)maxc, ws, counters);
-                    count_launch();
-                    e = cudaGetLastError();
+                    if (e == cudaSuccess) {
+                        e = launch_pdl(dgemm_streamk_kernel<TA, TB>, dim3((unsigned)((units + upc - 1) / upc)), dim3(THREADS), smem_bytes(128), s,
+                                       mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
+                                       (unsigned)main_tiles, (unsigned)units, (unsigned)upc, (unsigned)maxc, ws, counters);
+                        count_launch();
+                    }
                 }
                 const cudaError_t e2 = ws_free(ws, s);
                 return e != cudaSuccess ? e : e2;
@@ -483,10 +492,11 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
         }
     }
     set_last_variant(variant_name(TA, TB, BN, TRI, false));
-    dgemm_mma_tma_kernel<TA, TB, BN, TRI><<<(unsigned)main_tiles, THREADS, smem_bytes(BN), s>>>(
-        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 1), p.tri);
+    const cudaError_t e = launch_pdl(dgemm_mma_tma_kernel<TA, TB, BN, TRI>, dim3((unsigned)main_tiles), dim3(THREADS), smem_bytes(BN), s,
+                                     mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
+                                     (unsigned)(sm_count() * 1), p.tri);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // Shared-memory opt-in and module load of every instantiation without the triangular mode (what a
@@ -501,7 +511,9 @@ cudaError_t prepare_transposition()
     if ((e = prepare_main<TA, TB, 64, false>()) != cudaSuccess) return e;
     if ((e = cudaFuncGetAttributes(&fa, dgemm_mma_tma_kernel<TA, TB, 64, false>)) != cudaSuccess) return e;
     if ((e = prepare_main<TA, TB, 32, false>()) != cudaSuccess) return e;
-    return cudaFuncGetAttributes(&fa, dgemm_mma_tma_kernel<TA, TB, 32, false>);
+    if ((e = cudaFuncGetAttributes(&fa, dgemm_mma_tma_kernel<TA, TB, 32, false>)) != cudaSuccess) return e;
+    if ((e = prepare_main<TA, TB, 16, false>()) != cudaSuccess) return e;
+    return cudaFuncGetAttributes(&fa, dgemm_mma_tma_kernel<TA, TB, 16, false>);
 }
 
 template <int BN>
@@ -527,13 +539,14 @@ cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s, i
     if (!aligned16(p.A) || !aligned16(p.B) || (p.lda & 1) || (p.ldb & 1)) return cudaErrorNotSupported;
     if (p.M >= (1u << 31) || p.N >= (1u << 31) || p.K >= (1u << 31)) return cudaErrorNotSupported;
     const size_t tilesM = (p.M + BM - 1) / BM;
-    if (tilesM * ((p.N + 31) / 32) >= (1u << 31)) return cudaErrorNotSupported;
+    if (tilesM * ((p.N + 15) / 16) >= (1u << 31)) return cudaErrorNotSupported;
     set_last_kernel("dgemm_mma_tma");
     // Widest tile that still gives the 148 SMs about one CTA each; narrower tiles only for
     // problems that 128-wide tiles would leave most SMs idle on.
     if (min_bn >= 128 || tilesM * ((p.N + 127) / 128) >= 120) return launch_t<128>(p, s);
     if (tilesM * ((p.N + 63) / 64) >= 120) return launch_t<64>(p, s);
-    return launch_t<32>(p, s);
+    if (tilesM * ((p.N + 31) / 32) >= 120) return launch_t<32>(p, s);
+    return launch_t<16>(p, s);
 }
 
 cudaError_t dgemm_prepare_all_kernels()

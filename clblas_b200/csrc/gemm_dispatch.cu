@@ -7,12 +7,15 @@
 // questions are (1) can the operands be fetched by TMA (16-byte aligned base addresses and leading
 // dimensions) and (2) is it worth giving an operand a better layout first:
 //   * an operand TMA cannot address is copied once into an aligned workspace when the product is
-//     large enough for the copy to pay (BASELINE config 3: offsets 7/13/5, odd leading dimensions);
+//     large enough for the copy to pay (offsets of a few elements, odd leading dimensions);
 //   * for SGEMM a K-contiguous operand is transposed on the way, so that large products always run
 //     the fastest (N/T) variant of the FFMA kernel;
 //   * everything else (small or huge unaligned problems, or when allocation is not allowed) runs
 //     the alignment-free kernel in place.
 #include "common.h"
+
+#include <algorithm>
+#include <cstdlib>
 
 namespace cb200 {
 
@@ -74,12 +77,17 @@ cudaError_t gemm_any(const GemmProblem<T>& p, cudaStream_t s)
     Fix fa = KEEP, fb = KEEP;
     const bool may_alloc = t_forbid_alloc == 0 && forced_gemm_path() == PATH_AUTO;
     const double work = 2.0 * (double)p.M * (double)p.N * (double)p.K;
-    if (may_alloc && p.K >= 64 && work >= 1.5e10) {
+    static const double transpose_min_work = [] { const char* v = getenv("CLBLAS_B200_TRANSPOSE_MIN_WORK"); return v ? atof(v) : 4e9; }();
+    if (may_alloc && p.K >= 64 && work >= (kFloat ? std::min(transpose_min_work, 1.5e10) : 1.5e10)) {
         // The extra pass over an operand is paid back by the other dimension of C; products below
-        // about 2000^3 are too short for the extra launches to pay.
-        if (!okA && p.N >= 512) fa = COPY;
-        if (!okB && p.M >= 512) fb = COPY;
-        if (kFloat) {
+        // about 2000^3 are too short for the extra launches of a plain copy to pay.  A transposition for SGEMM
+        // pays from about 1500^3 on (N/N 1536^3: 40.6 in place, 49 TFLOP/s through the N/T kernel; 1024^3: 31.6
+        // either way): the kernels for K-contiguous operands are bound by shared-memory bandwidth.
+        if (work >= 1.5e10) {
+            if (!okA && p.N >= 512) fa = COPY;
+            if (!okB && p.M >= 512) fb = COPY;
+        }
+        if (kFloat && work >= transpose_min_work && (work >= 1.5e10 || (okA && okB && p.K >= 1024))) {
             if (p.ta && p.N >= 1024 && p.M >= 256) fa = TRANSPOSE;      // K-contiguous A -> M-contiguous
             if (!p.tb && p.M >= 1024 && p.N >= 256) fb = TRANSPOSE;     // K-contiguous B -> N-contiguous
         }

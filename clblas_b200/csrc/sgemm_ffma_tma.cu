@@ -74,9 +74,11 @@ template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS, bool TRI>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                      unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg, unsigned splits, size_t split_stride)
+                      unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg, unsigned splits, size_t split_stride,
+                      float* __restrict__ planes, size_t ldw, unsigned* __restrict__ tickets)
 {
     int tri = TRI ? tri_arg : TRI_FULL;
+    __shared__ unsigned s_ticket;
     constexpr int STAGE_BYTES = stage_bytes(BN);
     constexpr int NJ = BN / 16;                     // columns per thread: 8 or 4
     constexpr int NH = NJ / 4;                      // 4-column groups per thread (64 columns apart)
@@ -86,6 +88,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
+    pdl_launch_dependents();
 
     unsigned tm, tn;
     {
@@ -103,12 +106,12 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
     }
     // Split-K launches (gridDim.y = splits): this CTA owns K slabs [kt0, kt0 + nk) and writes its partial tile
-    // into plane blockIdx.y of a workspace; a reduction kernel sums the planes in a fixed order.
+    // into plane blockIdx.y of a workspace; the CTA of a tile that finishes last sums the planes in plane order
+    // (a fixed order, whoever finishes last) and writes C.
     const int nk_total = (int)((K + BK - 1) / BK);
     const int nk_per = (nk_total + (int)splits - 1) / (int)splits;
     const int kt0 = (int)blockIdx.y * nk_per;
     const int nk = max(0, min(nk_per, nk_total - kt0));
-    C += (size_t)blockIdx.y * split_stride;
     // Every other wave of CTAs walks K backwards: it starts on the K range the wave before it
     // finished on, which is what L2 still holds, instead of re-streaming those panels from DRAM.
     const bool reverse_k = wave != 0 && ((blockIdx.x / wave) & 1);
@@ -122,6 +125,7 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();               // everything below reads or writes global memory
 
     auto issue = [&](int kt) {
         const int s = kt % STAGES;
@@ -238,67 +242,96 @@ sgemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
             for (int j = 0; j < NJ; j++) unpack2(acc2[pr][j], acc[2 * pr][j], acc[2 * pr + 1][j]);
     }
 
-    // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
-    const bool useC = (beta != 0.f);
-    const bool vec = !TA && (!TRI || tri == TRI_FULL) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
+    // ---- epilogue: D = al*acc + be*D; be == 0 never reads D
+    auto epilogue = [&](float* D, size_t ldd, float al, float be, int trimode) {
+        const bool useC = (be != 0.f);
+        const bool vec = !TA && (!TRI || trimode == TRI_FULL) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0) && (ldd % 4 == 0);
 #pragma unroll
-    for (int j = 0; j < NJ; j++) {
-        const size_t col = n0 + colB(j);
-        if (col >= N) continue;
-        float* cc = C + col * ldc;
-        if (vec) {
+        for (int j = 0; j < NJ; j++) {
+            const size_t col = n0 + colB(j);
+            if (col >= N) continue;
+            float* cc = D + col * ldd;
+            if (vec) {
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const size_t row = m0 + tx * 4 + 64 * h;
-                if (row + 3 < M) {
-                    float4 r;
-                    r.x = alpha * acc[4 * h + 0][j]; r.y = alpha * acc[4 * h + 1][j];
-                    r.z = alpha * acc[4 * h + 2][j]; r.w = alpha * acc[4 * h + 3][j];
-                    if (useC) {
-                        const float4 o = *reinterpret_cast<const float4*>(cc + row);
-                        r.x = fmaf(beta, o.x, r.x); r.y = fmaf(beta, o.y, r.y);
-                        r.z = fmaf(beta, o.z, r.z); r.w = fmaf(beta, o.w, r.w);
-                    }
-                    *reinterpret_cast<float4*>(cc + row) = r;
-                } else {
+                for (int h = 0; h < 2; h++) {
+                    const size_t row = m0 + tx * 4 + 64 * h;
+                    if (row + 3 < M) {
+                        float4 r;
+                        r.x = al * acc[4 * h + 0][j]; r.y = al * acc[4 * h + 1][j];
+                        r.z = al * acc[4 * h + 2][j]; r.w = al * acc[4 * h + 3][j];
+                        if (useC) {
+                            const float4 o = *reinterpret_cast<const float4*>(cc + row);
+                            r.x = fmaf(be, o.x, r.x); r.y = fmaf(be, o.y, r.y);
+                            r.z = fmaf(be, o.z, r.z); r.w = fmaf(be, o.w, r.w);
+                        }
+                        *reinterpret_cast<float4*>(cc + row) = r;
+                    } else {
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        if (row + e < M && !(TRI && tri_masked(tri, row + e, col))) {
-                            float r = alpha * acc[4 * h + e][j];
-                            if (useC) r = fmaf(beta, cc[row + e], r);
-                            cc[row + e] = r;
+                        for (int e = 0; e < 4; e++) {
+                            if (row + e < M && !(TRI && tri_masked(trimode, row + e, col))) {
+                                float r = al * acc[4 * h + e][j];
+                                if (useC) r = fmaf(be, cc[row + e], r);
+                                cc[row + e] = r;
+                            }
                         }
                     }
                 }
-            }
-        } else {
+            } else {
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const size_t row = m0 + rowA(i);
-                if (row < M && !(TRI && tri_masked(tri, row, col))) {
-                    float r = alpha * acc[i][j];
-                    if (useC) r = fmaf(beta, cc[row], r);
-                    cc[row] = r;
+                for (int i = 0; i < 8; i++) {
+                    const size_t row = m0 + rowA(i);
+                    if (row < M && !(TRI && tri_masked(trimode, row, col))) {
+                        float r = al * acc[i][j];
+                        if (useC) r = fmaf(be, cc[row], r);
+                        cc[row] = r;
+                    }
+                }
+            }
+        }
+    };
+    if (splits <= 1) {
+        epilogue(C, ldc, alpha, beta, tri);
+        return;
+    }
+    // ---- split K: partial tile to this CTA's plane, then a ticket; the last CTA of the tile reduces
+    epilogue(planes + (size_t)blockIdx.y * split_stride, ldw, 1.f, 0.f, TRI_FULL);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&tickets[blockIdx.x], 1u);
+    __syncthreads();
+    if (s_ticket != splits - 1) return;
+    __threadfence();
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < NJ; j++) acc[i][j] = 0.f;
+    for (unsigned sp = 0; sp < splits; sp++) {
+        const float* P = planes + (size_t)sp * split_stride;
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const size_t col = n0 + colB(j);
+            if (col >= N) continue;
+            const float* pc = P + col * ldw;
+            if (!TA) {
+                // ldw is a multiple of 4 and covers the rows up to the next multiple of 4: whole float4s
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const size_t row = m0 + tx * 4 + 64 * h;
+                    if (row < M) {
+                        const float4 v = __ldcg(reinterpret_cast<const float4*>(pc + row));
+                        acc[4 * h + 0][j] += v.x; acc[4 * h + 1][j] += v.y; acc[4 * h + 2][j] += v.z; acc[4 * h + 3][j] += v.w;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const size_t row = m0 + rowA(i);
+                    if (row < M) acc[i][j] += __ldcg(pc + row);
                 }
             }
         }
     }
-}
-
-// C <- alpha * (plane 0 + plane 1 + ...) + beta * C, planes summed in index order (deterministic).
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ W, size_t ldw, size_t stride, unsigned splits,
-                                                            float* __restrict__ C, size_t ldc, size_t M, size_t N, float alpha, float beta)
-{
-    const size_t total = M * N;
-    for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < total; e += (size_t)gridDim.x * 256) {
-        const size_t i = e % M, j = e / M;
-        float acc = W[i + j * ldw];
-        for (unsigned sp = 1; sp < splits; sp++) acc += W[sp * stride + i + j * ldw];
-        float* c = C + i + j * ldc;
-        float r = alpha * acc;
-        if (beta != 0.f) r = fmaf(beta, *c, r);
-        *c = r;
-    }
+    epilogue(C, ldc, alpha, beta, tri);
 }
 
 template <bool TA, bool TB, int BN, int STAGES, int MIN_CTAS, bool TRI>
@@ -325,34 +358,32 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s, unsigned splits 
     char name[64];
     snprintf(name, sizeof(name), "sgemm_ffma_tma<%c,%c,%d,%d,%d>%s", TA ? 'T' : 'N', TB ? 'T' : 'N', BN, STAGES, MIN_CTAS, TRI ? "+tri" : "");
     float* W = nullptr;
-    const size_t ldw = (p.M + 3) / 4 * 4, stride = ldw * p.N;
-    if (splits > 1 && ws_alloc(reinterpret_cast<void**>(&W), splits * stride * sizeof(float), s) != cudaSuccess) {
+    const size_t ldw = (p.M + 3) / 4 * 4, stride = ldw * p.N, tiles = tilesM * tilesN;
+    if (splits > 1 && ws_alloc(reinterpret_cast<void**>(&W), splits * stride * sizeof(float) + tiles * sizeof(unsigned) + 256, s) != cudaSuccess) {
         cudaGetLastError();          // no workspace: the same kernel, unsplit, needs none
         splits = 1;
     }
     if (splits > 1) {
-        // partial products into `splits` planes of a workspace, then one deterministic reduction into C
+        // partial products into `splits` planes of a workspace; the last CTA of each tile sums them (in plane order) into C
         snprintf(name + strlen(name), sizeof(name) - strlen(name), "+splitk%u", splits);
         set_last_variant(name);
-        sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI><<<dim3((unsigned)(tilesM * tilesN), splits), THREADS, SMEM, s>>>(
-            mapA, mapB, W, ldw, p.M, p.N, p.K, 1.f, 0.f, (unsigned)tilesM, (unsigned)tilesN, 0u, TRI_FULL, splits, stride);
-        count_launch();
-        e = cudaGetLastError();
+        unsigned* tickets = reinterpret_cast<unsigned*>(W + splits * stride);
+        e = cudaMemsetAsync(tickets, 0, tiles * sizeof(unsigned), s);
         if (e == cudaSuccess) {
-            const unsigned blocks = (unsigned)std::min<size_t>((p.M * p.N + 255) / 256, (size_t)sm_count() * 8);
-            splitk_reduce_kernel<<<blocks, 256, 0, s>>>(W, ldw, stride, splits, p.C, p.ldc, p.M, p.N, p.alpha, p.beta);
+            e = launch_pdl(sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI>, dim3((unsigned)tiles, splits), dim3(THREADS), SMEM, s,
+                           mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, 0u, p.tri, splits, stride,
+                           W, ldw, tickets);
             count_launch();
-            e = cudaGetLastError();
         }
         const cudaError_t e2 = ws_free(W, s);
         return e != cudaSuccess ? e : e2;
     }
     set_last_variant(name);
-    sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI><<<(unsigned)(tilesM * tilesN), THREADS, SMEM, s>>>(
-        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * MIN_CTAS), p.tri,
-        1u, (size_t)0);
+    e = launch_pdl(sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI>, dim3((unsigned)(tilesM * tilesN)), dim3(THREADS), SMEM, s,
+                   mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
+                   (unsigned)(sm_count() * MIN_CTAS), p.tri, 1u, (size_t)0, (float*)nullptr, (size_t)0, (unsigned*)nullptr);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -375,14 +406,17 @@ template <bool TRI>
 __global__ void __launch_bounds__(T16_THREADS, 2)
 sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                     unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg)
+                     unsigned tilesM, unsigned tilesN, unsigned wave, int tri_arg, unsigned splits, size_t split_stride,
+                     float* __restrict__ planes, size_t ldw, unsigned* __restrict__ tickets)
 {
     int tri = TRI ? tri_arg : TRI_FULL;
+    __shared__ unsigned s_ticket;
     constexpr int BN = 128;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + T16_STAGES * T16_STAGE_BYTES);
     uint64_t* empty = full + T16_STAGES;
+    pdl_launch_dependents();
 
     unsigned tm, tn;
     {
@@ -399,7 +433,11 @@ sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         if (tri_tile_outside(tri, m0, BM, n0, BN)) return;
         if (tri_tile_inside(tri, m0, BM, n0, BN)) tri = TRI_FULL;
     }
-    const int nk = (int)((K + BK - 1) / BK);
+    // Split-K launches (gridDim.y = splits): K slabs [kt0, kt0 + nk) belong to this CTA, see the fix-up at the end.
+    const int nk_total = (int)((K + BK - 1) / BK);
+    const int nk_per = (nk_total + (int)splits - 1) / (int)splits;
+    const int kt0 = (int)blockIdx.y * nk_per;
+    const int nk = max(0, min(nk_per, nk_total - kt0));
     const bool reverse_k = wave != 0 && ((blockIdx.x / wave) & 1);
     const int lane = threadIdx.x % 32;
 
@@ -411,13 +449,14 @@ sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();               // everything below reads or writes global memory
 
     auto issue = [&](int kt) {
         const int s = kt % T16_STAGES;
         unsigned char* sa = smem + s * T16_STAGE_BYTES;
         unsigned char* sb = sa + A_BYTES;
         mbar_expect_tx(&full[s], T16_STAGE_BYTES);
-        const int k0 = (reverse_k ? nk - 1 - kt : kt) * BK;
+        const int k0 = (kt0 + (reverse_k ? nk - 1 - kt : kt)) * BK;
         tma_load_2d(sa, &mapA, (int)m0, k0, &full[s]);
         tma_load_2d(sb, &mapB, (int)n0, k0, &full[s]);
     };
@@ -480,45 +519,83 @@ sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         if (lane == 0) mbar_arrive(&empty[s]);
     }
 
-    // ---- epilogue: C = alpha*acc + beta*C; beta == 0 never reads C
-    const bool useC = (beta != 0.f);
-    const bool vec = (!TRI || tri == TRI_FULL) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
+    // ---- epilogue: D = al*acc + be*D; be == 0 never reads D
+    auto epilogue = [&](float* D, size_t ldd, float al, float be, int trimode) {
+        const bool useC = (be != 0.f);
+        const bool vec = (!TRI || trimode == TRI_FULL) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0) && (ldd % 4 == 0);
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const size_t col = n0 + ty * 4 + (j & 3) + 64 * (j >> 2);
-        if (col >= N) continue;
-        float* cc = C + col * ldc;
+        for (int j = 0; j < 8; j++) {
+            const size_t col = n0 + ty * 4 + (j & 3) + 64 * (j >> 2);
+            if (col >= N) continue;
+            float* cc = D + col * ldd;
 #pragma unroll
-        for (int g = 0; g < 4; g++) {
-            const size_t row = m0 + tx * 4 + 32 * g;
-            float v[4];
-            unpack2(acc2[2 * g][j], v[0], v[1]);
-            unpack2(acc2[2 * g + 1][j], v[2], v[3]);
-            if (vec && row + 3 < M) {
-                float4 r;
-                r.x = alpha * v[0]; r.y = alpha * v[1]; r.z = alpha * v[2]; r.w = alpha * v[3];
-                if (useC) {
-                    const float4 o = *reinterpret_cast<const float4*>(cc + row);
-                    r.x = fmaf(beta, o.x, r.x); r.y = fmaf(beta, o.y, r.y);
-                    r.z = fmaf(beta, o.z, r.z); r.w = fmaf(beta, o.w, r.w);
-                }
-                *reinterpret_cast<float4*>(cc + row) = r;
-            } else {
+            for (int g = 0; g < 4; g++) {
+                const size_t row = m0 + tx * 4 + 32 * g;
+                float v[4];
+                unpack2(acc2[2 * g][j], v[0], v[1]);
+                unpack2(acc2[2 * g + 1][j], v[2], v[3]);
+                if (vec && row + 3 < M) {
+                    float4 r;
+                    r.x = al * v[0]; r.y = al * v[1]; r.z = al * v[2]; r.w = al * v[3];
+                    if (useC) {
+                        const float4 o = *reinterpret_cast<const float4*>(cc + row);
+                        r.x = fmaf(be, o.x, r.x); r.y = fmaf(be, o.y, r.y);
+                        r.z = fmaf(be, o.z, r.z); r.w = fmaf(be, o.w, r.w);
+                    }
+                    *reinterpret_cast<float4*>(cc + row) = r;
+                } else {
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    if (row + e < M && !(TRI && tri_masked(tri, row + e, col))) {
-                        float r = alpha * v[e];
-                        if (useC) r = fmaf(beta, cc[row + e], r);
-                        cc[row + e] = r;
+                    for (int e = 0; e < 4; e++) {
+                        if (row + e < M && !(TRI && tri_masked(trimode, row + e, col))) {
+                            float r = al * v[e];
+                            if (useC) r = fmaf(be, cc[row + e], r);
+                            cc[row + e] = r;
+                        }
                     }
                 }
             }
         }
+    };
+    if (splits <= 1) {
+        epilogue(C, ldc, alpha, beta, tri);
+        return;
     }
+    // ---- split K: the partial tile goes to this CTA's plane of the workspace; the CTA of a tile that draws the last
+    // ticket adds the planes in plane order (a fixed order, whoever comes last) and writes C.  Nobody waits.
+    epilogue(planes + (size_t)blockIdx.y * split_stride, ldw, 1.f, 0.f, TRI_FULL);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&tickets[blockIdx.x], 1u);
+    __syncthreads();
+    if (s_ticket != splits - 1) return;
+    __threadfence();
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc2[i][j] = 0ull;
+    const unsigned long long ones = pack2(1.f, 1.f);
+    for (unsigned sp = 0; sp < splits; sp++) {
+        const float* P = planes + (size_t)sp * split_stride;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const size_t col = n0 + ty * 4 + (j & 3) + 64 * (j >> 2);
+            if (col >= N) continue;
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                const size_t row = m0 + tx * 4 + 32 * g;
+                if (row >= M) continue;
+                // ldw is a multiple of 4 that covers the rows up to the next multiple of 4: whole float4s
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(P + col * ldw + row));
+                acc2[2 * g][j] = ffma2(pack2(v.x, v.y), ones, acc2[2 * g][j]);            // x * 1 + acc: an exact addition
+                acc2[2 * g + 1][j] = ffma2(pack2(v.z, v.w), ones, acc2[2 * g + 1][j]);
+            }
+        }
+    }
+    epilogue(C, ldc, alpha, beta, tri);
 }
 
 template <bool TRI>
-cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s)
+cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s, unsigned splits = 1)
 {
     void* enc = get_tensor_map_encoder();
     CUtensorMap mapA, mapB;
@@ -527,16 +604,60 @@ cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s)
     if (!make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.N, p.K, p.ldb, 128, BK, CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorNotSupported;
     static DeviceOnce once;
-    const cudaError_t e = once.run([] {
+    cudaError_t e = once.run([] {
         return cudaFuncSetAttribute(sgemm_nt_16x8_kernel<TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, T16_SMEM);
     });
     if (e != cudaSuccess) return e;
+    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128, tiles = tilesM * tilesN;
+    float* W = nullptr;
+    const size_t ldw = (p.M + 3) / 4 * 4, stride = ldw * p.N;
+    if (splits > 1 && ws_alloc(reinterpret_cast<void**>(&W), splits * stride * sizeof(float) + tiles * sizeof(unsigned) + 256, s) != cudaSuccess) {
+        cudaGetLastError();          // no workspace: unsplit
+        splits = 1;
+    }
+    if (splits > 1) {
+        char name[48];
+        snprintf(name, sizeof(name), "sgemm_nt_16x8+splitk%u", splits);
+        set_last_variant(name);
+        unsigned* tickets = reinterpret_cast<unsigned*>(W + splits * stride);
+        e = cudaMemsetAsync(tickets, 0, tiles * sizeof(unsigned), s);
+        if (e == cudaSuccess) {
+            e = launch_pdl(sgemm_nt_16x8_kernel<TRI>, dim3((unsigned)tiles, splits), dim3(T16_THREADS), T16_SMEM, s,
+                           mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, 0u, p.tri,
+                           splits, stride, W, ldw, tickets);
+            count_launch();
+        }
+        const cudaError_t e2 = ws_free(W, s);
+        return e != cudaSuccess ? e : e2;
+    }
     set_last_variant(TRI ? "sgemm_nt_16x8+tri" : "sgemm_nt_16x8");
-    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128;
-    sgemm_nt_16x8_kernel<TRI><<<(unsigned)(tilesM * tilesN), T16_THREADS, T16_SMEM, s>>>(
-        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)(sm_count() * 2), p.tri);
+    e = launch_pdl(sgemm_nt_16x8_kernel<TRI>, dim3((unsigned)tiles), dim3(T16_THREADS), T16_SMEM, s,
+                   mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
+                   (unsigned)(sm_count() * 2), p.tri, 1u, (size_t)0, (float*)nullptr, (size_t)0, (unsigned*)nullptr);
     count_launch();
-    return cudaGetLastError();
+    return e;
+}
+
+// Number of K splits for the 8 x 8 kernel (two CTAs per SM) on `tiles` 128 x 128 tiles.  CTAs of equal length run in
+// rounds: a full round of 2 * sms CTAs takes twice a CTA's length, a last round of at most sms CTAs runs them alone on
+// their SMs (a lone CTA reaches about 0.8 of an SM's paired rate), one of more than sms CTAs costs a full round for a
+// fraction of the machine -- the wave quantisation a split can remove.  A split has to beat the unsplit launch by
+// 10 % to pay for its partial tiles and shorter K loops.  Measured N/T, unsplit -> split: 3584^3 52.6 -> 58.0 TFLOP/s
+// (three splits).
+unsigned choose_splits_8x8(size_t tiles, size_t K, size_t sms)
+{
+    auto rounds = [&](size_t ctas, double len) {
+        const size_t full = ctas / (2 * sms), rest = ctas % (2 * sms);
+        return 2.0 * len * full + (rest == 0 ? 0.0 : rest <= sms ? len / 0.8 : 2.0 * len);
+    };
+    unsigned best = 1;
+    double best_t = rounds(tiles, 1.0);
+    for (unsigned sp = 2; sp <= 4; sp++) {
+        if (K / sp < 256) break;
+        const double t = rounds(tiles * sp, 1.0 / sp) * 1.10;
+        if (t < best_t) { best_t = t; best = sp; }
+    }
+    return best;
 }
 
 template <int BN, int STAGES, int MIN_CTAS>
@@ -573,18 +694,37 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     const int forced = forced_gemm_path();
     if (forced == PATH_TMA_ONE_CTA) return launch_any<128, 5, 1>(p, s);
     if (forced == PATH_TMA_TWO_CTAS) return launch_any<128, 3, 2>(p, s);
+    const bool may_split = gemm_may_allocate() && p.C != p.A && p.C != p.B && getenv("CLBLAS_B200_NO_SPLITK") == nullptr;
+    // Tuning aid: CLBLAS_B200_SGEMM_FORCE="<tile>,<splits>" with tile 64 / 128 (8 x 8 register-tile kernel) or 16 (16 x 8).
+    if (const char* f = getenv("CLBLAS_B200_SGEMM_FORCE")) {
+        int tile = 0, sp = 1;
+        if (sscanf(f, "%d,%d", &tile, &sp) >= 1 && may_split && p.tri == TRI_FULL && min_bn < 128 && sp >= 1 && sp <= 8) {
+            if (tile == 16 && !p.ta && p.tb) return launch_nt_16x8<false>(p, s, (unsigned)sp);
+            if (tile == 64) return p.ta ? launch_any<64, 5, 1>(p, s, (unsigned)sp) : launch_any<64, 3, 2>(p, s, (unsigned)sp);
+            if (tile == 128) return p.ta ? launch_any<128, 5, 1>(p, s, (unsigned)sp) : launch_any<128, 3, 2>(p, s, (unsigned)sp);
+        }
+    }
+    // The 16 x 8 register-tile kernel has four warps per CTA: it needs both of an SM's CTA slots filled for several
+    // waves and a K loop long enough to amortise its per-thread epilogue.  Measured against the 8 x 8 kernel: 8192^3
+    // 63.5 vs 57.8-60.2, 3008 x 4100 x 1537 48.6 vs 47.2, 4096^3 58.9 vs 59.1, but 1536^3 (144 tiles) 35.6 vs 50.4,
+    // 2048^3 44.5 vs 48.9 and 4096 x 4096 x 512 48.7 vs 53.9 TFLOP/s.  Between two and six waves the 8 x 8 kernel
+    // takes over where splitting K evens out its last round (choose_splits_8x8).
+    if (!p.ta && p.tb && min_bn < 128 && tiles128 >= (size_t)sm_count() * 4 && p.K >= 1024 && getenv("CLBLAS_B200_SGEMM_8X8") == nullptr) {
+        if (p.tri != TRI_FULL) return launch_nt_16x8<true>(p, s);
+        const unsigned sp = (may_split && tiles128 < (size_t)sm_count() * 12) ? choose_splits_8x8(tiles128, p.K, (size_t)sm_count()) : 1;
+        if (sp > 1) return launch_any<128, 3, 2>(p, s, sp);
+        return launch_nt_16x8<false>(p, s);
+    }
     // Fewer 128-wide tiles than SMs: halve the tile width so that twice as many CTAs share the work
     // (three of them fit an SM).  With A K-contiguous the 4-k fragments need the one-CTA register budget.
     if (min_bn < 128 && tiles128 < 120) {
-        // Tiles for less than a third of the SMs' CTA slots and a long K loop: split K over 2-4 CTAs per tile (partial
-        // tiles in a workspace, summed in a fixed order by a second kernel).  Measured N/N: 768 x 768 x 2048 18.6 -> 34.2,
-        // 512^3 7.2 -> 10.5 TFLOP/s; with more tiles than that the second kernel costs more than the split gains
-        // (1024^3, 128 tiles: 31.3 -> 29.9), so those stay unsplit.
+        // Tiles for less than a third of the SMs' CTA slots and a long K loop: split K over 2-4 CTAs per tile, partial tiles
+        // summed in plane order by the CTA that finishes last (768 x 768 x 2048 N/N: 18.6 -> 34.2 TFLOP/s; with more
+        // tiles than that the split loses: 1024^3, 128 tiles, N/T 33.4 unsplit against 29.8 TFLOP/s in two).
         const size_t tiles64 = tilesM * ((p.N + 63) / 64);
         const size_t slots = (size_t)sm_count() * (p.ta ? 1 : 2);
         unsigned splits = 1;
-        if (p.tri == TRI_FULL && tiles64 * 3 <= slots && gemm_may_allocate() && p.C != p.A && p.C != p.B &&
-            getenv("CLBLAS_B200_NO_SPLITK") == nullptr)
+        if (p.tri == TRI_FULL && tiles64 * 3 <= slots && may_split)
             splits = (unsigned)std::max<size_t>(1, std::min<size_t>(std::min<size_t>(4, slots / tiles64), p.K / 256));
         if (p.ta) return launch_any<64, 5, 1>(p, s, splits);
         return launch_any<64, 3, 2>(p, s, splits);
@@ -592,12 +732,6 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     // A K-contiguous operand is fetched 4 k at a time (32 fragment registers on top of the
     // accumulators), which the two-CTA budget of 128 registers holds only for B; measured at 8192^3
     // with packed FMAs: N/T 60.2 (two CTAs) vs 53.6 TFLOP/s (one), N/N 48.6 vs 47.2.
-    // The 16 x 8 register-tile kernel has four warps per CTA: it needs both of an SM's CTA slots filled for
-    // several waves and a K loop long enough to amortise its per-thread epilogue.  Measured against the 8 x 8
-    // kernel: 8192^3 63.5 vs 57.8-60.2, 3008 x 4100 x 1537 48.6 vs 47.2, but 1536^3 (144 tiles) 38.3 vs 50.9 and
-    // 4096 x 4096 x 512 48.7 vs 53.9 TFLOP/s.
-    if (!p.ta && p.tb && tiles128 >= (size_t)sm_count() * 4 && p.K >= 1024 && getenv("CLBLAS_B200_SGEMM_8X8") == nullptr)
-        return p.tri != TRI_FULL ? launch_nt_16x8<true>(p, s) : launch_nt_16x8<false>(p, s);
     if (!p.ta) return launch_any<128, 3, 2>(p, s);
     return launch_any<128, 5, 1>(p, s);
 }

@@ -119,8 +119,10 @@ cudaError_t panel_events(ShardComm* c, size_t n)
 }
 
 // Column panels [b[i], b[i+1]) of a matrix with `cols` columns: a first panel of about 1/32 of the
-// columns (at least min_cols), each next one twice as wide, boundaries multiples of 128, at most
-// `max_panels` panels.  Every rank computes the same plan from the same arguments.
+// columns (at least min_cols), each next one four times as wide, boundaries multiples of 128, at most
+// `max_panels` panels.  Every rank computes the same plan from the same arguments.  (The work on a panel
+// lasts far longer than its transfer, so the panel after a small first one can already be large: few
+// panels mean few short products.)
 std::vector<size_t> growing_panels(size_t cols, size_t min_cols, size_t max_panels)
 {
     std::vector<size_t> b{0};
@@ -131,7 +133,7 @@ std::vector<size_t> growing_panels(size_t cols, size_t min_cols, size_t max_pane
         size_t next = b.back() + w;
         if (next >= cols || b.size() == max_panels || cols - next < w / 2) next = cols;
         b.push_back(next);
-        w *= 2;
+        w *= 4;
     }
     return b;
 }

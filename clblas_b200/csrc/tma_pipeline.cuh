@@ -5,6 +5,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <cstdlib>
+#include <utility>
 
 namespace cb200 {
 
@@ -17,6 +19,45 @@ inline unsigned read_wait_timeout_flag()
     unsigned v = 0;
     if (cudaMemcpyFromSymbol(&v, g_wait_timeout_flag, sizeof(v)) != cudaSuccess) { cudaGetLastError(); return 0x80000000u; }
     return v;
+}
+
+// Programmatic dependent launch.  A kernel launched through launch_pdl may start while the kernel before it on
+// the stream is still running: its CTAs take SMs the earlier grid no longer needs and run their set-up (barrier
+// initialisation, descriptor prefetch) there.  pdl_wait() returns once the earlier grid has completed and its
+// writes are visible; every global-memory access of such a kernel comes after it.  pdl_launch_dependents() tells
+// the scheduler that the next kernel may be started as far as this CTA is concerned.  Chains of short dependent
+// launches (the leaves and small updates of a triangular solve) save the launch gap and the set-up time this way.
+// Both instructions do nothing in a kernel that was launched the ordinary way.
+//
+// Off unless CLBLAS_B200_PDL=1.  Measured on B200: no gain on the solve's chains (DTRSM 8192 x 2048 27.2 with, 27.4
+// TFLOP/s without; 4096 x 1024 15.7 against 16.4) and a large loss for back-to-back products whose grid is smaller than
+// one wave (SGEMM N/T 1024^3: 111 us against 68 us): the CTAs of the next kernels are placed while the current one
+// runs, on whatever SMs have room at that moment, so when their turn comes some SMs hold three of a kernel's CTAs and
+// others none.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled()
+{
+    static const bool on = [] { const char* v = std::getenv("CLBLAS_B200_PDL"); return v != nullptr && v[0] == '1'; }();
+    return on;
+}
+
+// Only for kernels that call pdl_wait() before their first global-memory access.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)

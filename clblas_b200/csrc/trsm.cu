@@ -12,6 +12,7 @@
 //    src/library/blas/functor/functor_xtrsm.cc:130-152) and double.
 // Only the referenced triangle of A is ever loaded; a unit diagonal is never loaded.
 #include "common.h"
+#include "tma_pipeline.cuh"
 
 #include <algorithm>
 #include <mutex>
@@ -39,6 +40,8 @@ trtri_diag_kernel(const T* __restrict__ A, size_t lda, size_t n, bool lower, boo
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* Ls = reinterpret_cast<T*>(smem_raw);                 // Ls[k*NB + i] = L[i][k]
     T* rowbuf = Ls + NB * NB;                               // 2 x NB
+    pdl_launch_dependents();
+    pdl_wait();                                             // A may be the result of the kernel before this one
 
     const size_t b = (size_t)b_first + blockIdx.x;
     const size_t r0 = b * NB;
@@ -144,10 +147,10 @@ template <typename T>
 cudaError_t invert_blocks(const TrsmCtx<T>& c, size_t b0, size_t b1)
 {
     if (b1 <= b0) return cudaSuccess;
-    trtri_diag_kernel<T><<<(unsigned)(b1 - b0), TRTRI_THREADS, trtri_smem(sizeof(T)), c.s>>>(c.A, c.lda, c.n, c.lower, c.unit, c.inv,
-                                                                                              (unsigned)b0);
+    const cudaError_t e = launch_pdl(trtri_diag_kernel<T>, dim3((unsigned)(b1 - b0)), dim3(TRTRI_THREADS), trtri_smem(sizeof(T)), c.s,
+                                     c.A, c.lda, c.n, c.lower, c.unit, c.inv, (unsigned)b0);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // Before an operation that reads columns [c0, c1) of the stored A: with a gate, orders the stream after

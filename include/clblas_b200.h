@@ -433,7 +433,7 @@ clblasStatus clblasB200DtrsmSharded(
     unsigned numEventsInWaitList, const clblasEvent* eventWaitList, clblasEvent* events);
 
 /*      The panel plan the sharded calls use for a matrix of `columns` stored columns: a first panel of about
- *      1/32 of the columns (at least min_columns), each next one twice as wide, boundaries multiples of 128,
+ *      1/32 of the columns (at least min_columns), each next one four times as wide, boundaries multiples of 128,
  *      at most max_panels panels.  Writes count+1 boundaries (bounds needs max_panels+1 entries).  Pure host
  *      arithmetic, exported for the tests. */
 clblasStatus clblasB200PanelPlan(size_t columns, size_t min_columns, unsigned max_panels, size_t* bounds, unsigned* count);
