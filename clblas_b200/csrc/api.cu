@@ -1143,7 +1143,7 @@ unsigned long long clblasB200LaunchCount(void) { return g_launches.load(); }
 unsigned clblasB200DeviceFault(void)
 {
     if (cudaDeviceSynchronize() != cudaSuccess) { cudaGetLastError(); return 0x80000000u; }
-    return dgemm_tma_fault_flag() | sgemm_tma_fault_flag() | sgemm_3xtf32_fault_flag();
+    return dgemm_tma_fault_flag() | sgemm_tma_fault_flag() | sgemm_3xtf32_fault_flag() | dtrsm_fused_fault_flag();
 }
 const char* clblasB200LastGemmKernel(void) { return t_last_kernel; }
 const char* clblasB200LastGemmVariant(void) { return t_last_variant; }

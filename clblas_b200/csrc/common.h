@@ -239,6 +239,15 @@ cudaError_t dtrsm_colmajor_noalloc(bool right, bool lower, bool trans, bool unit
 cudaError_t dgemm_prepare_all_kernels();
 cudaError_t gemm_simt_load_double_kernels();
 
+// Fused solve of up to dtrsm_diag_fused_max_blocks() consecutive diagonal blocks of a Left-side DTRSM with few
+// right-hand sides (dtrsm_diag_fused.cu).
+int dtrsm_diag_fused_max_blocks();
+bool dtrsm_diag_fused_applicable(const double* A, size_t lda, const double* B, size_t ldb, size_t n, size_t N);
+cudaError_t launch_dtrsm_diag_fused(bool trans, bool forward, const double* A, size_t lda, size_t n, const double* inv, size_t nblk,
+                                    double* B, size_t ldb, size_t N, double alpha, size_t b0, size_t b1, cudaStream_t s);
+cudaError_t dtrsm_diag_fused_prepare_all();
+unsigned dtrsm_fused_fault_flag();
+
 // Sticky per-translation-unit flags set when a bounded mbarrier wait inside a kernel ran out.
 unsigned dgemm_tma_fault_flag();
 unsigned sgemm_tma_fault_flag();

@@ -15,6 +15,7 @@
 #include "tma_pipeline.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 namespace cb200 {
@@ -128,7 +129,16 @@ struct TrsmCtx {
     T* tmp;                      // staging panel for one leaf
     cudaStream_t s;
     TrsmPanelGate* gate = nullptr;   // set when columns of A are still arriving (see common.h)
+    bool fused = false;              // ranges of up to four diagonal blocks go to the fused kernel (FP64, Left, few columns)
 };
+
+// The end of the recursion for double precision, Left side, few right-hand sides: one launch solves the whole range.
+inline cudaError_t solve_fused(const TrsmCtx<double>& c, size_t b0, size_t b1, double alpha)
+{
+    const size_t nblk = (c.n + NB - 1) / NB;
+    return launch_dtrsm_diag_fused(c.trans, c.eff_lower, c.A, c.lda, c.n, c.inv, nblk, c.B, c.ldb, c.N, alpha, b0, b1, c.s);
+}
+inline cudaError_t solve_fused(const TrsmCtx<float>&, size_t, size_t, float) { return cudaErrorNotSupported; }
 
 constexpr size_t trtri_smem(size_t elem) { return (size_t)(NB * NB + 2 * NB) * elem; }
 
@@ -233,6 +243,12 @@ cudaError_t solve_leaf(const TrsmCtx<T>& c, size_t b, T alpha)
 template <typename T>
 cudaError_t solve_range(const TrsmCtx<T>& c, size_t b0, size_t b1, T alpha)
 {
+    if (c.fused && b1 - b0 <= (size_t)dtrsm_diag_fused_max_blocks()) {
+        cudaError_t ef = need_columns(c, b0 * NB, std::min<size_t>(b1 * NB, c.n));
+        if (ef != cudaSuccess) return ef;
+        ef = solve_fused(c, b0, b1, alpha);
+        if (ef != cudaErrorNotSupported) return ef;
+    }
     if (b1 - b0 == 1) return solve_leaf(c, b0, alpha);
     const size_t mid = b0 + (b1 - b0 + 1) / 2;
     const size_t r0 = b0 * NB, r1 = mid * NB, r2 = std::min<size_t>(b1 * NB, c.n);
@@ -274,6 +290,12 @@ cudaError_t solve_range(const TrsmCtx<T>& c, size_t b0, size_t b1, T alpha)
     return solve_range(c, b0, mid, T(1));
 }
 
+inline bool fused_applicable(const TrsmCtx<double>& c)
+{
+    return !c.right && getenv("CLBLAS_B200_NO_TRSM_FUSE") == nullptr && dtrsm_diag_fused_applicable(c.A, c.lda, c.B, c.ldb, c.n, c.N);
+}
+inline bool fused_applicable(const TrsmCtx<float>&) { return false; }
+
 }  // namespace
 
 template <typename T>
@@ -289,6 +311,7 @@ cudaError_t trsm_colmajor(bool right, bool lower, bool trans, bool unit, size_t 
     const size_t nblk = (c.n + NB - 1) / NB;
     const size_t inv_elems = nblk * (size_t)(NB * NB);
     const size_t tmp_elems = (size_t)NB * (right ? M : N);
+    c.fused = fused_applicable(c);
 
     cudaError_t e = trtri_prepare<T>();
     if (e != cudaSuccess) return e;
@@ -350,6 +373,7 @@ static cudaError_t noalloc_scratch_address(double** out)
         cudaFuncAttributes fa;
         if ((e = cudaFuncGetAttributes(&fa, trtri_diag_kernel<double>)) != cudaSuccess) return e;
         if ((e = dgemm_prepare_all_kernels()) != cudaSuccess) return e;
+        if ((e = dtrsm_diag_fused_prepare_all()) != cudaSuccess) return e;
         addr[dev] = p;
     }
     *out = addr[dev];
@@ -374,6 +398,7 @@ cudaError_t dtrsm_colmajor_noalloc(bool right, bool lower, bool trans, bool unit
     c.M = M; c.N = N; c.n = n; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.s = s;
     c.inv = ws;
     c.tmp = ws + NOALLOC_INV_ELEMS;
+    c.fused = fused_applicable(c);
     const size_t nblk = (n + NB - 1) / NB;
     if ((e = invert_blocks(c, 0, nblk)) != cudaSuccess) return e;
     return solve_range<double>(c, 0, nblk, alpha);
@@ -514,6 +539,7 @@ cudaError_t ctrsm_left(bool lower, int op, bool unit, size_t M, size_t N, const 
     c.tmp = ws + inv_elems;
     R* E = ws + inv_elems + tmp_elems;
     c.A = E; c.lda = lde;
+    c.fused = fused_applicable(c);       // the fused kernel reads only blocks off the block diagonal, which is all E holds
 
     const size_t smem = (size_t)(2 * CNB * CNB + CNB) * 2 * sizeof(R);
     static DeviceOnce once[2];

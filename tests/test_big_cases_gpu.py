@@ -106,10 +106,26 @@ def test_gemm_reference_big_shapes(lib, order):
 
 
 def test_sgemm_16x8_register_tile_kernel_is_exact(lib):
-    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3200, 3200, 1024, seed=8010)
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 5504, 5504, 1024, seed=8010)          # 1849 tiles: more than 12 per SM
     assert v == "sgemm_nt_16x8", v
-    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3200 - 37, 3200 + 5, 1024 + 19, alpha=-1.0, beta=0.0, seed=8011)
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 5504 - 37, 5504 + 5, 1024 + 19, alpha=-1.0, beta=0.0, seed=8011)
     assert v == "sgemm_nt_16x8", v               # ragged edges in M, N and K
+
+
+def test_sgemm_split_k_against_wave_quantisation_is_exact(lib):
+    """784 tiles of 128 x 128 are 2.65 rounds of CTAs: the dispatcher cuts K in three so that the rounds come out even.
+    Same bits as the unsplit product (integer inputs), the same call twice gives the same bits (fixed reduction order)."""
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3584, 3584, 1024 + 512, seed=8012)
+    assert v == "sgemm_ffma_tma<N,T,128,3,2>+splitk3", v
+    import oracle as _o
+    g = _o.rng(8013, 0)
+    n, k = 3584, 1536
+    A, B = (torch.from_numpy(g.standard_normal(n * k).astype(np.float32)).cuda() for _ in range(2))
+    C1, C2 = torch.zeros(n * n, device="cuda"), torch.zeros(n * n, device="cuda")
+    for C in (C1, C2):
+        assert lib.clblasSgemm(ColumnMajor, NoTrans, Trans, n, n, k, 1.0, A, 0, n, B, 0, n, 0.0, C, 0, n) == lib.clblasSuccess
+    torch.cuda.synchronize()
+    assert lib.last_gemm_variant().endswith("+splitk3") and torch.equal(C1, C2)
 
 
 def test_dgemm_streamk_tail_and_sgemm_splitk_are_exact(lib):
