@@ -45,12 +45,14 @@ def build(force: bool = False) -> None:
     src = os.path.join(_HERE, "oracle_blas.c")
     ref = os.path.join(_HERE, "_ref", "libnaive_ref.so")
     stale = (not os.path.exists(port)) or os.path.getmtime(port) < os.path.getmtime(src)
-    ref_possible = os.path.exists("/root/reference/src/library/tools/ktest/naive/naive_blas.cpp")
+    # the reference tree: REF_ROOT, or a checkout named "reference" beside this repository
+    ref_root = os.environ.get("REF_ROOT") or os.path.normpath(os.path.join(_HERE, "..", "..", "reference"))
+    ref_possible = os.path.exists(os.path.join(ref_root, "src", "library", "tools", "ktest", "naive", "naive_blas.cpp"))
     shim = os.path.join(_HERE, "ref_shim.cpp")
     if ref_possible and os.path.exists(ref) and os.path.getmtime(ref) < os.path.getmtime(shim):
         force = True
     if force or stale or (ref_possible and not os.path.exists(ref)):
-        subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True,
+        subprocess.run(["make", "-C", _HERE, "-B" if force else "-s", f"REF_ROOT={ref_root}"], check=True,
                        stdout=subprocess.DEVNULL)
 
 

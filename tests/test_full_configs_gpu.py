@@ -1,4 +1,4 @@
-"""BASELINE.json's configurations at their full sizes on one GPU.
+"""The benchmark's workloads at their full sizes on one GPU (DGEMM T/N 8192^3, DTRSM 8192 x 16384, SGEMM N/T 32768^3).
 
 A full float64 host product is out of reach at these sizes, so each run is checked through
 (a) sampled rows x columns of the result against a float64 host evaluation of the SAME device data,

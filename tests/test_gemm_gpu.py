@@ -235,8 +235,8 @@ def test_dgemm_stream_k_tail_exact(lib):
 
 
 def test_config2_shape_family_dgemm_tn(lib):
-    """DGEMM column-major T/N, normal(0,1), alpha = beta = 1, tight leading dimensions (BASELINE
-    config 2) at 1024^3, where the float64 host check is cheap; the 8192^3 run is checked through
+    """DGEMM column-major T/N, normal(0,1), alpha = beta = 1, tight leading dimensions (the benchmark's
+    DGEMM workload) at 1024^3, where the float64 host check is cheap; the 8192^3 run is checked through
     sampled rows/columns in test_full_configs_gpu.py."""
     c = cases.gemm_case("d", ColumnMajor, Trans, NoTrans, 1024, 1024, 1024, alpha=1.0, beta=1.0, mode="normal")
     r = check_real(lib, c)

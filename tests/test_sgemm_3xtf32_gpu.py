@@ -3,7 +3,7 @@
 It is not an FFMA evaluation, so it is qualified the way the stated tolerance demands and NOT with
 the exact-integer inputs (small integers fit a TF32 mantissa and would hide the split): real-valued
 inputs, max |C - C_exact| / (|alpha||A||B| + |beta||C|) <= 4*K*u with u = 2^-24, on every transpose
-case, ragged shapes, unaligned operands, and BASELINE's SGEMM configurations at reduced K."""
+case, ragged shapes, unaligned operands, and the benchmark's SGEMM shapes at reduced K."""
 import numpy as np
 import pytest
 

@@ -84,7 +84,7 @@ def test_alpha_zero(lib, prec):
 
 
 def test_medium_dtrsm_left_lower(lib):
-    """The shape family of BASELINE config 4 at a size the CPU check finishes quickly: 1024 x 1024
+    """The benchmark's DTRSM (Left/Lower/NoTrans/NonUnit) at a size the CPU check finishes quickly: 1024 x 1024
     lower triangle (diag U[1,2], strict lower U[-1,1]/n, garbage above), 512 right-hand sides."""
     n, nrhs = 1024, 512
     g = oracle.rng(12345, 21)
