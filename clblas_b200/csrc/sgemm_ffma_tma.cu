@@ -642,8 +642,8 @@ cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s, unsigned
 // rounds: a full round of 2 * sms CTAs takes twice a CTA's length, a last round of at most sms CTAs runs them alone on
 // their SMs (a lone CTA reaches about 0.8 of an SM's paired rate), one of more than sms CTAs costs a full round for a
 // fraction of the machine -- the wave quantisation a split can remove.  A split has to beat the unsplit launch by
-// 10 % to pay for its partial tiles and shorter K loops.  Measured N/T, unsplit -> split: 3584^3 52.6 -> 58.0 TFLOP/s
-// (three splits).
+// 6 % to pay for its partial tiles and shorter K loops.  Measured N/T, unsplit -> split: 3584^3 52.6 -> 58.0 TFLOP/s
+// (three splits), 3008 x 4100 x 1537 46.7 -> 49.0 (two).
 unsigned choose_splits_8x8(size_t tiles, size_t K, size_t sms)
 {
     auto rounds = [&](size_t ctas, double len) {
@@ -654,7 +654,7 @@ unsigned choose_splits_8x8(size_t tiles, size_t K, size_t sms)
     double best_t = rounds(tiles, 1.0);
     for (unsigned sp = 2; sp <= 4; sp++) {
         if (K / sp < 256) break;
-        const double t = rounds(tiles * sp, 1.0 / sp) * 1.10;
+        const double t = rounds(tiles * sp, 1.0 / sp) * 1.06;
         if (t < best_t) { best_t = t; best = sp; }
     }
     return best;

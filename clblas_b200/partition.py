@@ -34,11 +34,11 @@ def plan_columns(total: int, parts: int, align: int = 128) -> List[int]:
     return cb.plan_shards(total, parts, align)
 
 
-def gemm_panels(transA: int, M: int, n_local: int, K: int, sm_count: int = 148) -> List[Tuple[int, int]]:
+def gemm_panels(prec: str, transA: int, M: int, n_local: int, K: int, sm_count: int = 148) -> List[Tuple[int, int]]:
     """Column ranges [c0, c1) of the stored A in the order they are broadcast: the plan of gemm_sharded_colmajor."""
     ta = transA != cb.clblasNoTrans
     cols = M if ta else K
-    min_cols = 128
+    min_cols = 1024 if prec == "s" else 512
     if ta:
         min_cols = max(128, sm_count * 2 * 128 * 128 // max(n_local, 128))
     b = cb.panel_plan(cols, min_cols, 12)
@@ -46,19 +46,13 @@ def gemm_panels(transA: int, M: int, n_local: int, K: int, sm_count: int = 148) 
 
 
 def trsm_panels(uplo: int, transA: int, n: int, right: bool = False) -> List[Tuple[int, int]]:
-    """Column ranges of the stored triangular matrix in broadcast order: small panels where the substitution
-    starts (the plan of trsm_sharded_colmajor)."""
-    b = cb.panel_plan(n, 128, 10)
+    """Column ranges of the stored triangular matrix in broadcast order: equal panels, first the one where the
+    substitution starts (the plan of trsm_sharded_colmajor)."""
+    b = cb.panel_plan(n, 0, 32)
     lower, trans = uplo == cb.clblasLower, transA != cb.clblasNoTrans
     ascending = ((lower != trans) != right)
-    if ascending:
-        return [(b[i], b[i + 1]) for i in range(len(b) - 1)]
-    m = []
-    for i in range(len(b)):
-        v = n - b[len(b) - 1 - i]
-        m.append(0 if i == 0 else n if i == len(b) - 1 else (v + 127) // 128 * 128)
-    m = sorted(set(m))
-    return [(m[i], m[i + 1]) for i in range(len(m) - 1)][::-1]
+    plan = [(b[i], b[i + 1]) for i in range(len(b) - 1)]
+    return plan if ascending else plan[::-1]
 
 
 def get_comm(group: Optional[dist.ProcessGroup] = None) -> int:
@@ -102,7 +96,7 @@ def gemm_column_sharded(prec: str, transA: int, transB: int, M: int, n_local: in
         # C <- beta*C; A is not referenced and nothing travels
         return gemm_fn(cb.clblasColumnMajor, transA, transB, M, n_local, K, alpha, A, 0, lda, B_local, 0, ldb, beta, C_local, 0, ldc) \
             if n_local else cb.clblasSuccess
-    plan = gemm_panels(transA, M, n_local, K)
+    plan = gemm_panels(prec, transA, M, n_local, K)
     works = []
     if _world(group) > 1:
         for (c0, c1) in plan:

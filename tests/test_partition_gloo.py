@@ -41,8 +41,8 @@ def _worker(rank, world, port, q):
         from clblas_b200 import partition
         results = {}
         g = np.random.Generator(np.random.Philox(key=[777, 0]))
-        for (M, N, K, ta, tb) in ((96, 300, 520, NoTrans, Trans), (400, 300, 260, Trans, NoTrans), (96, 300, 260, NoTrans, NoTrans),
-                                  (300, 300, 70, Trans, Trans), (64, 100, 300, NoTrans, Trans), (64, 300, 0, NoTrans, NoTrans)):
+        for (M, N, K, ta, tb) in ((96, 300, 2100, NoTrans, Trans), (400, 300, 260, Trans, NoTrans), (96, 300, 1300, NoTrans, NoTrans),
+                                  (300, 300, 70, Trans, Trans), (64, 100, 700, NoTrans, Trans), (64, 300, 0, NoTrans, NoTrans)):
             bounds = partition.plan_columns(N, world, 128)       # N = 100: rank 1 owns no column
             j0, j1 = bounds[rank], bounds[rank + 1]
             opA = g.integers(-8, 8, (M, K)).astype(np.float64)
@@ -61,7 +61,7 @@ def _worker(rank, world, port, q):
             want = 2.0 * opA @ opB[:, j0:j1] + 3.0 * C0[:, j0:j1]
             results[f"gemm{ta}{tb}_{M}x{N}x{K}"] = (st, bool(np.array_equal(got, want)), bool(np.array_equal(A.numpy(), A_full)))
 
-        n, nrhs = 64, 200
+        n, nrhs = 64, 140
         bounds = partition.plan_columns(nrhs, world, 128)
         j0, j1 = bounds[rank], bounds[rank + 1]
         T = np.tril(g.uniform(-1, 1, (n, n)) / n, -1) + np.diag(g.uniform(1, 2, n))
@@ -74,7 +74,7 @@ def _worker(rank, world, port, q):
         # several broadcast panels, both substitution directions (panels sent from the first or from the last column)
         from oracle import Upper
         for name, uplo in (("trsm_panels_lower", Lower), ("trsm_panels_upper", Upper)):
-            n2 = 300
+            n2 = 1300                  # three panels of 512 columns
             T2 = np.tril(g.uniform(-1, 1, (n2, n2)) / n2) + np.diag(g.uniform(1, 2, n2))
             T2 = T2 if uplo == Lower else T2.T.copy()
             B2 = g.standard_normal((n2, nrhs))
