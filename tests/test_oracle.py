@@ -150,3 +150,32 @@ def test_poison_outside_triangle_never_read(built_oracle):
         X = oracle.view(Bb, c["order"], NoTrans, c["M"], c["N"], c["ldb"], c["offB"])
         assert np.all(np.isfinite(X)), c
         assert oracle.trsm_backward_ratio(X, c["alpha"], cases.trsm_op_triangle(c, A), B, c["side"], np.float64) <= 1.0, c
+
+
+def test_trsm_delta_bound_accepts_a_netlib_solution(built_oracle):
+    """The restated acceptance rule of the reference's TRSM tests (trsmDelta, src/tests/correctness/trsm-delta.h:44-240):
+    the oracle's solution and a Netlib-interface solution (what the reference's tests compare the library against)
+    must lie within delta of each other on reference-style inputs, for both sides, both triangles, both precisions --
+    and delta must mean something: for a typical entry it is a small fraction of the solution (it is a loose bound:
+    a few per cent in float at order 150, because it adds the absolute errors of a whole column)."""
+    from scipy.linalg import blas
+    import oracle
+    from oracle import ColumnMajor, Left, Right, Lower, Upper, NoTrans, Trans, NonUnit, Unit
+    for dt, fn in ((np.float32, blas.strsm), (np.float64, blas.dtrsm)):
+        for side, uplo, trans, diag in ((Left, Lower, NoTrans, NonUnit), (Left, Upper, Trans, Unit), (Right, Upper, NoTrans, NonUnit),
+                                        (Right, Lower, Trans, NonUnit)):
+            M, N = (150, 40) if side == Left else (40, 150)
+            n = M if side == Left else N
+            A, B = oracle.trsm_inputs(n, (M, N), uplo, diag, dt, seed=77, poison=False)
+            T = oracle.clean_triangle(A, uplo, diag)
+            ld = n
+            Ab = oracle.pack(A, ColumnMajor, NoTrans, ld, 0)
+            Bb = oracle.pack(B, ColumnMajor, NoTrans, M, 0)
+            oracle.trsm(ColumnMajor, side, uplo, trans, diag, M, N, 1.5, Ab, 0, ld, Bb, 0, M)
+            X = oracle.view(Bb, ColumnMajor, NoTrans, M, N, M, 0)
+            Xn = fn(dt(1.5), np.asfortranarray(T), np.asfortranarray(B), side=1 if side == Right else 0, lower=1 if uplo == Lower else 0,
+                    trans_a=1 if trans == Trans else 0, diag=1 if diag == Unit else 0)
+            delta = oracle.trsm_delta(side, uplo, trans, diag, T, B, 1.5, dt)
+            assert delta.shape == (M, N) and np.all(delta > 0)
+            assert np.all(np.abs(X.astype(np.float64) - Xn.astype(np.float64)) <= delta)
+            assert np.median(delta / (np.abs(Xn) + 1e-30)) < (0.1 if dt == np.float32 else 1e-9)
