@@ -638,26 +638,360 @@ cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s, unsigned
     return e;
 }
 
-// Number of K splits for the 8 x 8 kernel (two CTAs per SM) on `tiles` 128 x 128 tiles.  CTAs of equal length run in
-// rounds: a full round of 2 * sms CTAs takes twice a CTA's length, a last round of at most sms CTAs runs them alone on
-// their SMs (a lone CTA reaches about 0.8 of an SM's paired rate), one of more than sms CTAs costs a full round for a
-// fraction of the machine -- the wave quantisation a split can remove.  A split has to beat the unsplit launch by
-// 6 % to pay for its partial tiles and shorter K loops.  Measured N/T, unsplit -> split: 3584^3 52.6 -> 58.0 TFLOP/s
-// (three splits), 3008 x 4100 x 1537 46.7 -> 49.0 (two).
-unsigned choose_splits_8x8(size_t tiles, size_t K, size_t sms)
+// How the 8 x 8 kernel covers `tiles` 128 x 128 tiles on `sms` SMs that hold `per_sm` CTAs each.  CTAs of equal length
+// run in rounds: a full round of per_sm * sms CTAs takes per_sm times a CTA's length; a last round of at most sms CTAs
+// runs them alone on their SMs, which costs one CTA's length (a lone eight-warp CTA reaches an SM's full rate:
+// 1536^3, 144 tiles, 50.5 TFLOP/s); a last round of more than sms CTAs costs a full round for a fraction of the
+// machine -- the wave quantisation.  Three plans, in units of one tile's length on a whole SM:
+//   one CTA per tile                rounds(tiles, 1)
+//   K cut in s, reduced in-kernel   rounds(s * tiles, 1 / s) * 1.06     (partial tiles, shorter K loops)
+//   stream-K                        per_sm * tiles / (per_sm * sms) / 0.92, every CTA at least 8 slabs
+// Measured N/T, TFLOP/s, unsplit / best split / stream-K: 1280^3 34.6 / 36.7 / 36.9, 1536^3 50.5 / 47.3 / 48.3,
+// 2048^3 48.9 / 51.0 / 51.9, 2560^3 52.2 / 54.0 / 54.2, 3072^3 57.3 / 56.3 / 56.4, 3584^3 52.7 / 58.0 / 57.1,
+// 4096^3 59.0 / 58.5 / 57.8.
+struct Plan { int kind; unsigned splits; };       // kind 0: one CTA per tile, 1: split K, 2: stream-K
+Plan choose_plan_8x8(size_t tiles, size_t K, size_t sms, size_t per_sm, bool may_alloc)
 {
     auto rounds = [&](size_t ctas, double len) {
-        const size_t full = ctas / (2 * sms), rest = ctas % (2 * sms);
-        return 2.0 * len * full + (rest == 0 ? 0.0 : rest <= sms ? len / 0.8 : 2.0 * len);
+        const size_t full = ctas / (per_sm * sms), rest = ctas % (per_sm * sms);
+        return (double)per_sm * len * full + (rest == 0 ? 0.0 : rest <= sms ? len : (double)per_sm * len);
     };
-    unsigned best = 1;
+    Plan best{0, 1};
     double best_t = rounds(tiles, 1.0);
+    if (!may_alloc) return best;
     for (unsigned sp = 2; sp <= 4; sp++) {
         if (K / sp < 256) break;
         const double t = rounds(tiles * sp, 1.0 / sp) * 1.06;
-        if (t < best_t) { best_t = t; best = sp; }
+        if (t < best_t * 0.999) { best_t = t; best = Plan{1, sp}; }
+    }
+    const size_t nk = (K + BK - 1) / BK;
+    if (tiles * nk >= per_sm * sms * 8) {
+        const double t = (double)tiles / (double)sms / 0.92;
+        if (t < best_t * 0.98) best = Plan{2, 1};
     }
     return best;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stream-K form of the 8 x 8 kernel for products of a few waves: all K slabs of all 128 x 128 tiles are one sequence
+// of units, cut into equal consecutive shares, one per CTA of a grid that exactly fills the machine (two CTAs per SM;
+// one when A is K-contiguous).  With one CTA per tile the last round of CTAs is as long as the others however few
+// tiles it holds (256 tiles on 296 slots: two rounds of time for 1.73 rounds of work, and SMs left with one CTA run
+// below their paired rate); here every CTA works the same number of slabs and all finish together.  A CTA whose
+// share covers a whole tile writes C directly; otherwise it stores its partial tile in its slot of a workspace and
+// draws a ticket from the tile's counter, and the CTA that draws the last ticket adds the slots in slot order -- a fixed
+// order, so the result does not depend on who finishes last -- applies alpha and beta and writes C.  Nobody waits for
+// anybody: no spin loop besides the bounded mbarrier waits of the TMA ring.  (The FP64 kernel does the same for the
+// tail of its grid, dgemm_mma_tma.cu.)
+__device__ __forceinline__ void sk_tile_coords(unsigned tile, unsigned tilesM, unsigned tilesN, unsigned& tm, unsigned& tn)
+{
+    const unsigned per_group = GROUP_M * tilesN;
+    const unsigned g = tile / per_group;
+    const unsigned first = g * GROUP_M;
+    const unsigned rows = min((unsigned)GROUP_M, tilesM - first);
+    const unsigned r = tile - g * per_group;
+    tm = first + r % rows;
+    tn = r / rows;
+}
+
+template <bool TA, bool TB, int STAGES, int MIN_CTAS>
+__global__ void __launch_bounds__(THREADS, MIN_CTAS)
+sgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                     float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
+                     unsigned tilesM, unsigned tilesN, unsigned units, unsigned upc, unsigned maxc,
+                     float* __restrict__ ws, unsigned* __restrict__ counters)
+{
+    constexpr int BN = 128, NJ = 8, NH = 2;
+    constexpr int STAGE_BYTES = stage_bytes(BN);
+    constexpr int B_ROW = BN * 4;
+    __shared__ unsigned s_ticket;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    pdl_launch_dependents();
+
+    const unsigned nk = (unsigned)((K + BK - 1) / BK);
+    const unsigned u0 = blockIdx.x * upc, u1 = min(u0 + upc, units);
+    if (u0 >= u1) return;
+    const unsigned count_local = u1 - u0;
+    const int lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], THREADS / 32);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_wait();
+
+    // unit i of this CTA = K slab (u0 + i) % nk of tile (u0 + i) / nk
+    auto issue = [&](unsigned i) {
+        const unsigned u = u0 + i, t = u / nk, kt = u - t * nk;
+        unsigned tm, tn;
+        sk_tile_coords(t, tilesM, tilesN, tm, tn);
+        const int s = (int)(i % STAGES);
+        unsigned char* sa = smem + s * STAGE_BYTES;
+        unsigned char* sb = sa + A_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        const int k0 = (int)(kt * BK), m0 = (int)(tm * BM), n0 = (int)(tn * BN);
+        if (TA) tma_load_2d(sa, &mapA, k0, m0, &full[s]); else tma_load_2d(sa, &mapA, m0, k0, &full[s]);
+        if (TB) tma_load_2d(sb, &mapB, n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, n0, &full[s]);
+    };
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&mapA);
+        tma_prefetch_descriptor(&mapB);
+        for (unsigned i = 0; i < (unsigned)(STAGES - 1) && i < count_local; i++) issue(i);
+    }
+
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+    auto rowA = [&](int i) { return TA ? tx + 16 * i : tx * 4 + (i & 3) + 64 * (i >> 2); };
+    auto colB = [&](int j) { return ty * 4 + (j & 3) + 64 * (j >> 2); };
+
+    float acc[8][NJ];
+    unsigned long long acc2[4][NJ];
+    auto clear = [&]() {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                if (TA) acc[i][j] = 0.f;
+                else if (i < 4) acc2[i][j] = 0ull;
+            }
+    };
+    clear();
+
+    bool alive = true;
+    unsigned i = 0;
+    while (i < count_local) {
+        const unsigned t = (u0 + i) / nk, seg_first = (u0 + i) - t * nk;
+        const unsigned seg_end = min(u1, (t + 1) * nk) - u0;             // one past the last local unit of this segment
+        for (; i < seg_end; i++) {
+            const int s = (int)(i % STAGES);
+            if (!mbar_wait(&full[s], (i / STAGES) & 1)) return;           // flagged; this tile stays unwritten
+            const unsigned char* sa = smem + s * STAGE_BYTES;
+            const unsigned char* sb = sa + A_BYTES;
+#pragma unroll
+            for (int kc = 0; kc < BK / 4; kc++) {
+                // refill the slot consumed during the previous unit with the unit STAGES-1 ahead (see the kernel above)
+                if (kc == REFILL_KC && threadIdx.x == 32 * (i & 7) && i + STAGES - 1 < count_local) {
+                    if (i >= 1) alive = mbar_wait(&empty[(i - 1) % STAGES], ((i - 1) / STAGES) & 1);
+                    if (alive) issue(i + STAGES - 1);
+                }
+                float a4[4][8], b4[4][NJ];
+                if (TA) {
+#pragma unroll
+                    for (int r = 0; r < 8; r++) {
+                        const float4 v = *reinterpret_cast<const float4*>(sa + (tx + 16 * r) * 128 + ((kc ^ (tx & 7)) << 4));
+                        a4[0][r] = v.x; a4[1][r] = v.y; a4[2][r] = v.z; a4[3][r] = v.w;
+                    }
+                }
+                if (!TB) {
+#pragma unroll
+                    for (int j = 0; j < NJ; j++) {
+                        const int n = ty * 4 + (j & 3) + 64 * (j >> 2);
+                        const float4 v = *reinterpret_cast<const float4*>(sb + n * 128 + ((kc ^ (n & 7)) << 4));
+                        b4[0][j] = v.x; b4[1][j] = v.y; b4[2][j] = v.z; b4[3][j] = v.w;
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float a[8], b[NJ];
+                    if (TA) {
+#pragma unroll
+                        for (int r = 0; r < 8; r++) a[r] = a4[q][r];
+                    } else {
+                        const float4 v0 = *reinterpret_cast<const float4*>(sa + (kc * 4 + q) * 512 + tx * 16);
+                        const float4 v1 = *reinterpret_cast<const float4*>(sa + (kc * 4 + q) * 512 + 256 + tx * 16);
+                        a[0] = v0.x; a[1] = v0.y; a[2] = v0.z; a[3] = v0.w;
+                        a[4] = v1.x; a[5] = v1.y; a[6] = v1.z; a[7] = v1.w;
+                    }
+                    if (!TB) {
+#pragma unroll
+                        for (int j = 0; j < NJ; j++) b[j] = b4[q][j];
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < NH; h++) {
+                            const float4 v = *reinterpret_cast<const float4*>(sb + (kc * 4 + q) * B_ROW + h * 256 + ty * 16);
+                            b[4 * h + 0] = v.x; b[4 * h + 1] = v.y; b[4 * h + 2] = v.z; b[4 * h + 3] = v.w;
+                        }
+                    }
+                    if (TA) {
+#pragma unroll
+                        for (int r = 0; r < 8; r++)
+#pragma unroll
+                            for (int j = 0; j < NJ; j++) acc[r][j] = fmaf(a[r], b[j], acc[r][j]);
+                    } else {
+                        unsigned long long a2[4], bd[NJ];
+#pragma unroll
+                        for (int pr = 0; pr < 4; pr++) a2[pr] = pack2(a[2 * pr], a[2 * pr + 1]);
+#pragma unroll
+                        for (int j = 0; j < NJ; j++) bd[j] = pack2(b[j], b[j]);
+#pragma unroll
+                        for (int pr = 0; pr < 4; pr++)
+#pragma unroll
+                            for (int j = 0; j < NJ; j++) acc2[pr][j] = ffma2(a2[pr], bd[j], acc2[pr][j]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        if (!TA) {
+#pragma unroll
+            for (int pr = 0; pr < 4; pr++)
+#pragma unroll
+                for (int j = 0; j < NJ; j++) unpack2(acc2[pr][j], acc[2 * pr][j], acc[2 * pr + 1][j]);
+        }
+
+        // ---- end of this CTA's segment [seg_first, seg_last] of tile t
+        const unsigned seg_last = (u0 + seg_end - 1) - t * nk;
+        unsigned tm, tn;
+        sk_tile_coords(t, tilesM, tilesN, tm, tn);
+        const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
+        bool write_c = true;
+        if (!(seg_first == 0 && seg_last == nk - 1)) {
+            const unsigned first_cta = (t * nk) / upc;
+            const unsigned idx = blockIdx.x - first_cta;
+            const unsigned count = ((t + 1) * nk - 1) / upc - first_cta + 1;
+            float* slot = ws + ((size_t)t * maxc + idx) * (size_t)(BM * BN);
+#pragma unroll
+            for (int r = 0; r < 8; r++)
+#pragma unroll
+                for (int j = 0; j < NJ; j++) __stcg(slot + (r * NJ + j) * THREADS + tid, acc[r][j]);
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) s_ticket = atomicAdd(&counters[t], 1u);
+            __syncthreads();
+            write_c = (s_ticket == count - 1);
+            if (write_c) {
+                __threadfence();
+                const float* base = ws + (size_t)t * maxc * (size_t)(BM * BN) + tid;
+#pragma unroll
+                for (int r = 0; r < 8; r++)
+#pragma unroll
+                    for (int j = 0; j < NJ; j++) acc[r][j] = 0.f;
+                for (unsigned c = 0; c < count; c++) {
+                    const float* sl = base + (size_t)c * (BM * BN);
+                    float v[8][NJ];
+#pragma unroll
+                    for (int r = 0; r < 8; r++)
+#pragma unroll
+                        for (int j = 0; j < NJ; j++) v[r][j] = __ldcg(sl + (r * NJ + j) * THREADS);
+#pragma unroll
+                    for (int r = 0; r < 8; r++)
+#pragma unroll
+                        for (int j = 0; j < NJ; j++) acc[r][j] += v[r][j];
+                }
+            }
+            __syncthreads();                                  // s_ticket is reused by the next segment
+        }
+        if (write_c) {
+            // C = alpha*acc + beta*C; beta == 0 never reads C
+            const bool useC = (beta != 0.f);
+            const bool vec = !TA && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (ldc % 4 == 0);
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const size_t col = n0 + colB(j);
+                if (col >= N) continue;
+                float* cc = C + col * ldc;
+                if (vec) {
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const size_t row = m0 + tx * 4 + 64 * h;
+                        if (row + 3 < M) {
+                            float4 r;
+                            r.x = alpha * acc[4 * h + 0][j]; r.y = alpha * acc[4 * h + 1][j];
+                            r.z = alpha * acc[4 * h + 2][j]; r.w = alpha * acc[4 * h + 3][j];
+                            if (useC) {
+                                const float4 o = *reinterpret_cast<const float4*>(cc + row);
+                                r.x = fmaf(beta, o.x, r.x); r.y = fmaf(beta, o.y, r.y);
+                                r.z = fmaf(beta, o.z, r.z); r.w = fmaf(beta, o.w, r.w);
+                            }
+                            *reinterpret_cast<float4*>(cc + row) = r;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                if (row + e < M) {
+                                    float r = alpha * acc[4 * h + e][j];
+                                    if (useC) r = fmaf(beta, cc[row + e], r);
+                                    cc[row + e] = r;
+                                }
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int r8 = 0; r8 < 8; r8++) {
+                        const size_t row = m0 + rowA(r8);
+                        if (row < M) {
+                            float r = alpha * acc[r8][j];
+                            if (useC) r = fmaf(beta, cc[row], r);
+                            cc[row] = r;
+                        }
+                    }
+                }
+            }
+        }
+        clear();
+    }
+}
+
+constexpr unsigned SK_MIN_UNITS = 4;         // smallest share of a CTA, in K slabs of 32
+
+template <bool TA, bool TB, int STAGES, int MIN_CTAS>
+cudaError_t launch_streamk(const GemmProblem<float>& p, cudaStream_t s)
+{
+    void* enc = get_tensor_map_encoder();
+    CUtensorMap mapA, mapB;
+    bool ok;
+    if (TA) ok = make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.A, p.K, p.M, p.lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    else    ok = make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.A, p.M, p.K, p.lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!ok) return cudaErrorNotSupported;
+    if (TB) ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.N, p.K, p.ldb, 128, BK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    else    ok = make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.K, p.N, p.ldb, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!ok) return cudaErrorNotSupported;
+    constexpr int SMEM = smem_bytes(STAGES, 128);
+    static DeviceOnce once;
+    cudaError_t e = once.run([] {
+        return cudaFuncSetAttribute(sgemm_streamk_kernel<TA, TB, STAGES, MIN_CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    });
+    if (e != cudaSuccess) return e;
+    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128, tiles = tilesM * tilesN;
+    const size_t nk = (p.K + BK - 1) / BK, units = tiles * nk;
+    if (units >= (1ull << 31)) return cudaErrorNotSupported;
+    const size_t slots = (size_t)sm_count() * MIN_CTAS;
+    const size_t ctas = std::max<size_t>(1, std::min<size_t>(slots, units / SK_MIN_UNITS));
+    const size_t upc = (units + ctas - 1) / ctas;
+    const size_t maxc = (nk + upc - 1) / upc + 1;
+    const size_t ws_floats = tiles * maxc * (size_t)(BM * 128);
+    float* ws = nullptr;
+    e = ws_alloc(reinterpret_cast<void**>(&ws), ws_floats * sizeof(float) + tiles * sizeof(unsigned) + 256, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return cudaErrorNotSupported; }     // the caller falls back to one CTA per tile
+    unsigned* counters = reinterpret_cast<unsigned*>(ws + ws_floats);
+    e = cudaMemsetAsync(counters, 0, tiles * sizeof(unsigned), s);
+    if (e == cudaSuccess) {
+        char name[64];
+        snprintf(name, sizeof(name), "sgemm_streamk<%c,%c>", TA ? 'T' : 'N', TB ? 'T' : 'N');
+        set_last_variant(name);
+        e = launch_pdl(sgemm_streamk_kernel<TA, TB, STAGES, MIN_CTAS>, dim3((unsigned)((units + upc - 1) / upc)), dim3(THREADS), SMEM, s,
+                       mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)units,
+                       (unsigned)upc, (unsigned)maxc, ws, counters);
+        count_launch();
+    }
+    const cudaError_t e2 = ws_free(ws, s);
+    return e != cudaSuccess ? e : e2;
+}
+
+cudaError_t launch_streamk_any(const GemmProblem<float>& p, cudaStream_t s)
+{
+    if (!p.ta && !p.tb) return launch_streamk<false, false, 3, 2>(p, s);
+    if (!p.ta && p.tb) return launch_streamk<false, true, 3, 2>(p, s);
+    if (p.ta && !p.tb) return launch_streamk<true, false, 5, 1>(p, s);
+    return launch_streamk<true, true, 5, 1>(p, s);
 }
 
 template <int BN, int STAGES, int MIN_CTAS>
@@ -695,26 +1029,36 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     if (forced == PATH_TMA_ONE_CTA) return launch_any<128, 5, 1>(p, s);
     if (forced == PATH_TMA_TWO_CTAS) return launch_any<128, 3, 2>(p, s);
     const bool may_split = gemm_may_allocate() && p.C != p.A && p.C != p.B && getenv("CLBLAS_B200_NO_SPLITK") == nullptr;
-    // Tuning aid: CLBLAS_B200_SGEMM_FORCE="<tile>,<splits>" with tile 64 / 128 (8 x 8 register-tile kernel) or 16 (16 x 8).
+    // Tuning aid: CLBLAS_B200_SGEMM_FORCE="<tile>,<splits>" with tile 64 / 128 (8 x 8 register-tile kernel), 16 (16 x 8) or 1 (stream-K).
     if (const char* f = getenv("CLBLAS_B200_SGEMM_FORCE")) {
         int tile = 0, sp = 1;
         if (sscanf(f, "%d,%d", &tile, &sp) >= 1 && may_split && p.tri == TRI_FULL && min_bn < 128 && sp >= 1 && sp <= 8) {
             if (tile == 16 && !p.ta && p.tb) return launch_nt_16x8<false>(p, s, (unsigned)sp);
+            if (tile == 1) { const cudaError_t e = launch_streamk_any(p, s); if (e != cudaErrorNotSupported) return e; }     // "1,0": stream-K
             if (tile == 64) return p.ta ? launch_any<64, 5, 1>(p, s, (unsigned)sp) : launch_any<64, 3, 2>(p, s, (unsigned)sp);
             if (tile == 128) return p.ta ? launch_any<128, 5, 1>(p, s, (unsigned)sp) : launch_any<128, 3, 2>(p, s, (unsigned)sp);
         }
     }
     // The 16 x 8 register-tile kernel has four warps per CTA: it needs both of an SM's CTA slots filled for several
     // waves and a K loop long enough to amortise its per-thread epilogue.  Measured against the 8 x 8 kernel: 8192^3
-    // 63.5 vs 57.8-60.2, 3008 x 4100 x 1537 48.6 vs 47.2, 4096^3 58.9 vs 59.1, but 1536^3 (144 tiles) 35.6 vs 50.4,
-    // 2048^3 44.5 vs 48.9 and 4096 x 4096 x 512 48.7 vs 53.9 TFLOP/s.  Between two and six waves the 8 x 8 kernel
-    // takes over where splitting K evens out its last round (choose_splits_8x8).
-    if (!p.ta && p.tb && min_bn < 128 && tiles128 >= (size_t)sm_count() * 4 && p.K >= 1024 && getenv("CLBLAS_B200_SGEMM_8X8") == nullptr) {
-        if (p.tri != TRI_FULL) return launch_nt_16x8<true>(p, s);
-        const unsigned sp = (may_split && tiles128 < (size_t)sm_count() * 12) ? choose_splits_8x8(tiles128, p.K, (size_t)sm_count()) : 1;
-        if (sp > 1) return launch_any<128, 3, 2>(p, s, sp);
-        return launch_nt_16x8<false>(p, s);
+    // 63.5 vs 57.8-60.2, 6144^3 62.2 vs 58.6, 4096^3 58.9 vs 59.0, but 1536^3 (144 tiles) 35.6 vs 50.5, 2048^3 44.5 vs 48.9
+    // and 4096 x 4096 x 512 48.7 vs 53.9 TFLOP/s.  From four waves on it takes the unsplit N/T products.
+    const bool k8x8 = getenv("CLBLAS_B200_SGEMM_8X8") != nullptr;
+    const bool big_nt = !p.ta && p.tb && min_bn < 128 && tiles128 >= (size_t)sm_count() * 4 && p.K >= 1024 && !k8x8;
+    if (big_nt && p.tri != TRI_FULL) return launch_nt_16x8<true>(p, s);
+    // Between about half a wave and twelve waves the 8 x 8 kernel's rounds may come out uneven: split K or go
+    // stream-K where the model says so (choose_plan_8x8).
+    if (p.tri == TRI_FULL && min_bn < 128 && p.K >= 256 && tiles128 >= 64 && tiles128 < (size_t)sm_count() * 12) {
+        Plan plan = choose_plan_8x8(tiles128, p.K, (size_t)sm_count(), p.ta ? 1 : 2, may_split);
+        if (tiles128 < 96 && plan.kind != 2) plan = Plan{0, 1};      // below 96 tiles the 128 x 64 tiles further down beat a split
+        if (plan.kind == 2) {
+            const cudaError_t e = launch_streamk_any(p, s);
+            if (e != cudaErrorNotSupported) return e;
+        } else if (plan.kind == 1) {
+            return p.ta ? launch_any<128, 5, 1>(p, s, plan.splits) : launch_any<128, 3, 2>(p, s, plan.splits);
+        }
     }
+    if (big_nt) return launch_nt_16x8<false>(p, s);
     // Fewer 128-wide tiles than SMs: halve the tile width so that twice as many CTAs share the work
     // (three of them fit an SM).  With A K-contiguous the 4-k fragments need the one-CTA register budget.
     if (min_bn < 128 && tiles128 < 120) {

@@ -128,6 +128,26 @@ def test_sgemm_split_k_against_wave_quantisation_is_exact(lib):
     assert lib.last_gemm_variant().endswith("+splitk3") and torch.equal(C1, C2)
 
 
+def test_sgemm_stream_k_is_exact_and_deterministic(lib):
+    """Products of about one round of CTAs go to the stream-K kernel (every CTA the same number of K slabs, partial
+    tiles added in slot order by the CTA that finishes a tile last): exact on integer inputs, ragged edges included,
+    for M-contiguous and K-contiguous A, and bit-identical when repeated."""
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1280, 1280, 1280, seed=8040)
+    assert v == "sgemm_streamk<N,T>", v
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1397, 1401, 1413, alpha=-1.0, beta=0.0, pad=(3, 3, 0), seed=8041)      # 11 x 11 tiles
+    assert v == "sgemm_streamk<N,T>", v
+    v = _exact_gemm(lib, "s", ColumnMajor, Trans, NoTrans, 1408, 1408, 990, seed=8042)           # K-contiguous A: one CTA per SM
+    assert v == "sgemm_streamk<T,N>", v
+    g = oracle.rng(8043, 0)
+    n = 1280
+    A, B = (torch.from_numpy(g.standard_normal(n * n).astype(np.float32)).cuda() for _ in range(2))
+    C1, C2 = torch.zeros(n * n, device="cuda"), torch.zeros(n * n, device="cuda")
+    for C in (C1, C2):
+        assert lib.clblasSgemm(ColumnMajor, NoTrans, Trans, n, n, n, 1.0, A, 0, n, B, 0, n, 0.0, C, 0, n) == lib.clblasSuccess
+    torch.cuda.synchronize()
+    assert lib.last_gemm_variant() == "sgemm_streamk<N,T>" and torch.equal(C1, C2)
+
+
 def test_dgemm_streamk_tail_and_sgemm_splitk_are_exact(lib):
     v = _exact_gemm(lib, "d", ColumnMajor, Trans, NoTrans, 2048, 2048, 2048, seed=8020)
     assert v.endswith("+streamk_tail"), v

@@ -267,3 +267,23 @@ def test_repacked_operands_exact(lib, prec):
                 assert np.array_equal(oracle.view(got, order, NoTrans, M, N, c["ldc"], c["offC"]), want), c
                 assert outside_untouched(bufs[2], got, c)
     assert lib.device_fault() == 0
+
+
+def test_sgemm_transposed_in_16_byte_accesses_exact(lib):
+    """Aligned K-contiguous SGEMM operands of a product large enough to be transposed first (the 16-byte path of the
+    transposition kernel, edges that are not multiples of its 64 x 64 tile): every transposition ends in the N/T
+    kernel and must give the exact product of the integer-valued inputs."""
+    seed = 31000
+    for order in (ColumnMajor, RowMajor):
+        for ta, tb in ((NoTrans, NoTrans), (Trans, NoTrans), (Trans, Trans)):
+            seed += 1
+            M, N, K = 2052, 2116, 2056
+            c = cases.gemm_case("s", order, ta, tb, M, N, K, alpha=1.0, beta=2.0, mode="int", seed=seed)
+            opA, opB, C = cases.gemm_logical(c)
+            bufs = cases.gemm_buffers(c, (opA, opB, C), tail=0)
+            st, got = run_gemm_gpu(lib, c, bufs)
+            assert st == lib.clblasSuccess
+            assert "<N,T," in lib.last_gemm_variant() or lib.last_gemm_variant().startswith("sgemm_nt_16x8"), lib.last_gemm_variant()
+            want = (opA.astype(np.float64) @ opB.astype(np.float64) + 2.0 * C.astype(np.float64)).astype(np.float32)
+            assert np.array_equal(oracle.view(got, order, NoTrans, M, N, c["ldc"], c["offC"]), want), c
+    assert lib.device_fault() == 0
