@@ -136,7 +136,7 @@ def test_sgemm_stream_k_is_exact_and_deterministic(lib):
     assert v == "sgemm_streamk<N,T>", v
     v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1397, 1401, 1413, alpha=-1.0, beta=0.0, pad=(3, 3, 0), seed=8041)      # 11 x 11 tiles
     assert v == "sgemm_streamk<N,T>", v
-    v = _exact_gemm(lib, "s", ColumnMajor, Trans, NoTrans, 1408, 1408, 990, seed=8042)           # K-contiguous A: one CTA per SM
+    v = _exact_gemm(lib, "s", ColumnMajor, Trans, NoTrans, 1408, 1408, 992, seed=8042)           # K-contiguous A: one CTA per SM
     assert v == "sgemm_streamk<T,N>", v
     g = oracle.rng(8043, 0)
     n = 1280
