@@ -36,3 +36,29 @@ def test_compare_tables(tmp_path):
     shipped = os.path.join(ROOT, "doc", "performance", "B200", "clblas_b200_dgemm_col_nt.csv")
     r = subprocess.run([sys.executable, os.path.join(PERF, "compare_performance.py"), shipped, shipped], capture_output=True, text=True)
     assert r.returncode == 0 and r.stdout.count("\n") >= 16
+
+
+def test_reference_arm_of_the_benchmark_maps_nothing_of_the_cuda_library():
+    """`bench.py --impl reference` times the reference's CPU code only: the process must never import the CUDA package
+    (or torch) and must print the same `config` object as the GPU arm builds for that workload."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, json; sys.path.insert(0, %r); import bench\n"
+        "bench.cpu_reference_sample = lambda wl, seconds_target=1.0, threads=None: (0.01, 4, 'port', 'stub sample')\n"
+        "sys.argv = ['bench.py', '--impl', 'reference', '--steps', '2', '--warmup', '1']\n"
+        "bench.main()\n"
+        "maps = open('/proc/self/maps').read()\n"
+        "print(json.dumps({'lib': 'libclblas_b200' in maps, 'pkg': 'clblas_b200' in sys.modules, 'torch': 'torch' in sys.modules}))\n" % root)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    line, flags = json.loads(lines[0]), json.loads(lines[1])
+    assert flags == {"lib": False, "pkg": False, "torch": False}
+    assert line["impl"] == "reference" and line["metric"] == "SGEMM TFLOP/s" and line["e2e"]["h2d_bytes_per_step"] == 0
+    sys.path.insert(0, root)
+    import bench
+    assert line["config"] == bench.workloads()["sgemm32768"].config(1)
+    assert line["cpu_baseline"]["kind"] in ("reference", "port")
