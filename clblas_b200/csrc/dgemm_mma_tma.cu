@@ -457,9 +457,14 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
     size_t main_tiles = tilesM * tilesN;
     if (BN == 128 && !TRI) {
-        // Whole waves go to the kernel above, the last partial wave to the stream-K kernel.
+        // Whole waves go to the kernel above, the last partial wave to the stream-K kernel.  A product of fewer tiles than
+        // SMs with a long K loop is one partial wave: all of it goes to the stream-K kernel, every SM working the same
+        // number of slabs.  It pays from about 40 slabs per SM on (TFLOP/s, with / narrow tiles instead: 1280^3 27.5 / 20.9,
+        // 1024 x 1024 x 8192 33.7 / 29.0; but 1024^3, 28 slabs per SM, 22.8 / 25.7).
         const size_t T = tilesM * tilesN, S = (size_t)sm_count(), R = T % S, nk = (p.K + BK - 1) / BK;
-        if (T > S && R != 0 && R * 20 <= S * 17 && nk >= 2 * SK_MIN_SLABS && nk < (1u << 20) && gemm_may_allocate() &&
+        const bool tail = T > S && R != 0 && R * 20 <= S * 17;
+        const bool whole = T < S && T * 20 <= S * 19 && T * nk >= S * 40;
+        if ((tail || whole) && nk >= 2 * SK_MIN_SLABS && nk < (1u << 20) && gemm_may_allocate() &&
             p.C != p.A && p.C != p.B && getenv("CLBLAS_B200_NO_STREAMK") == nullptr) {
             const size_t units = R * nk;
             const size_t ctas = std::max<size_t>(1, std::min<size_t>(S, units / SK_MIN_SLABS));
@@ -475,9 +480,11 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
                 if (e == cudaSuccess) {
                     main_tiles = T - R;
                     set_last_variant(variant_name(TA, TB, BN, TRI, true));
-                    e = launch_pdl(dgemm_mma_tma_kernel<TA, TB, BN, TRI>, dim3((unsigned)main_tiles), dim3(THREADS), smem_bytes(BN), s,
-                                   mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)S, p.tri);
-                    count_launch();
+                    if (main_tiles > 0) {
+                        e = launch_pdl(dgemm_mma_tma_kernel<TA, TB, BN, TRI>, dim3((unsigned)main_tiles), dim3(THREADS), smem_bytes(BN), s,
+                                       mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)S, p.tri);
+                        count_launch();
+                    }
                     if (e == cudaSuccess) {
                         e = launch_pdl(dgemm_streamk_kernel<TA, TB>, dim3((unsigned)((units + upc - 1) / upc)), dim3(THREADS), smem_bytes(128), s,
                                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
@@ -543,7 +550,11 @@ cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s, i
     set_last_kernel("dgemm_mma_tma");
     // Widest tile that still gives the 148 SMs about one CTA each; narrower tiles only for
     // problems that 128-wide tiles would leave most SMs idle on.
-    if (min_bn >= 128 || tilesM * ((p.N + 127) / 128) >= 120) return launch_t<128>(p, s);
+    const size_t tiles128 = tilesM * ((p.N + 127) / 128), nk = (p.K + BK - 1) / BK;
+    // (fewer 128-wide tiles than that but at least 40 K slabs per SM: still 128 wide, shared out by the stream-K kernel)
+    const bool share_k = p.tri == TRI_FULL && tiles128 * nk >= (size_t)sm_count() * 40 && gemm_may_allocate() && p.C != p.A && p.C != p.B &&
+                         getenv("CLBLAS_B200_NO_STREAMK") == nullptr;
+    if (min_bn >= 128 || tiles128 >= 120 || share_k) return launch_t<128>(p, s);
     if (tilesM * ((p.N + 63) / 64) >= 120) return launch_t<64>(p, s);
     if (tilesM * ((p.N + 31) / 32) >= 120) return launch_t<32>(p, s);
     return launch_t<16>(p, s);

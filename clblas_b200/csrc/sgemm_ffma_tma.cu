@@ -45,6 +45,13 @@ constexpr int BM = 128, BK = 32;
 constexpr int A_BYTES = BM * BK * 4;                // 16 KB
 constexpr int THREADS = 256;
 constexpr int GROUP_M = 16;
+
+// CTAs per wave as the kernels' `wave` argument (every other wave walks K backwards), or 0 = all forwards when
+// CLBLAS_B200_REVERSE_K=0 (a measuring switch).
+static unsigned reverse_wave(int ctas) {
+    static const bool off = [] { const char* e = getenv("CLBLAS_B200_REVERSE_K"); return e && e[0] == '0'; }();
+    return off ? 0u : (unsigned)ctas;
+}
 constexpr int REFILL_KC = 6;                         // eighth of the slab (0..7) in which the freed slot is refilled
 
 constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 4; }
@@ -381,7 +388,7 @@ cudaError_t launch(const GemmProblem<float>& p, cudaStream_t s, unsigned splits 
     set_last_variant(name);
     e = launch_pdl(sgemm_ffma_tma_kernel<TA, TB, BN, STAGES, MIN_CTAS, TRI>, dim3((unsigned)(tilesM * tilesN)), dim3(THREADS), SMEM, s,
                    mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
-                   (unsigned)(sm_count() * MIN_CTAS), p.tri, 1u, (size_t)0, (float*)nullptr, (size_t)0, (unsigned*)nullptr);
+                   reverse_wave(sm_count() * MIN_CTAS), p.tri, 1u, (size_t)0, (float*)nullptr, (size_t)0, (unsigned*)nullptr);
     count_launch();
     return e;
 }
@@ -633,7 +640,7 @@ cudaError_t launch_nt_16x8(const GemmProblem<float>& p, cudaStream_t s, unsigned
     set_last_variant(TRI ? "sgemm_nt_16x8+tri" : "sgemm_nt_16x8");
     e = launch_pdl(sgemm_nt_16x8_kernel<TRI>, dim3((unsigned)tiles), dim3(T16_THREADS), T16_SMEM, s,
                    mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
-                   (unsigned)(sm_count() * 2), p.tri, 1u, (size_t)0, (float*)nullptr, (size_t)0, (unsigned*)nullptr);
+                   reverse_wave(sm_count() * 2), p.tri, 1u, (size_t)0, (float*)nullptr, (size_t)0, (unsigned*)nullptr);
     count_launch();
     return e;
 }

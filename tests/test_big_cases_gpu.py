@@ -155,6 +155,9 @@ def test_dgemm_streamk_tail_and_sgemm_splitk_are_exact(lib):
     assert "+splitk" in v, v
     v = _exact_gemm(lib, "d", ColumnMajor, NoTrans, Trans, 128, 1000, 128, seed=8022)
     assert v.startswith("dgemm_mma_tma<N,T,") and not v.startswith("dgemm_mma_tma<N,T,128>"), v     # a narrow-tile variant
+    # nine 128-wide tiles with 1000 K slabs each: no whole wave at all, every SM takes an equal share of the slabs
+    v = _exact_gemm(lib, "d", ColumnMajor, NoTrans, NoTrans, 300, 384, 16000, seed=8023)
+    assert v == "dgemm_mma_tma<N,N,128>+streamk_tail", v
 
 
 def test_triangular_16x8_kernel_through_ssyrk_and_cherk(lib):
