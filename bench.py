@@ -45,12 +45,14 @@ LEFT, LOWER, NON_UNIT = 0, 1, 1
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum), captured with ncu
 # at the workload's full size where the capture is one pass (profiles/dram_traffic_full_size.md).  None where no
-# capture of that workload exists (the DTRSM is > 100 launches of different shapes; the 32768^3 SGEMM runs > 1 s).
+# capture of that workload exists: the 32768^3 SGEMM (12 GB, launches of over a second) is beyond what a capture may
+# hold, and its traffic cannot be scaled from a smaller case (8192^3 -> 16384^3: 8x the flops, 26x the bytes).  The
+# DTRSM figure is the sum over the 43 launches of one call.
 NCU_TRAFFIC_BYTES = {
     "sgemm1024": int(12.63e6),
     "dgemm8192": int(6.107e9 + 509.2e6 + 620.1e6 + 12.4e6),
     "sgemm_ragged": int(94.89e6 + 18.84e6),
-    "dtrsm8192": None,
+    "dtrsm8192": int(7.93e9 + 1.75e9),
     "sgemm32768": None,
     "sgemm8192": int(3.257e9 + 263.6e6),
 }
