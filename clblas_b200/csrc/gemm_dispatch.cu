@@ -77,12 +77,13 @@ cudaError_t gemm_any(const GemmProblem<T>& p, cudaStream_t s)
     Fix fa = KEEP, fb = KEEP;
     const bool may_alloc = t_forbid_alloc == 0 && forced_gemm_path() == PATH_AUTO;
     const double work = 2.0 * (double)p.M * (double)p.N * (double)p.K;
-    static const double transpose_min_work = [] { const char* v = getenv("CLBLAS_B200_TRANSPOSE_MIN_WORK"); return v ? atof(v) : 4e9; }();
+    static const double transpose_min_work = [] { const char* v = getenv("CLBLAS_B200_TRANSPOSE_MIN_WORK"); return v ? atof(v) : 3e9; }();
     if (may_alloc && p.K >= 64 && work >= (kFloat ? std::min(transpose_min_work, 1.5e10) : 1.5e10)) {
         // The extra pass over an operand is paid back by the other dimension of C; products below
         // about 2000^3 are too short for the extra launches of a plain copy to pay.  A transposition for SGEMM
-        // pays from about 1500^3 on (N/N 1536^3: 40.6 in place, 49 TFLOP/s through the N/T kernel; 1024^3: 31.6
-        // either way): the kernels for K-contiguous operands are bound by shared-memory bandwidth.
+        // pays from about 1150^3 on (TFLOP/s, transposed first / in place: N/N 1152^3 35.9 / 31.7, 1536^3 48.2 / 40.6,
+        // 4096^3 60.5 / 46.4; T/N 1152^3 33.5 / 27.1; but N/N 1024^3 29.8 / 31.6): the kernels for K-contiguous
+        // operands are bound by shared-memory bandwidth and cannot use the 16 x 8 register tile.
         if (work >= 1.5e10) {
             if (!okA && p.N >= 512) fa = COPY;
             if (!okB && p.M >= 512) fb = COPY;

@@ -409,6 +409,81 @@ constexpr int T16_REFILL_KC = 3;        // quarter of the slab (0..3) in which t
 constexpr int T16_STAGE_BYTES = (128 + 128) * BK * 4;          // 32 KB
 constexpr int T16_SMEM = T16_STAGES * T16_STAGE_BYTES + 1024 + 256;
 
+// NCH chunks of eight k rows of the 16 x 8 register tile: sa / sb point at this thread's fragment of the first row in the
+// A / B slab in shared memory (512 bytes per k row); `refill` runs once, before chunk REFILL_AT (the producer step of the
+// TMA ring).  acc2[2*g + q][4*h + c] = rows (tx*4 + 32*g + 2*q, +1) of column ty*4 + 64*h + c.
+template <int NCH, int REFILL_AT, class Refill>
+__device__ __forceinline__ void t16_rows(const unsigned char* sa, const unsigned char* sb, unsigned long long (&acc2)[8][8], Refill&& refill)
+{
+    // Fully unrolled: a trip count of eight k rows keeps the code in the instruction cache but costs 3 % at
+    // 8192^3 (fragment loads are not carried across trips), measured.
+#pragma unroll
+    for (int kc = 0; kc < NCH; kc++) {
+        if (kc == REFILL_AT) refill();
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            unsigned long long a2[8], bd[8];
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                // 16 bytes = rows (0,1) and (2,3) of the group: already the two packed operands
+                const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(sa + (kc * 8 + q) * 512 + g * 128);
+                a2[2 * g] = v.x; a2[2 * g + 1] = v.y;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const float4 v = *reinterpret_cast<const float4*>(sb + (kc * 8 + q) * 512 + h * 256);
+                bd[4 * h + 0] = pack2(v.x, v.x); bd[4 * h + 1] = pack2(v.y, v.y);
+                bd[4 * h + 2] = pack2(v.z, v.z); bd[4 * h + 3] = pack2(v.w, v.w);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc2[i][j] = ffma2(a2[i], bd[j], acc2[i][j]);
+        }
+    }
+}
+
+// D = al*acc + be*D on row groups [G0, G1) of the thread's 16 x 8 entries of the tile at (m0, n0); be == 0 never reads D.
+template <bool TRI, int G0, int G1>
+__device__ __forceinline__ void t16_epilogue(const unsigned long long (&acc2)[8][8], float* D, size_t ldd, float al, float be, int trimode,
+                                             size_t m0, size_t n0, size_t M, size_t N, int tx, int ty)
+{
+    const bool useC = (be != 0.f);
+    const bool vec = (!TRI || trimode == TRI_FULL) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0) && (ldd % 4 == 0);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const size_t col = n0 + ty * 4 + (j & 3) + 64 * (j >> 2);
+        if (col >= N) continue;
+        float* cc = D + col * ldd;
+#pragma unroll
+        for (int g = G0; g < G1; g++) {
+            const size_t row = m0 + tx * 4 + 32 * g;
+            float v[4];
+            unpack2(acc2[2 * g][j], v[0], v[1]);
+            unpack2(acc2[2 * g + 1][j], v[2], v[3]);
+            if (vec && row + 3 < M) {
+                float4 r;
+                r.x = al * v[0]; r.y = al * v[1]; r.z = al * v[2]; r.w = al * v[3];
+                if (useC) {
+                    const float4 o = *reinterpret_cast<const float4*>(cc + row);
+                    r.x = fmaf(be, o.x, r.x); r.y = fmaf(be, o.y, r.y);
+                    r.z = fmaf(be, o.z, r.z); r.w = fmaf(be, o.w, r.w);
+                }
+                *reinterpret_cast<float4*>(cc + row) = r;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    if (row + e < M && !(TRI && tri_masked(trimode, row + e, col))) {
+                        float r = al * v[e];
+                        if (useC) r = fmaf(be, cc[row + e], r);
+                        cc[row + e] = r;
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <bool TRI>
 __global__ void __launch_bounds__(T16_THREADS, 2)
 sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
@@ -489,79 +564,22 @@ sgemm_nt_16x8_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         if (!mbar_wait(&full[s], (kt / T16_STAGES) & 1)) break;
         const unsigned char* sa = smem + s * T16_STAGE_BYTES + offA;
         const unsigned char* sb = smem + s * T16_STAGE_BYTES + A_BYTES + offB;
-        // Fully unrolled: a trip count of eight k rows keeps the code in the instruction cache but costs 3 % at
-        // 8192^3 (fragment loads are not carried across trips), measured.
-#pragma unroll
-        for (int kc = 0; kc < BK / 8; kc++) {
-            // Refill the slot consumed during the previous slab, in the last quarter of this one (by then even a
-            // lagging warp has released it) and from a different warp every slab, so that the wait, when there
-            // is one, does not always hold back the same quarter of the CTA.  Measured at 8192^3: first quarter /
-            // thread 0: 61.7, last quarter / thread 0: 63.3, last quarter / rotating: 63.5 TFLOP/s.
-            if (kc == T16_REFILL_KC && threadIdx.x == 32 * (kt & 3) && kt + T16_STAGES - 1 < nk) {
+        // Refill the slot consumed during the previous slab, in the last quarter of this one (by then even a
+        // lagging warp has released it) and from a different warp every slab, so that the wait, when there
+        // is one, does not always hold back the same quarter of the CTA.  Measured at 8192^3: first quarter /
+        // thread 0: 61.7, last quarter / thread 0: 63.3, last quarter / rotating: 63.5 TFLOP/s.
+        t16_rows<BK / 8, T16_REFILL_KC>(sa, sb, acc2, [&] {
+            if (threadIdx.x == 32 * (kt & 3) && kt + T16_STAGES - 1 < nk) {
                 if (kt >= 1) alive = mbar_wait(&empty[(kt - 1) % T16_STAGES], ((kt - 1) / T16_STAGES) & 1);
                 if (alive) issue(kt + T16_STAGES - 1);
             }
-#pragma unroll
-            for (int q = 0; q < 8; q++) {
-                unsigned long long a2[8], bd[8];
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    // 16 bytes = rows (0,1) and (2,3) of the group: already the two packed operands
-                    const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(sa + (kc * 8 + q) * 512 + g * 128);
-                    a2[2 * g] = v.x; a2[2 * g + 1] = v.y;
-                }
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const float4 v = *reinterpret_cast<const float4*>(sb + (kc * 8 + q) * 512 + h * 256);
-                    bd[4 * h + 0] = pack2(v.x, v.x); bd[4 * h + 1] = pack2(v.y, v.y);
-                    bd[4 * h + 2] = pack2(v.z, v.z); bd[4 * h + 3] = pack2(v.w, v.w);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; i++)
-#pragma unroll
-                    for (int j = 0; j < 8; j++) acc2[i][j] = ffma2(a2[i], bd[j], acc2[i][j]);
-            }
-        }
+        });
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
 
-    // ---- epilogue: D = al*acc + be*D; be == 0 never reads D
     auto epilogue = [&](float* D, size_t ldd, float al, float be, int trimode) {
-        const bool useC = (be != 0.f);
-        const bool vec = (!TRI || trimode == TRI_FULL) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0) && (ldd % 4 == 0);
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const size_t col = n0 + ty * 4 + (j & 3) + 64 * (j >> 2);
-            if (col >= N) continue;
-            float* cc = D + col * ldd;
-#pragma unroll
-            for (int g = 0; g < 4; g++) {
-                const size_t row = m0 + tx * 4 + 32 * g;
-                float v[4];
-                unpack2(acc2[2 * g][j], v[0], v[1]);
-                unpack2(acc2[2 * g + 1][j], v[2], v[3]);
-                if (vec && row + 3 < M) {
-                    float4 r;
-                    r.x = al * v[0]; r.y = al * v[1]; r.z = al * v[2]; r.w = al * v[3];
-                    if (useC) {
-                        const float4 o = *reinterpret_cast<const float4*>(cc + row);
-                        r.x = fmaf(be, o.x, r.x); r.y = fmaf(be, o.y, r.y);
-                        r.z = fmaf(be, o.z, r.z); r.w = fmaf(be, o.w, r.w);
-                    }
-                    *reinterpret_cast<float4*>(cc + row) = r;
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        if (row + e < M && !(TRI && tri_masked(trimode, row + e, col))) {
-                            float r = al * v[e];
-                            if (useC) r = fmaf(be, cc[row + e], r);
-                            cc[row + e] = r;
-                        }
-                    }
-                }
-            }
-        }
+        t16_epilogue<TRI, 0, 4>(acc2, D, ldd, al, be, trimode, m0, n0, M, N, tx, ty);
     };
     if (splits <= 1) {
         epilogue(C, ldc, alpha, beta, tri);
@@ -682,14 +700,14 @@ Plan choose_plan_8x8(size_t tiles, size_t K, size_t sms, size_t per_sm, bool may
 // ---------------------------------------------------------------------------------------------
 // Stream-K form of the 8 x 8 kernel for products of a few waves: all K slabs of all 128 x 128 tiles are one sequence
 // of units, cut into equal consecutive shares, one per CTA of a grid that exactly fills the machine (two CTAs per SM;
-// one when A is K-contiguous).  With one CTA per tile the last round of CTAs is as long as the others however few
-// tiles it holds (256 tiles on 296 slots: two rounds of time for 1.73 rounds of work, and SMs left with one CTA run
-// below their paired rate); here every CTA works the same number of slabs and all finish together.  A CTA whose
-// share covers a whole tile writes C directly; otherwise it stores its partial tile in its slot of a workspace and
-// draws a ticket from the tile's counter, and the CTA that draws the last ticket adds the slots in slot order -- a fixed
-// order, so the result does not depend on who finishes last -- applies alpha and beta and writes C.  Nobody waits for
-// anybody: no spin loop besides the bounded mbarrier waits of the TMA ring.  (The FP64 kernel does the same for the
-// tail of its grid, dgemm_mma_tma.cu.)
+// one when A is K-contiguous or the shares would be short).  With one CTA per tile the last round of CTAs is as long
+// as the others however few tiles it holds (256 tiles on 296 slots: two rounds of time for 1.73 rounds of work, and SMs
+// left with one CTA run below their paired rate); here every CTA works the same number of slabs and all finish
+// together.  A CTA whose share covers a whole tile writes C directly; otherwise it stores its partial tile in its slot
+// of a workspace and draws a ticket from the tile's counter, and the CTA that draws the last ticket adds the slots in
+// slot order -- a fixed order, so the result does not depend on who finishes last -- applies alpha and beta and writes
+// C.  Nobody waits for anybody: no spin loop besides the bounded mbarrier waits of the TMA ring.  (The FP64 kernel does
+// the same for the tail of its grid, dgemm_mma_tma.cu.)
 __device__ __forceinline__ void sk_tile_coords(unsigned tile, unsigned tilesM, unsigned tilesN, unsigned& tm, unsigned& tn)
 {
     const unsigned per_group = GROUP_M * tilesN;
@@ -947,7 +965,218 @@ sgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Stream-K with the 16 x 8 register tile on eight-warp CTAs, one CTA per SM, both operands M/N-contiguous.
+//
+// The 16 x 8 tile needs the 255-register budget, i.e. at most eight warps per SM; as two four-warp CTAs per SM (the
+// kernel above) that only pays with many rounds of CTAs.  Here one CTA holds all eight warps: warps 0-3 take k rows
+// 0-15 of every slab, warps 4-7 rows 16-31, each group with the full 128 x 128 tile in registers.  At the end of a
+// segment (this CTA's run of slabs of one tile) the groups swap halves through shared memory -- group 0 keeps row groups
+// 0-1 and receives group 1's sums for them, group 1 keeps row groups 2-3 -- and each finishes its half: straight to C
+// when the segment is the whole tile, else to the CTA's slot of the workspace, ticket, and the CTA that draws the last
+// ticket adds the slots in slot order (a fixed order) and writes C.  Nobody waits for anybody.
+constexpr int T16W_THREADS = 256;
+constexpr int T16W_STAGES = 4;
+constexpr int T16W_RED_BYTES = 64 * 128 * 8;         // the halves the two groups hand each other
+constexpr int T16W_SMEM = T16W_STAGES * T16_STAGE_BYTES + T16W_RED_BYTES + 1024 + 256;
+constexpr size_t T16W_MIN_UNITS = 8;                  // smallest share of a CTA, in K slabs of 32
+
+__global__ void __launch_bounds__(T16W_THREADS, 1)
+sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                              float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
+                              unsigned tilesM, unsigned tilesN, unsigned units, unsigned upc, unsigned maxc,
+                              unsigned long long* __restrict__ ws, unsigned* __restrict__ counters)
+{
+    __shared__ unsigned s_ticket;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned long long* red = reinterpret_cast<unsigned long long*>(smem + T16W_STAGES * T16_STAGE_BYTES);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + T16W_STAGES * T16_STAGE_BYTES + T16W_RED_BYTES);
+    uint64_t* empty = full + T16W_STAGES;
+    pdl_launch_dependents();
+
+    const unsigned nk = (unsigned)((K + BK - 1) / BK);
+    const unsigned u0 = blockIdx.x * upc, u1 = min(u0 + upc, units);
+    if (u0 >= u1) return;
+    const unsigned count_local = u1 - u0;
+    const int lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T16W_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], T16W_THREADS / 32);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_wait();
+
+    // unit i of this CTA = K slab (u0 + i) % nk of tile (u0 + i) / nk
+    auto issue = [&](unsigned i) {
+        const unsigned u = u0 + i, t = u / nk, kt = u - t * nk;
+        unsigned tm, tn;
+        sk_tile_coords(t, tilesM, tilesN, tm, tn);
+        const int s = (int)(i % T16W_STAGES);
+        unsigned char* sa = smem + s * T16_STAGE_BYTES;
+        unsigned char* sb = sa + A_BYTES;
+        mbar_expect_tx(&full[s], T16_STAGE_BYTES);
+        tma_load_2d(sa, &mapA, (int)(tm * BM), (int)(kt * BK), &full[s]);
+        tma_load_2d(sb, &mapB, (int)(tn * 128), (int)(kt * BK), &full[s]);
+    };
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&mapA);
+        tma_prefetch_descriptor(&mapB);
+        for (unsigned i = 0; i < (unsigned)(T16W_STAGES - 1) && i < count_local; i++) issue(i);
+    }
+
+    const int tid = threadIdx.x, grp = tid / 128, tg = tid % 128, tx = tg % 8, ty = tg / 8;
+    unsigned long long acc2[8][8];
+    auto clear = [&]() {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc2[i][j] = 0ull;
+    };
+    clear();
+
+    const int offA = grp * (16 * 512) + tx * 16, offB = A_BYTES + grp * (16 * 512) + ty * 16;
+    const unsigned long long ones = pack2(1.f, 1.f);
+    bool alive = true;
+    unsigned i = 0;
+    while (i < count_local) {
+        const unsigned t = (u0 + i) / nk, seg_first = (u0 + i) - t * nk;
+        const unsigned seg_end = min(u1, (t + 1) * nk) - u0;              // one past the last local unit of this segment
+        for (; i < seg_end; i++) {
+            const int s = (int)(i % T16W_STAGES);
+            if (!mbar_wait(&full[s], (i / T16W_STAGES) & 1)) return;      // flagged; this tile stays unwritten
+            const unsigned char* sa = smem + s * T16_STAGE_BYTES + offA;
+            const unsigned char* sb = smem + s * T16_STAGE_BYTES + offB;
+            // the slot freed one slab earlier is refilled in the second half of this one, by a different warp every slab
+            t16_rows<2, 1>(sa, sb, acc2, [&] {
+                if (threadIdx.x == 32 * (i & 7) && i + T16W_STAGES - 1 < count_local) {
+                    if (i >= 1) alive = mbar_wait(&empty[(i - 1) % T16W_STAGES], ((i - 1) / T16W_STAGES) & 1);
+                    if (alive) issue(i + T16W_STAGES - 1);
+                }
+            });
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+
+        // ---- end of this CTA's segment [seg_first, seg_last] of tile t: the groups swap halves ...
+        {
+            unsigned long long* out = red + (size_t)(grp * 32) * 128 + tg;
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) out[(r * 8 + j) * 128] = grp == 0 ? acc2[4 + r][j] : acc2[r][j];
+        }
+        __syncthreads();
+        {
+            const unsigned long long* in = red + (size_t)((1 - grp) * 32) * 128 + tg;
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const unsigned long long v = in[(r * 8 + j) * 128];
+                    if (grp == 0) acc2[r][j] = ffma2(v, ones, acc2[r][j]);            // x * 1 + acc: an exact addition
+                    else acc2[4 + r][j] = ffma2(v, ones, acc2[4 + r][j]);
+                }
+        }
+        // ... and each finishes its own: acc2[0..3] (row groups 0-1) in group 0, acc2[4..7] (row groups 2-3) in group 1
+        const unsigned seg_last = (u0 + seg_end - 1) - t * nk;
+        unsigned tm, tn;
+        sk_tile_coords(t, tilesM, tilesN, tm, tn);
+        const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * 128;
+        bool write_c = true;
+        if (!(seg_first == 0 && seg_last == nk - 1)) {
+            const unsigned first_cta = (t * nk) / upc;
+            const unsigned idx = blockIdx.x - first_cta;
+            const unsigned count = ((t + 1) * nk - 1) / upc - first_cta + 1;
+            unsigned long long* slot = ws + ((size_t)t * maxc + idx) * (size_t)(32 * T16W_THREADS);
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) __stcg(slot + (r * 8 + j) * T16W_THREADS + tid, grp == 0 ? acc2[r][j] : acc2[4 + r][j]);
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) s_ticket = atomicAdd(&counters[t], 1u);
+            __syncthreads();
+            write_c = (s_ticket == count - 1);
+            if (write_c) {
+                __threadfence();
+                const unsigned long long* base = ws + (size_t)t * maxc * (size_t)(32 * T16W_THREADS) + tid;
+                unsigned long long sum[4][8];
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) sum[r][j] = 0ull;
+                for (unsigned c = 0; c < count; c++) {
+                    const unsigned long long* sl = base + (size_t)c * (32 * T16W_THREADS);
+                    unsigned long long v[4][8];               // thirty-two independent loads in flight
+#pragma unroll
+                    for (int r = 0; r < 4; r++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) v[r][j] = __ldcg(sl + (r * 8 + j) * T16W_THREADS);
+#pragma unroll
+                    for (int r = 0; r < 4; r++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) sum[r][j] = ffma2(v[r][j], ones, sum[r][j]);
+                }
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        if (grp == 0) acc2[r][j] = sum[r][j]; else acc2[4 + r][j] = sum[r][j];
+                    }
+            }
+        }
+        if (write_c) {
+            if (grp == 0) t16_epilogue<false, 0, 2>(acc2, C, ldc, alpha, beta, TRI_FULL, m0, n0, M, N, tx, ty);
+            else t16_epilogue<false, 2, 4>(acc2, C, ldc, alpha, beta, TRI_FULL, m0, n0, M, N, tx, ty);
+        }
+        __syncthreads();                                      // the exchange buffer and s_ticket are reused by the next segment
+        clear();
+    }
+}
+
+cudaError_t launch_nt_16x8w_streamk(const GemmProblem<float>& p, cudaStream_t s)
+{
+    void* enc = get_tensor_map_encoder();
+    CUtensorMap mapA, mapB;
+    if (!make_tensor_map_2d(&mapA, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.A, p.M, p.K, p.lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return cudaErrorNotSupported;
+    if (!make_tensor_map_2d(&mapB, enc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.N, p.K, p.ldb, 128, BK, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return cudaErrorNotSupported;
+    static DeviceOnce once;
+    cudaError_t e = once.run([] {
+        return cudaFuncSetAttribute(sgemm_nt_16x8w_streamk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T16W_SMEM);
+    });
+    if (e != cudaSuccess) return e;
+    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128, tiles = tilesM * tilesN;
+    const size_t nk = (p.K + BK - 1) / BK, units = tiles * nk;
+    if (units >= (1ull << 31)) return cudaErrorNotSupported;
+    const size_t ctas = std::max<size_t>(1, std::min<size_t>((size_t)sm_count(), units / T16W_MIN_UNITS));
+    const size_t upc = (units + ctas - 1) / ctas;
+    const size_t maxc = (nk + upc - 1) / upc + 1;
+    const size_t ws_words = tiles * maxc * (size_t)(32 * T16W_THREADS);
+    unsigned long long* ws = nullptr;
+    e = ws_alloc(reinterpret_cast<void**>(&ws), ws_words * sizeof(unsigned long long) + tiles * sizeof(unsigned) + 256, s);
+    if (e != cudaSuccess) { cudaGetLastError(); return cudaErrorNotSupported; }     // the caller goes on to a kernel that needs no workspace
+    unsigned* counters = reinterpret_cast<unsigned*>(ws + ws_words);
+    e = cudaMemsetAsync(counters, 0, tiles * sizeof(unsigned), s);
+    if (e == cudaSuccess) {
+        set_last_variant("sgemm_nt_16x8w_streamk");
+        e = launch_pdl(sgemm_nt_16x8w_streamk_kernel, dim3((unsigned)((units + upc - 1) / upc)), dim3(T16W_THREADS), T16W_SMEM, s,
+                       mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)units,
+                       (unsigned)upc, (unsigned)maxc, ws, counters);
+        count_launch();
+    }
+    const cudaError_t e2 = ws_free(ws, s);
+    return e != cudaSuccess ? e : e2;
+}
+
 constexpr unsigned SK_MIN_UNITS = 4;         // smallest share of a CTA, in K slabs of 32
+constexpr unsigned SK_PAIR_MIN_UNITS = 20;   // smallest share for which two CTAs per SM beat one
 
 template <bool TA, bool TB, int STAGES, int MIN_CTAS>
 cudaError_t launch_streamk(const GemmProblem<float>& p, cudaStream_t s)
@@ -970,7 +1199,11 @@ cudaError_t launch_streamk(const GemmProblem<float>& p, cudaStream_t s)
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128, tiles = tilesM * tilesN;
     const size_t nk = (p.K + BK - 1) / BK, units = tiles * nk;
     if (units >= (1ull << 31)) return cudaErrorNotSupported;
-    const size_t slots = (size_t)sm_count() * MIN_CTAS;
+    // Two CTAs per SM only when each still gets 20 slabs: shorter shares are mostly fixed cost (pipeline fill, partial-tile
+    // store, reduction), and one CTA per SM with a share twice as long wins (N/T, TFLOP/s, one / two per SM: 1152^3 38.1 /
+    // 36.2, 1280^3 41.5 / 37.3, 1408^3 45.6 / 44.6, but 1536^3 47.9 / 48.4, 2048^3 51.7 / 52.0).
+    size_t slots = (size_t)sm_count() * MIN_CTAS;
+    if (MIN_CTAS > 1 && units < slots * SK_PAIR_MIN_UNITS) slots = (size_t)sm_count();
     const size_t ctas = std::max<size_t>(1, std::min<size_t>(slots, units / SK_MIN_UNITS));
     const size_t upc = (units + ctas - 1) / ctas;
     const size_t maxc = (nk + upc - 1) / upc + 1;
@@ -1036,11 +1269,13 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     if (forced == PATH_TMA_ONE_CTA) return launch_any<128, 5, 1>(p, s);
     if (forced == PATH_TMA_TWO_CTAS) return launch_any<128, 3, 2>(p, s);
     const bool may_split = gemm_may_allocate() && p.C != p.A && p.C != p.B && getenv("CLBLAS_B200_NO_SPLITK") == nullptr;
-    // Tuning aid: CLBLAS_B200_SGEMM_FORCE="<tile>,<splits>" with tile 64 / 128 (8 x 8 register-tile kernel), 16 (16 x 8) or 1 (stream-K).
+    // Tuning aid: CLBLAS_B200_SGEMM_FORCE="<tile>,<splits>" with tile 64 / 128 (8 x 8 register-tile kernel), 16 (16 x 8), 18 (16 x 8 on
+    // eight-warp CTAs, stream-K) or 1 (8 x 8 stream-K).
     if (const char* f = getenv("CLBLAS_B200_SGEMM_FORCE")) {
         int tile = 0, sp = 1;
         if (sscanf(f, "%d,%d", &tile, &sp) >= 1 && may_split && p.tri == TRI_FULL && min_bn < 128 && sp >= 1 && sp <= 8) {
             if (tile == 16 && !p.ta && p.tb) return launch_nt_16x8<false>(p, s, (unsigned)sp);
+            if (tile == 18 && !p.ta && p.tb) { const cudaError_t e = launch_nt_16x8w_streamk(p, s); if (e != cudaErrorNotSupported) return e; }
             if (tile == 1) { const cudaError_t e = launch_streamk_any(p, s); if (e != cudaErrorNotSupported) return e; }     // "1,0": stream-K
             if (tile == 64) return p.ta ? launch_any<64, 5, 1>(p, s, (unsigned)sp) : launch_any<64, 3, 2>(p, s, (unsigned)sp);
             if (tile == 128) return p.ta ? launch_any<128, 5, 1>(p, s, (unsigned)sp) : launch_any<128, 3, 2>(p, s, (unsigned)sp);
@@ -1053,6 +1288,20 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     const bool k8x8 = getenv("CLBLAS_B200_SGEMM_8X8") != nullptr;
     const bool big_nt = !p.ta && p.tb && min_bn < 128 && tiles128 >= (size_t)sm_count() * 4 && p.K >= 1024 && !k8x8;
     if (big_nt && p.tri != TRI_FULL) return launch_nt_16x8<true>(p, s);
+    // N/T products of up to sixteen tiles per SM with a K loop of at least 36 slabs: the eight-warp 16 x 8 stream-K kernel.
+    // Measured against the choices below (TFLOP/s, this kernel / the best of the others): 1152^3 38.9 / 38.0, 1408^3 47.6 /
+    // 45.5, 2048^3 55.2 / 51.1, 2560^3 58.0 / 54.3, 3072^3 59.8 / 57.5, 4096^3 61.4 / 58.9, 5120^3 62.1 / 61.0, 6144^3 62.6 /
+    // 62.2, 1024 x 1024 x 8192 57.3 / 52.7, 768 x 768 x 2048 37.7 / 32.7; but 8192^3 62.8 / 63.5, and with short K loops its
+    // exposed epilogue (one CTA per SM: nothing else runs meanwhile) loses: 1024^3 33.5 / 33.4, 4096 x 4096 x 1024 53.3 /
+    // 53.9, 8192 x 8192 x 1024 54.7 / 58.3, 4096 x 4096 x 256 36.0 / 51.4.
+    {
+        const size_t nk = (p.K + BK - 1) / BK, sms = (size_t)sm_count();
+        if (!p.ta && p.tb && p.tri == TRI_FULL && min_bn < 128 && may_split && nk >= 36 && tiles128 <= sms * 16 &&
+            tiles128 * nk >= sms * T16W_MIN_UNITS && getenv("CLBLAS_B200_NO_STREAMK") == nullptr && !k8x8) {
+            const cudaError_t e = launch_nt_16x8w_streamk(p, s);
+            if (e != cudaErrorNotSupported) return e;
+        }
+    }
     // Between about half a wave and twelve waves the 8 x 8 kernel's rounds may come out uneven: split K or go
     // stream-K where the model says so (choose_plan_8x8).
     if (p.tri == TRI_FULL && min_bn < 128 && p.K >= 256 && tiles128 >= 64 && tiles128 < (size_t)sm_count() * 12) {
