@@ -1296,7 +1296,10 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     // 53.9, 8192 x 8192 x 1024 54.7 / 58.3, 4096 x 4096 x 256 36.0 / 51.4.
     {
         const size_t nk = (p.K + BK - 1) / BK, sms = (size_t)sm_count();
-        if (!p.ta && p.tb && p.tri == TRI_FULL && min_bn < 128 && may_split && nk >= 36 && tiles128 <= sms * 16 &&
+        // (C must allow 16-byte accesses: the element-wise epilogue is exposed too -- the ragged row-major product with
+        // C at an offset of 5 elements ran at 47.2 against 49.1 TFLOP/s with K in two.)
+        const bool c_vec = (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && p.ldc % 4 == 0;
+        if (!p.ta && p.tb && p.tri == TRI_FULL && min_bn < 128 && may_split && nk >= 36 && tiles128 <= sms * 16 && c_vec &&
             tiles128 * nk >= sms * T16W_MIN_UNITS && getenv("CLBLAS_B200_NO_STREAMK") == nullptr && !k8x8) {
             const cudaError_t e = launch_nt_16x8w_streamk(p, s);
             if (e != cudaErrorNotSupported) return e;
