@@ -984,7 +984,7 @@ constexpr size_t T16W_MIN_UNITS = 8;                  // smallest share of a CTA
 __global__ void __launch_bounds__(T16W_THREADS, 1)
 sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                               float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                              unsigned tilesM, unsigned tilesN, unsigned units, unsigned upc, unsigned maxc,
+                              unsigned tilesM, unsigned tilesN, unsigned units, unsigned upc,
                               unsigned long long* __restrict__ ws, unsigned* __restrict__ counters)
 {
     __shared__ unsigned s_ticket;
@@ -1046,6 +1046,7 @@ sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __
     while (i < count_local) {
         const unsigned t = (u0 + i) / nk, seg_first = (u0 + i) - t * nk;
         const unsigned seg_end = min(u1, (t + 1) * nk) - u0;              // one past the last local unit of this segment
+        const bool first_seg = (i == 0);
         for (; i < seg_end; i++) {
             const int s = (int)(i % T16W_STAGES);
             if (!mbar_wait(&full[s], (i / T16W_STAGES) & 1)) return;      // flagged; this tile stays unwritten
@@ -1089,10 +1090,11 @@ sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __
         const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * 128;
         bool write_c = true;
         if (!(seg_first == 0 && seg_last == nk - 1)) {
+            // Two slots per CTA: a partial tile is either the CTA's first segment (slot 0) or, begun at a tile boundary and
+            // cut short by the end of the share, its last (slot 1); whole tiles in between need none.
             const unsigned first_cta = (t * nk) / upc;
-            const unsigned idx = blockIdx.x - first_cta;
             const unsigned count = ((t + 1) * nk - 1) / upc - first_cta + 1;
-            unsigned long long* slot = ws + ((size_t)t * maxc + idx) * (size_t)(32 * T16W_THREADS);
+            unsigned long long* slot = ws + ((size_t)blockIdx.x * 2 + (first_seg ? 0 : 1)) * (size_t)(32 * T16W_THREADS);
 #pragma unroll
             for (int r = 0; r < 4; r++)
 #pragma unroll
@@ -1104,14 +1106,14 @@ sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __
             write_c = (s_ticket == count - 1);
             if (write_c) {
                 __threadfence();
-                const unsigned long long* base = ws + (size_t)t * maxc * (size_t)(32 * T16W_THREADS) + tid;
                 unsigned long long sum[4][8];
 #pragma unroll
                 for (int r = 0; r < 4; r++)
 #pragma unroll
                     for (int j = 0; j < 8; j++) sum[r][j] = 0ull;
-                for (unsigned c = 0; c < count; c++) {
-                    const unsigned long long* sl = base + (size_t)c * (32 * T16W_THREADS);
+                for (unsigned c = first_cta; c < first_cta + count; c++) {
+                    // CTA c's part of this tile is its first segment if its share starts inside the tile
+                    const unsigned long long* sl = ws + ((size_t)c * 2 + (c * upc >= t * nk ? 0 : 1)) * (size_t)(32 * T16W_THREADS) + tid;
                     unsigned long long v[4][8];               // thirty-two independent loads in flight
 #pragma unroll
                     for (int r = 0; r < 4; r++)
@@ -1156,9 +1158,8 @@ cudaError_t launch_nt_16x8w_streamk(const GemmProblem<float>& p, cudaStream_t s)
     const size_t nk = (p.K + BK - 1) / BK, units = tiles * nk;
     if (units >= (1ull << 31)) return cudaErrorNotSupported;
     const size_t ctas = std::max<size_t>(1, std::min<size_t>((size_t)sm_count(), units / T16W_MIN_UNITS));
-    const size_t upc = (units + ctas - 1) / ctas;
-    const size_t maxc = (nk + upc - 1) / upc + 1;
-    const size_t ws_words = tiles * maxc * (size_t)(32 * T16W_THREADS);
+    const size_t upc = (units + ctas - 1) / ctas, grid = (units + upc - 1) / upc;
+    const size_t ws_words = grid * 2 * (size_t)(32 * T16W_THREADS);               // two partial-tile slots per CTA
     unsigned long long* ws = nullptr;
     e = ws_alloc(reinterpret_cast<void**>(&ws), ws_words * sizeof(unsigned long long) + tiles * sizeof(unsigned) + 256, s);
     if (e != cudaSuccess) { cudaGetLastError(); return cudaErrorNotSupported; }     // the caller goes on to a kernel that needs no workspace
@@ -1166,9 +1167,9 @@ cudaError_t launch_nt_16x8w_streamk(const GemmProblem<float>& p, cudaStream_t s)
     e = cudaMemsetAsync(counters, 0, tiles * sizeof(unsigned), s);
     if (e == cudaSuccess) {
         set_last_variant("sgemm_nt_16x8w_streamk");
-        e = launch_pdl(sgemm_nt_16x8w_streamk_kernel, dim3((unsigned)((units + upc - 1) / upc)), dim3(T16W_THREADS), T16W_SMEM, s,
+        e = launch_pdl(sgemm_nt_16x8w_streamk_kernel, dim3((unsigned)grid), dim3(T16W_THREADS), T16W_SMEM, s,
                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)units,
-                       (unsigned)upc, (unsigned)maxc, ws, counters);
+                       (unsigned)upc, ws, counters);
         count_launch();
     }
     const cudaError_t e2 = ws_free(ws, s);

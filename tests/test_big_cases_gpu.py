@@ -156,7 +156,9 @@ def test_sgemm_eight_warp_16x8_stream_k_is_exact_and_deterministic(lib):
     call that maps onto it) and bit-identical when repeated."""
     name = "sgemm_nt_16x8w_streamk"
     assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1280, 1280, 1280, seed=8050) == name
-    assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1397, 1401, 1413, alpha=-1.0, beta=0.0, pad=(3, 3, 0), seed=8051) == name
+    assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1397, 1401, 1413, alpha=-1.0, beta=0.0, pad=(3, 3, 3), seed=8051) == name
+    # a C that does not allow 16-byte accesses stays with the two-CTAs-per-SM kernels
+    assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1397, 1401, 1413, pad=(3, 3, 0), seed=8056) != name
     assert _exact_gemm(lib, "s", RowMajor, Trans, NoTrans, 2200, 2056, 1153, seed=8052) == name
     assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 300, 200, 8000, seed=8053) == name             # six tiles, 250 slabs
     assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3584, 3584, 1536, seed=8054) == name           # 784 tiles
