@@ -403,17 +403,22 @@ static int run_sharded(const Options& o)
         const size_t am = trsm ? o.M : (o.transA ? o.K : o.M), an = trsm ? o.M : (o.transA ? o.M : o.K);      // A as stored
         const size_t lda = am, ldb = trsm ? o.M : (o.transB ? std::max<size_t>(nl, 1) : o.K), ldc = o.M;
         const size_t nbel = trsm ? o.M * std::max<size_t>(nl, 1) : (o.transB ? ldb * o.K : o.K * std::max<size_t>(nl, 1));
-        std::vector<T> hA(am * an), hB(nbel);
-        std::srand(10 + r);
-        auto rnd = [] { return (T)((std::rand() % 20) - 10) / (T)10; };
-        if (trsm) { std::fill(hA.begin(), hA.end(), (T)0); for (size_t i = 0; i < o.M; i++) hA[i + i * lda] = (T)(1 + (std::rand() % 4)); }
-        else for (auto& v : hA) v = rnd();
+        // Only the root holds A on the host; a generator of its own per thread (std::rand serialises the threads on a lock,
+        // which made the set-up of a 32768^2 problem take minutes).
+        std::vector<T> hA(r == 0 ? am * an : 0), hB(nbel);
+        unsigned long long lcg = 0x9E3779B97F4A7C15ull * (unsigned long long)(11 + r);
+        auto next = [&lcg] { lcg = lcg * 6364136223846793005ull + 1442695040888963407ull; return (unsigned)(lcg >> 40); };
+        auto rnd = [&next] { return (T)((int)(next() % 20) - 10) / (T)10; };
+        if (r == 0) {
+            if (trsm) { std::fill(hA.begin(), hA.end(), (T)0); for (size_t i = 0; i < o.M; i++) hA[i + i * lda] = (T)(1 + (next() % 4)); }
+            else for (auto& v : hA) v = rnd();
+        }
         for (auto& v : hB) v = rnd();
         T *dA, *dB, *dC = nullptr;
-        CUDA_OK(cudaMalloc(&dA, hA.size() * sizeof(T)));
+        CUDA_OK(cudaMalloc(&dA, am * an * sizeof(T)));
         CUDA_OK(cudaMalloc(&dB, hB.size() * sizeof(T)));
         if (r == 0) CUDA_OK(cudaMemcpy(dA, hA.data(), hA.size() * sizeof(T), cudaMemcpyHostToDevice));
-        else CUDA_OK(cudaMemset(dA, 0xff, hA.size() * sizeof(T)));          // the broadcast has to fill it
+        else CUDA_OK(cudaMemset(dA, 0xff, am * an * sizeof(T)));            // the broadcast has to fill it
         CUDA_OK(cudaMemcpy(dB, hB.data(), hB.size() * sizeof(T), cudaMemcpyHostToDevice));
         if (!trsm) { CUDA_OK(cudaMalloc(&dC, o.M * std::max<size_t>(nl, 1) * sizeof(T))); CUDA_OK(cudaMemset(dC, 0, o.M * std::max<size_t>(nl, 1) * sizeof(T))); }
         cudaStream_t stream;

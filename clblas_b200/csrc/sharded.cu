@@ -16,7 +16,7 @@
 //    transA = T a panel is a block of rows of C.  For TRSM the blocked solve itself waits for the panels
 //    (TrsmPanelGate): each step needs only the columns of A up to where the substitution has got.
 //    The first panel is small, so little of the broadcast is exposed (GEMM: later panels grow; TRSM:
-//    equal panels of 512 columns, because its early steps are short).
+//    equal panels of 2048 columns).
 //  * one process, several queues -- gemm_multi_queue, reached from clblasSgemm / clblasDgemm with
 //    numCommandQueues > 1: stripes of N as in the reference; a queue on another device gets copies of
 //    A and of its stripes of B and C (peer copies), computes there and copies its stripe of C back.
@@ -139,10 +139,12 @@ std::vector<size_t> growing_panels(size_t cols, size_t min_cols, size_t max_pane
     return b;
 }
 
-// Panels of the triangular matrix of a sharded solve: multiples of 512 columns, at most 32 panels.
+// Panels of the triangular matrix of a sharded solve: equal panels of 2048 columns (CLBLAS_B200_TRSM_PANEL_COLS changes
+// the width for measurements), wider only to keep their number at 32.
 std::vector<size_t> trsm_panel_bounds(size_t n)
 {
-    size_t w = 4 * kAlign;
+    static const size_t w0 = [] { const char* e = getenv("CLBLAS_B200_TRSM_PANEL_COLS"); const long v = e ? atol(e) : 0; return v >= (long)kAlign ? (size_t)v / kAlign * kAlign : 16 * kAlign; }();
+    size_t w = w0;
     while ((n + w - 1) / w > 32) w *= 2;
     std::vector<size_t> b{0};
     while (b.back() < n) b.push_back(std::min(n, b.back() + w));
@@ -231,11 +233,11 @@ cudaError_t trsm_sharded_colmajor(ShardComm* c, int root, bool right, bool lower
     // order -- a transposed A -- in which case that step waits for them; by then they have long arrived,
     // because the solve takes far longer than the broadcast).
     const bool ascending = ((lower != trans) != right);
-    // Equal panels of 512 columns (four diagonal blocks: what one step at the end of the solve's recursion reads), wider
-    // only to keep their number at 32.  The time the solve needs to reach column c grows like c^2 while the panels arrive
-    // at a constant rate, so the solve runs behind the broadcast for the first columns, as fast as the data comes in,
-    // and ahead of it from then on; with fine panels nothing else is lost (measured on 8 GPUs, 8192 x 2048 per rank:
-    // four growing panels 0.66 ms exposed of a 4.6 ms solve).
+    // Equal panels of 2048 columns, wider only to keep their number at 32.  The time the solve needs to reach column c
+    // grows like c^2 while the panels arrive at a constant rate, so what is exposed is the first panel and whatever
+    // the solve has to wait for the second; every further broadcast costs about 45 us of its own.  Measured on 2 GPUs,
+    // order 8192 with 8192 columns per rank, time per call above the 17.18 ms of the solve alone: panels of 512
+    // columns +1.22 ms, 1024 +0.81, 2048 +0.67, 4096 +0.66, one broadcast of everything +0.85.
     const std::vector<size_t> b = trsm_panel_bounds(n);
     const size_t np = b.size() - 1;
 
