@@ -965,6 +965,34 @@ sgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
 }
 
+// Triangular updates (SYRK, HERK): only the 128 x 128 tiles that touch the triangle are enumerated, column of tiles by
+// column of tiles.  Rows of tile column tn that take part: [lo, hi).
+__host__ __device__ inline void tri_column_rows(int tri, unsigned tilesM, unsigned tn, unsigned& lo, unsigned& hi)
+{
+    const int sh = (tri >> 2) & 1, kind = tri & 3;
+    const size_t n0 = (size_t)tn * 128;
+    lo = 0; hi = tilesM;
+    if (kind == TRI_LOWER) {            // tile row tm takes part when its last row, ((tm*128 + 127) >> sh), reaches column n0
+        const size_t first_row = n0 << sh;                       // first stored row that belongs to triangle row n0
+        lo = (unsigned)std::min<size_t>(tilesM, first_row >= 127 ? (first_row - 127 + 127) / 128 : 0);
+    } else if (kind == TRI_UPPER) {     // ... when its first row, ((tm*128) >> sh), is not beyond column n0 + 127
+        const size_t last_row = ((n0 + 128) << sh) - 1;          // last stored row that belongs to triangle row n0 + 127
+        hi = (unsigned)std::min<size_t>(tilesM, last_row / 128 + 1);
+    }
+}
+// tile number t of that enumeration -> (tm, tn)
+__device__ __forceinline__ void tri_tile_coords(int tri, unsigned t, unsigned tilesM, unsigned tilesN, unsigned& tm, unsigned& tn)
+{
+    unsigned before = 0;
+    for (unsigned c = 0; c < tilesN; c++) {
+        unsigned lo, hi;
+        tri_column_rows(tri, tilesM, c, lo, hi);
+        if (t < before + (hi - lo)) { tn = c; tm = lo + (t - before); return; }
+        before += hi - lo;
+    }
+    tn = tilesN - 1; tm = tilesM - 1;           // not reached: t is below the number of tiles the host counted
+}
+
 // ---------------------------------------------------------------------------------------------
 // Stream-K with the 16 x 8 register tile on eight-warp CTAs, one CTA per SM, both operands M/N-contiguous.
 //
@@ -981,13 +1009,15 @@ constexpr int T16W_RED_BYTES = 64 * 128 * 8;         // the halves the two group
 constexpr int T16W_SMEM = T16W_STAGES * T16_STAGE_BYTES + T16W_RED_BYTES + 1024 + 256;
 constexpr size_t T16W_MIN_UNITS = 8;                  // smallest share of a CTA, in K slabs of 32
 
+template <bool TRI>
 __global__ void __launch_bounds__(T16W_THREADS, 1)
 sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                               float* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, float alpha, float beta,
-                              unsigned tilesM, unsigned tilesN, unsigned units, unsigned upc,
+                              unsigned tilesM, unsigned tilesN, unsigned units, unsigned upc, int tri,
                               unsigned long long* __restrict__ ws, unsigned* __restrict__ counters)
 {
     __shared__ unsigned s_ticket;
+    __shared__ unsigned s_tile[3];             // TRI: the tile the producer looked up last, and its coordinates
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned long long* red = reinterpret_cast<unsigned long long*>(smem + T16W_STAGES * T16_STAGE_BYTES);
@@ -1007,15 +1037,27 @@ sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __
             mbar_init(&empty[s], T16W_THREADS / 32);
         }
         mbar_fence_init();
+        s_tile[0] = 0xffffffffu;
     }
     __syncthreads();
     pdl_wait();
 
+    auto tile_coords = [&](unsigned t, unsigned& tm, unsigned& tn) {
+        if (TRI) tri_tile_coords(tri, t, tilesM, tilesN, tm, tn);
+        else sk_tile_coords(t, tilesM, tilesN, tm, tn);
+    };
     // unit i of this CTA = K slab (u0 + i) % nk of tile (u0 + i) / nk
     auto issue = [&](unsigned i) {
         const unsigned u = u0 + i, t = u / nk, kt = u - t * nk;
         unsigned tm, tn;
-        sk_tile_coords(t, tilesM, tilesN, tm, tn);
+        if (TRI) {
+            // The look-up walks the tile columns; it is done once per tile and kept for the next K slabs.  The producers of
+            // consecutive slabs are different threads, ordered by the empty barrier each of them waits on first.
+            if (s_tile[0] != t) { tile_coords(t, tm, tn); s_tile[0] = t; s_tile[1] = tm; s_tile[2] = tn; }
+            else { tm = s_tile[1]; tn = s_tile[2]; }
+        } else {
+            tile_coords(t, tm, tn);
+        }
         const int s = (int)(i % T16W_STAGES);
         unsigned char* sa = smem + s * T16_STAGE_BYTES;
         unsigned char* sb = sa + A_BYTES;
@@ -1086,7 +1128,7 @@ sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __
         // ... and each finishes its own: acc2[0..3] (row groups 0-1) in group 0, acc2[4..7] (row groups 2-3) in group 1
         const unsigned seg_last = (u0 + seg_end - 1) - t * nk;
         unsigned tm, tn;
-        sk_tile_coords(t, tilesM, tilesN, tm, tn);
+        tile_coords(t, tm, tn);
         const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * 128;
         bool write_c = true;
         if (!(seg_first == 0 && seg_last == nk - 1)) {
@@ -1133,14 +1175,29 @@ sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __
             }
         }
         if (write_c) {
-            if (grp == 0) t16_epilogue<false, 0, 2>(acc2, C, ldc, alpha, beta, TRI_FULL, m0, n0, M, N, tx, ty);
-            else t16_epilogue<false, 2, 4>(acc2, C, ldc, alpha, beta, TRI_FULL, m0, n0, M, N, tx, ty);
+            const int trimode = TRI && !tri_tile_inside(tri, m0, BM, n0, 128) ? tri : TRI_FULL;     // tiles on the diagonal mask their stores
+            if (grp == 0) t16_epilogue<TRI, 0, 2>(acc2, C, ldc, alpha, beta, trimode, m0, n0, M, N, tx, ty);
+            else t16_epilogue<TRI, 2, 4>(acc2, C, ldc, alpha, beta, trimode, m0, n0, M, N, tx, ty);
         }
         __syncthreads();                                      // the exchange buffer and s_ticket are reused by the next segment
         clear();
     }
 }
 
+// Number of 128 x 128 tiles of an M x N matrix that touch the triangle `tri` (all of them for TRI_FULL).
+size_t tri_tile_count(int tri, size_t tilesM, size_t tilesN)
+{
+    if ((tri & 3) == TRI_FULL) return tilesM * tilesN;
+    size_t n = 0;
+    for (size_t c = 0; c < tilesN; c++) {
+        unsigned lo, hi;
+        tri_column_rows(tri, (unsigned)tilesM, (unsigned)c, lo, hi);
+        n += hi - lo;
+    }
+    return n;
+}
+
+template <bool TRI>
 cudaError_t launch_nt_16x8w_streamk(const GemmProblem<float>& p, cudaStream_t s)
 {
     void* enc = get_tensor_map_encoder();
@@ -1151,10 +1208,11 @@ cudaError_t launch_nt_16x8w_streamk(const GemmProblem<float>& p, cudaStream_t s)
         return cudaErrorNotSupported;
     static DeviceOnce once;
     cudaError_t e = once.run([] {
-        return cudaFuncSetAttribute(sgemm_nt_16x8w_streamk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T16W_SMEM);
+        return cudaFuncSetAttribute(sgemm_nt_16x8w_streamk_kernel<TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, T16W_SMEM);
     });
     if (e != cudaSuccess) return e;
-    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128, tiles = tilesM * tilesN;
+    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128, tiles = tri_tile_count(TRI ? p.tri : TRI_FULL, tilesM, tilesN);
+    if (tiles == 0) return cudaSuccess;
     const size_t nk = (p.K + BK - 1) / BK, units = tiles * nk;
     if (units >= (1ull << 31)) return cudaErrorNotSupported;
     const size_t ctas = std::max<size_t>(1, std::min<size_t>((size_t)sm_count(), units / T16W_MIN_UNITS));
@@ -1166,10 +1224,10 @@ cudaError_t launch_nt_16x8w_streamk(const GemmProblem<float>& p, cudaStream_t s)
     unsigned* counters = reinterpret_cast<unsigned*>(ws + ws_words);
     e = cudaMemsetAsync(counters, 0, tiles * sizeof(unsigned), s);
     if (e == cudaSuccess) {
-        set_last_variant("sgemm_nt_16x8w_streamk");
-        e = launch_pdl(sgemm_nt_16x8w_streamk_kernel, dim3((unsigned)grid), dim3(T16W_THREADS), T16W_SMEM, s,
+        set_last_variant(TRI ? "sgemm_nt_16x8w_streamk+tri" : "sgemm_nt_16x8w_streamk");
+        e = launch_pdl(sgemm_nt_16x8w_streamk_kernel<TRI>, dim3((unsigned)grid), dim3(T16W_THREADS), T16W_SMEM, s,
                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN, (unsigned)units,
-                       (unsigned)upc, ws, counters);
+                       (unsigned)upc, p.tri, ws, counters);
         count_launch();
     }
     const cudaError_t e2 = ws_free(ws, s);
@@ -1276,7 +1334,7 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
         int tile = 0, sp = 1;
         if (sscanf(f, "%d,%d", &tile, &sp) >= 1 && may_split && p.tri == TRI_FULL && min_bn < 128 && sp >= 1 && sp <= 8) {
             if (tile == 16 && !p.ta && p.tb) return launch_nt_16x8<false>(p, s, (unsigned)sp);
-            if (tile == 18 && !p.ta && p.tb) { const cudaError_t e = launch_nt_16x8w_streamk(p, s); if (e != cudaErrorNotSupported) return e; }
+            if (tile == 18 && !p.ta && p.tb) { const cudaError_t e = launch_nt_16x8w_streamk<false>(p, s); if (e != cudaErrorNotSupported) return e; }
             if (tile == 1) { const cudaError_t e = launch_streamk_any(p, s); if (e != cudaErrorNotSupported) return e; }     // "1,0": stream-K
             if (tile == 64) return p.ta ? launch_any<64, 5, 1>(p, s, (unsigned)sp) : launch_any<64, 3, 2>(p, s, (unsigned)sp);
             if (tile == 128) return p.ta ? launch_any<128, 5, 1>(p, s, (unsigned)sp) : launch_any<128, 3, 2>(p, s, (unsigned)sp);
@@ -1288,6 +1346,18 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     // and 4096 x 4096 x 512 48.7 vs 53.9 TFLOP/s.  From four waves on it takes the unsplit N/T products.
     const bool k8x8 = getenv("CLBLAS_B200_SGEMM_8X8") != nullptr;
     const bool big_nt = !p.ta && p.tb && min_bn < 128 && tiles128 >= (size_t)sm_count() * 4 && p.K >= 1024 && !k8x8;
+    const bool c_vec = (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && p.ldc % 4 == 0;
+    const bool share_k = may_split && getenv("CLBLAS_B200_NO_STREAMK") == nullptr && !k8x8;
+    // Triangular updates (SYRK, HERK) of N/T form with a K loop of at least 36 slabs: the eight-warp 16 x 8 stream-K kernel
+    // over the tiles that touch the triangle.  With one CTA per tile those tiles come in partly filled rounds (order 4096:
+    // 528 tiles on 296 slots).
+    if (!p.ta && p.tb && p.tri != TRI_FULL && min_bn < 128 && share_k && c_vec && (p.K + BK - 1) / BK >= 36) {
+        const size_t tt = tri_tile_count(p.tri, tilesM, (p.N + 127) / 128), nk = (p.K + BK - 1) / BK;
+        if (tt <= (size_t)sm_count() * 16 && tt * nk >= (size_t)sm_count() * T16W_MIN_UNITS) {
+            const cudaError_t e = launch_nt_16x8w_streamk<true>(p, s);
+            if (e != cudaErrorNotSupported) return e;
+        }
+    }
     if (big_nt && p.tri != TRI_FULL) return launch_nt_16x8<true>(p, s);
     // N/T products of up to sixteen tiles per SM with a K loop of at least 36 slabs: the eight-warp 16 x 8 stream-K kernel.
     // Measured against the choices below (TFLOP/s, this kernel / the best of the others): 1152^3 38.9 / 38.0, 1408^3 47.6 /
@@ -1299,10 +1369,9 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
         const size_t nk = (p.K + BK - 1) / BK, sms = (size_t)sm_count();
         // (C must allow 16-byte accesses: the element-wise epilogue is exposed too -- the ragged row-major product with
         // C at an offset of 5 elements ran at 47.2 against 49.1 TFLOP/s with K in two.)
-        const bool c_vec = (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && p.ldc % 4 == 0;
-        if (!p.ta && p.tb && p.tri == TRI_FULL && min_bn < 128 && may_split && nk >= 36 && tiles128 <= sms * 16 && c_vec &&
-            tiles128 * nk >= sms * T16W_MIN_UNITS && getenv("CLBLAS_B200_NO_STREAMK") == nullptr && !k8x8) {
-            const cudaError_t e = launch_nt_16x8w_streamk(p, s);
+        if (!p.ta && p.tb && p.tri == TRI_FULL && min_bn < 128 && share_k && nk >= 36 && tiles128 <= sms * 16 && c_vec &&
+            tiles128 * nk >= sms * T16W_MIN_UNITS) {
+            const cudaError_t e = launch_nt_16x8w_streamk<false>(p, s);
             if (e != cudaErrorNotSupported) return e;
         }
     }

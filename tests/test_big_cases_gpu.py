@@ -221,6 +221,52 @@ def test_triangular_16x8_kernel_through_ssyrk_and_cherk(lib):
     assert lib.device_fault() == 0
 
 
+@pytest.mark.parametrize("uplo", [Lower, Upper])
+def test_triangular_eight_warp_stream_k_through_ssyrk_and_cherk(lib, uplo):
+    """Rank-k updates with a K loop of 36 slabs or more: the eight-warp 16 x 8 stream-K kernel over the tiles that touch
+    the triangle (tiles on the diagonal mask their stores).  Exact on integer inputs, the other triangle untouched."""
+    n, k = 1920 + 77, 1184                     # 16 x 16 tiles with ragged edges, 136 of them in the triangle
+    ld = n + 3                                 # a leading dimension that still allows 16-byte accesses (2000)
+    g = oracle.rng(8060 + uplo, 0)
+    A = g.integers(-3, 4, (n, k)).astype(np.float32)
+    tri, other = (np.tril, np.triu_indices(n, 1)) if uplo == Lower else (np.triu, np.tril_indices(n, -1))
+    C = tri(g.integers(-3, 4, (n, n))).astype(np.float32)
+    Cb = np.full((ld, n), np.nan, np.float32, order="F")
+    Cb[:n] = C
+    Cb[:n][other] = np.nan                                                            # the other triangle must not be touched
+    Ab = np.zeros((ld, k), np.float32, order="F")
+    Ab[:n] = A
+    dA, dC = dev(Ab.ravel(order="F").copy()), dev(Cb.ravel(order="F").copy())
+    st = lib.clblasSsyrk(ColumnMajor, uplo, NoTrans, n, k, 2.0, dA, 0, ld, 3.0, dC, 0, ld)
+    torch.cuda.synchronize()
+    assert st == lib.clblasSuccess and lib.last_gemm_variant() == "sgemm_nt_16x8w_streamk+tri", lib.last_gemm_variant()
+    got = dC.cpu().numpy().reshape(n, ld).T
+    want = 2.0 * (A.astype(np.float64) @ A.astype(np.float64).T) + 3.0 * C
+    assert np.array_equal(tri(got[:n]), tri(want).astype(np.float32))
+    assert np.all(np.isnan(got[:n][other])) and np.all(np.isnan(got[n:]))
+
+    # CHERK: C <- alpha*A*A^H + beta*C, complex64; integer parts, exact (the real form pairs the rows of the triangle)
+    n, k = 1152, 640                           # K = 1280 in the real form
+    Ar, Ai = g.integers(-3, 4, (n, k)).astype(np.float64), g.integers(-3, 4, (n, k)).astype(np.float64)
+    Az = (Ar + 1j * Ai)
+    Cz = tri(g.integers(-3, 4, (n, n)) + 1j * g.integers(-3, 4, (n, n)))
+    Cz[np.diag_indices(n)] = Cz[np.diag_indices(n)].real
+    store = np.asfortranarray(Cz.astype(np.complex64))
+    other = np.triu_indices(n, 1) if uplo == Lower else np.tril_indices(n, -1)
+    store[other] = np.nan + 1j * np.nan
+    dA = dev(np.asfortranarray(Az.astype(np.complex64)).ravel(order="F").copy().view(np.float32))
+    dC = dev(store.ravel(order="F").copy().view(np.float32))
+    st = lib.clblasCherk(ColumnMajor, uplo, NoTrans, n, k, 2.0, dA, 0, n, -1.0, dC, 0, n)
+    torch.cuda.synchronize()
+    assert st == lib.clblasSuccess and lib.last_gemm_variant() == "sgemm_nt_16x8w_streamk+tri", lib.last_gemm_variant()
+    got = dC.cpu().numpy().view(np.complex64).reshape(n, n).T
+    want = 2.0 * (Az @ Az.conj().T) - Cz
+    keep = np.tril_indices(n) if uplo == Lower else np.triu_indices(n)
+    assert np.array_equal(got[keep], want[keep].astype(np.complex64))
+    assert np.all(np.isnan(got[other].real))
+    assert lib.device_fault() == 0
+
+
 @pytest.mark.parametrize("nq", [2, 3, 7])
 def test_gemm_over_several_queues_of_one_device(lib, nq):
     """numCommandQueues > 1: one stripe of N per queue, every queue's event recorded when its stripe is done."""
