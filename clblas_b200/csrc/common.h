@@ -55,6 +55,46 @@ __host__ __device__ inline bool tri_masked(int tri, size_t row, size_t col)
     return kind == TRI_LOWER ? r < col : kind == TRI_UPPER ? r > col : false;
 }
 
+// Triangular updates (SYRK, HERK) handed out stream-K fashion: only the 128 x 128 tiles that touch the triangle are
+// enumerated, column of tiles by column of tiles.  Rows of tile column tn that take part: [lo, hi).
+__host__ __device__ inline void tri_column_rows(int tri, unsigned tilesM, unsigned tn, unsigned& lo, unsigned& hi)
+{
+    const int sh = (tri >> 2) & 1, kind = tri & 3;
+    const size_t n0 = (size_t)tn * 128;
+    lo = 0; hi = tilesM;
+    if (kind == TRI_LOWER) {            // tile row tm takes part when its last row, (tm*128 + 127) >> sh, reaches column n0
+        const size_t lo_t = (n0 << sh) / 128;
+        lo = (unsigned)(lo_t < tilesM ? lo_t : tilesM);
+    } else if (kind == TRI_UPPER) {     // ... when its first row, (tm*128) >> sh, is not beyond column n0 + 127
+        const size_t hi_t = (((n0 + 128) << sh) - 1) / 128 + 1;
+        hi = (unsigned)(hi_t < tilesM ? hi_t : tilesM);
+    }
+}
+// tile number t of that enumeration -> (tm, tn)
+__host__ __device__ inline void tri_tile_coords(int tri, unsigned t, unsigned tilesM, unsigned tilesN, unsigned& tm, unsigned& tn)
+{
+    unsigned before = 0;
+    for (unsigned c = 0; c < tilesN; c++) {
+        unsigned lo, hi;
+        tri_column_rows(tri, tilesM, c, lo, hi);
+        if (t < before + (hi - lo)) { tn = c; tm = lo + (t - before); return; }
+        before += hi - lo;
+    }
+    tn = tilesN - 1; tm = tilesM - 1;           // not reached: t is below the number of tiles the host counted
+}
+// number of 128 x 128 tiles of a matrix of tilesM x tilesN tiles that touch the triangle (all of them for TRI_FULL)
+inline size_t tri_tile_count(int tri, size_t tilesM, size_t tilesN)
+{
+    if ((tri & 3) == TRI_FULL) return tilesM * tilesN;
+    size_t n = 0;
+    for (size_t c = 0; c < tilesN; c++) {
+        unsigned lo, hi;
+        tri_column_rows(tri, (unsigned)tilesM, (unsigned)c, lo, hi);
+        n += hi - lo;
+    }
+    return n;
+}
+
 // Kernel families (reported by clblasB200LastGemmKernel).
 enum GemmPath { PATH_AUTO = 0, PATH_SIMT_LDG = 1, PATH_TMA_ONE_CTA = 2, PATH_TMA_TWO_CTAS = 3, PATH_3XTF32 = 4 };
 

@@ -223,13 +223,19 @@ __device__ __forceinline__ void tile_coords(unsigned tile, unsigned tilesM, unsi
     tn = r / rows;
 }
 
-template <bool TA, bool TB>
+// TRI: a triangular update; the tiles are then those that touch the triangle, in the order of tri_tile_coords, and tiles
+// on the diagonal mask their stores.
+template <bool TA, bool TB, bool TRI>
 __global__ void __launch_bounds__(THREADS, 1)
 dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      double* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, double alpha, double beta,
                      unsigned tilesM, unsigned tilesN, unsigned tile0, unsigned units, unsigned upc, unsigned maxc,
-                     double* __restrict__ ws, unsigned* __restrict__ counters)
+                     double* __restrict__ ws, unsigned* __restrict__ counters, int tri)
 {
+    auto coords = [&](unsigned tile, unsigned& tm, unsigned& tn) {
+        if (TRI) tri_tile_coords(tri, tile, tilesM, tilesN, tm, tn);
+        else tile_coords(tile, tilesM, tilesN, tm, tn);
+    };
     constexpr int BN = 128;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -262,7 +268,7 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
             tma_prefetch_descriptor(&mapA);
             tma_prefetch_descriptor(&mapB);
             unsigned t = u0 / nk, kt = u0 % nk, tm, tn;
-            tile_coords(tile0 + t, tilesM, tilesN, tm, tn);
+            coords(tile0 + t, tm, tn);
             for (unsigned u = u0; u < u1; u++) {
                 const unsigned i = u - u0;
                 const int s = (int)(i % STAGES);
@@ -274,7 +280,7 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
                 const int k0 = (int)(kt * BK), m0 = (int)(tm * BM), n0 = (int)(tn * BN);
                 if (TA) tma_load_2d(sa, &mapA, k0, m0, &full[s]); else tma_load_2d(sa, &mapA, m0, k0, &full[s]);
                 if (TB) tma_load_2d(sb, &mapB, n0, k0, &full[s]); else tma_load_2d(sb, &mapB, k0, n0, &full[s]);
-                if (++kt == nk) { kt = 0; t++; if (u + 1 < u1) tile_coords(tile0 + t, tilesM, tilesN, tm, tn); }
+                if (++kt == nk) { kt = 0; t++; if (u + 1 < u1) coords(tile0 + t, tm, tn); }
             }
         }
         return;
@@ -301,6 +307,7 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     // C = alpha*acc + beta*C for the tile at (m0, n0); beta == 0 never reads C
     auto epilogue = [&](size_t m0, size_t n0) {
         const bool useC = (beta != 0.0);
+        const int trimode = TRI && !tri_tile_inside(tri, m0, BM, n0, BN) ? tri : TRI_FULL;
 #pragma unroll
         for (int ni = 0; ni < NI; ni++)
 #pragma unroll
@@ -313,6 +320,7 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
                 for (int mi = 0; mi < 8; mi++) {
                     const size_t row = m0 + wm * 64 + mi * 8 + (TA ? pg : g);
                     if (row >= M) continue;
+                    if (TRI && tri_masked(trimode, row, col)) continue;
                     double r = alpha * acc[mi][ni][e];
                     if (useC) r = fma(beta, cc[row], r);
                     cc[row] = r;
@@ -356,7 +364,7 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         // ---- end of this CTA's segment [seg_first, seg_last] of tile t
         const unsigned seg_last = seg_end - 1 - t * nk;
         unsigned tm, tn;
-        tile_coords(tile0 + t, tilesM, tilesN, tm, tn);
+        coords(tile0 + t, tm, tn);
         const size_t m0 = (size_t)tm * BM, n0 = (size_t)tn * BN;
         if (seg_first == 0 && seg_last == nk - 1) {
             epilogue(m0, n0);
@@ -421,21 +429,37 @@ cudaError_t prepare_main()
         return cudaFuncSetAttribute(dgemm_mma_tma_kernel<TA, TB, BN, TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN));
     });
 }
-template <bool TA, bool TB>
+template <bool TA, bool TB, bool TRI = false>
 cudaError_t prepare_streamk()
 {
     static DeviceOnce once;
     return once.run([] {
-        return cudaFuncSetAttribute(dgemm_streamk_kernel<TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128));
+        return cudaFuncSetAttribute(dgemm_streamk_kernel<TA, TB, TRI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128));
     });
 }
 
-// "dgemm_mma_tma<T,N,128>" (+ "+tri", "+streamk_tail"): the instantiation a call ran, for the tests.
+// A triangular update that the stream-K kernel should take whole: a last wave of one CTA per tile that would be less than
+// 85 % full, at least 12 K slabs per SM in all, at most 16 waves of tiles in the triangle.  DSYRK Lower/N n = k, TFLOP/s,
+// one CTA per tile -> stream-K: 1024 12.4 -> 15.5, 1536 16.0 -> 24.2, 2560 22.4 -> 28.9, 3072 21.9 -> 30.4, 4096 29.5 -> 32.1,
+// 5120 31.2 -> 33.0, 8192 32.6 -> 34.0; not 2048 (136 tiles, one nearly full wave: 28.6 against 27.7) nor 6144 (7.95 waves:
+// 33.9 against 33.5).
+constexpr size_t DGEMM_TRI_SK_MAX_WAVES = 16, DGEMM_TRI_SK_MIN_SLABS_PER_SM = 12;
+bool dgemm_tri_streamk_applies(const GemmProblem<double>& p)
+{
+    if (p.tri == TRI_FULL || !gemm_may_allocate() || p.C == p.A || p.C == p.B || getenv("CLBLAS_B200_NO_STREAMK") != nullptr) return false;
+    const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + 127) / 128, nk = (p.K + BK - 1) / BK, S = (size_t)sm_count();
+    const size_t T = tri_tile_count(p.tri, tilesM, tilesN), R = T % S;
+    if (R == 0 || R * 20 > S * 17) return false;                // the last wave of one CTA per tile is (nearly) full
+    return nk >= 2 * SK_MIN_SLABS && nk < (1u << 20) && T * nk >= S * DGEMM_TRI_SK_MIN_SLABS_PER_SM && T <= S * DGEMM_TRI_SK_MAX_WAVES &&
+           T * nk < (1ull << 31);
+}
+
+// "dgemm_mma_tma<T,N,128>" (+ "+tri", "+streamk_tail" / "+streamk"): the instantiation a call ran, for the tests.
 const char* variant_name(bool ta, bool tb, int bn, bool tri, bool streamk)
 {
     static thread_local char buf[64];
     snprintf(buf, sizeof(buf), "dgemm_mma_tma<%c,%c,%d>%s%s", ta ? 'T' : 'N', tb ? 'T' : 'N', bn, tri ? "+tri" : "",
-             streamk ? "+streamk_tail" : "");
+             !streamk ? "" : tri ? "+streamk" : "+streamk_tail");
     return buf;
 }
 
@@ -456,6 +480,33 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
     if (e0 != cudaSuccess) return e0;
     const size_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
     size_t main_tiles = tilesM * tilesN;
+    if (BN == 128 && TRI && dgemm_tri_streamk_applies(p)) {
+        // Triangular update: the tiles that touch the triangle, all of them through the stream-K kernel in equal shares.  With
+        // one CTA per tile they come in partly filled waves (order 3072: 300 tiles on 148 SMs, three waves for two of work).
+        const size_t T = tri_tile_count(p.tri, tilesM, tilesN), S = (size_t)sm_count(), nk = (p.K + BK - 1) / BK;
+        const size_t units = T * nk;
+        const size_t ctas = std::max<size_t>(1, std::min<size_t>(S, units / SK_MIN_SLABS));
+        const size_t upc = (units + ctas - 1) / ctas;
+        const size_t maxc = (nk + upc - 1) / upc + 1;
+        const size_t ws_doubles = T * maxc * (size_t)(BM * 128);
+        double* ws = nullptr;
+        cudaError_t e = ws_alloc(reinterpret_cast<void**>(&ws), ws_doubles * sizeof(double) + T * sizeof(unsigned) + 256, s);
+        if (e == cudaSuccess) {
+            unsigned* counters = reinterpret_cast<unsigned*>(ws + ws_doubles);
+            e = cudaMemsetAsync(counters, 0, T * sizeof(unsigned), s);
+            if (e == cudaSuccess) e = prepare_streamk<TA, TB, true>();
+            if (e == cudaSuccess) {
+                set_last_variant(variant_name(TA, TB, BN, true, true));
+                e = launch_pdl(dgemm_streamk_kernel<TA, TB, true>, dim3((unsigned)((units + upc - 1) / upc)), dim3(THREADS), smem_bytes(128), s,
+                               mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
+                               0u, (unsigned)units, (unsigned)upc, (unsigned)maxc, ws, counters, p.tri);
+                count_launch();
+            }
+            const cudaError_t e2 = ws_free(ws, s);
+            return e != cudaSuccess ? e : e2;
+        }
+        cudaGetLastError();        // no workspace: one CTA per tile as usual
+    }
     if (BN == 128 && !TRI) {
         // Whole waves go to the kernel above, the last partial wave to the stream-K kernel.  A product of fewer tiles than
         // SMs with a long K loop is one partial wave: all of it goes to the stream-K kernel, every SM working the same
@@ -476,7 +527,7 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
             if (e == cudaSuccess) {
                 unsigned* counters = reinterpret_cast<unsigned*>(ws + ws_doubles);
                 e = cudaMemsetAsync(counters, 0, R * sizeof(unsigned), s);
-                if (e == cudaSuccess) e = prepare_streamk<TA, TB>();
+                if (e == cudaSuccess) e = prepare_streamk<TA, TB, false>();
                 if (e == cudaSuccess) {
                     main_tiles = T - R;
                     set_last_variant(variant_name(TA, TB, BN, TRI, true));
@@ -486,9 +537,9 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
                         count_launch();
                     }
                     if (e == cudaSuccess) {
-                        e = launch_pdl(dgemm_streamk_kernel<TA, TB>, dim3((unsigned)((units + upc - 1) / upc)), dim3(THREADS), smem_bytes(128), s,
+                        e = launch_pdl(dgemm_streamk_kernel<TA, TB, false>, dim3((unsigned)((units + upc - 1) / upc)), dim3(THREADS), smem_bytes(128), s,
                                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
-                                       (unsigned)main_tiles, (unsigned)units, (unsigned)upc, (unsigned)maxc, ws, counters);
+                                       (unsigned)main_tiles, (unsigned)units, (unsigned)upc, (unsigned)maxc, ws, counters, 0);
                         count_launch();
                     }
                 }
@@ -554,7 +605,7 @@ cudaError_t launch_dgemm_mma_tma(const GemmProblem<double>& p, cudaStream_t s, i
     // (fewer 128-wide tiles than that but at least 40 K slabs per SM: still 128 wide, shared out by the stream-K kernel)
     const bool share_k = p.tri == TRI_FULL && tiles128 * nk >= (size_t)sm_count() * 40 && gemm_may_allocate() && p.C != p.A && p.C != p.B &&
                          getenv("CLBLAS_B200_NO_STREAMK") == nullptr;
-    if (min_bn >= 128 || tiles128 >= 120 || share_k) return launch_t<128>(p, s);
+    if (min_bn >= 128 || tiles128 >= 120 || share_k || dgemm_tri_streamk_applies(p)) return launch_t<128>(p, s);
     if (tilesM * ((p.N + 63) / 64) >= 120) return launch_t<64>(p, s);
     if (tilesM * ((p.N + 31) / 32) >= 120) return launch_t<32>(p, s);
     return launch_t<16>(p, s);

@@ -965,34 +965,6 @@ sgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
 }
 
-// Triangular updates (SYRK, HERK): only the 128 x 128 tiles that touch the triangle are enumerated, column of tiles by
-// column of tiles.  Rows of tile column tn that take part: [lo, hi).
-__host__ __device__ inline void tri_column_rows(int tri, unsigned tilesM, unsigned tn, unsigned& lo, unsigned& hi)
-{
-    const int sh = (tri >> 2) & 1, kind = tri & 3;
-    const size_t n0 = (size_t)tn * 128;
-    lo = 0; hi = tilesM;
-    if (kind == TRI_LOWER) {            // tile row tm takes part when its last row, ((tm*128 + 127) >> sh), reaches column n0
-        const size_t first_row = n0 << sh;                       // first stored row that belongs to triangle row n0
-        lo = (unsigned)std::min<size_t>(tilesM, first_row >= 127 ? (first_row - 127 + 127) / 128 : 0);
-    } else if (kind == TRI_UPPER) {     // ... when its first row, ((tm*128) >> sh), is not beyond column n0 + 127
-        const size_t last_row = ((n0 + 128) << sh) - 1;          // last stored row that belongs to triangle row n0 + 127
-        hi = (unsigned)std::min<size_t>(tilesM, last_row / 128 + 1);
-    }
-}
-// tile number t of that enumeration -> (tm, tn)
-__device__ __forceinline__ void tri_tile_coords(int tri, unsigned t, unsigned tilesM, unsigned tilesN, unsigned& tm, unsigned& tn)
-{
-    unsigned before = 0;
-    for (unsigned c = 0; c < tilesN; c++) {
-        unsigned lo, hi;
-        tri_column_rows(tri, tilesM, c, lo, hi);
-        if (t < before + (hi - lo)) { tn = c; tm = lo + (t - before); return; }
-        before += hi - lo;
-    }
-    tn = tilesN - 1; tm = tilesM - 1;           // not reached: t is below the number of tiles the host counted
-}
-
 // ---------------------------------------------------------------------------------------------
 // Stream-K with the 16 x 8 register tile on eight-warp CTAs, one CTA per SM, both operands M/N-contiguous.
 //
@@ -1182,19 +1154,6 @@ sgemm_nt_16x8w_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __
         __syncthreads();                                      // the exchange buffer and s_ticket are reused by the next segment
         clear();
     }
-}
-
-// Number of 128 x 128 tiles of an M x N matrix that touch the triangle `tri` (all of them for TRI_FULL).
-size_t tri_tile_count(int tri, size_t tilesM, size_t tilesN)
-{
-    if ((tri & 3) == TRI_FULL) return tilesM * tilesN;
-    size_t n = 0;
-    for (size_t c = 0; c < tilesN; c++) {
-        unsigned lo, hi;
-        tri_column_rows(tri, (unsigned)tilesM, (unsigned)c, lo, hi);
-        n += hi - lo;
-    }
-    return n;
 }
 
 template <bool TRI>

@@ -267,6 +267,57 @@ def test_triangular_eight_warp_stream_k_through_ssyrk_and_cherk(lib, uplo):
     assert lib.device_fault() == 0
 
 
+@pytest.mark.parametrize("uplo", [Lower, Upper])
+def test_triangular_dgemm_stream_k_through_dsyrk_and_zherk(lib, uplo):
+    """Double-precision rank-k updates whose tiles in the triangle would fill the last wave of CTAs only partly: all of them
+    go through the FP64 stream-K kernel in equal shares.  Exact on integer inputs, the other triangle untouched."""
+    n, k = 1100, 704                           # 9 x 9 tiles, 45 of them in the triangle, 44 K slabs
+    g = oracle.rng(8070 + uplo, 0)
+    A = g.integers(-3, 4, (n, k)).astype(np.float64)
+    tri, other = (np.tril, np.triu_indices(n, 1)) if uplo == Lower else (np.triu, np.tril_indices(n, -1))
+    C = tri(g.integers(-3, 4, (n, n))).astype(np.float64)
+    Cb = np.asfortranarray(C.copy())
+    Cb[other] = np.nan                                                               # the other triangle must not be touched
+    dA, dC = dev(np.asfortranarray(A).ravel(order="F").copy()), dev(Cb.ravel(order="F").copy())
+    st = lib.clblasDsyrk(ColumnMajor, uplo, NoTrans, n, k, 2.0, dA, 0, n, 3.0, dC, 0, n)
+    torch.cuda.synchronize()
+    assert st == lib.clblasSuccess and lib.last_gemm_variant() == "dgemm_mma_tma<N,T,128>+tri+streamk", lib.last_gemm_variant()
+    got = dC.cpu().numpy().reshape(n, n).T
+    want = 2.0 * (A @ A.T) + 3.0 * C
+    assert np.array_equal(tri(got), tri(want))
+    assert np.all(np.isnan(got[other]))
+    # the same call twice gives the same bits (real-valued inputs, fixed reduction order)
+    Ar = g.standard_normal((n, k))
+    dA = dev(np.asfortranarray(Ar).ravel(order="F").copy())
+    outs = []
+    for _ in range(2):
+        dC = dev(np.zeros(n * n))
+        assert lib.clblasDsyrk(ColumnMajor, uplo, NoTrans, n, k, 1.0, dA, 0, n, 0.0, dC, 0, n) == lib.clblasSuccess
+        outs.append(dC)
+    torch.cuda.synchronize()
+    assert lib.last_gemm_variant().endswith("+tri+streamk") and torch.equal(outs[0], outs[1])
+
+    # ZHERK: complex128; the real form pairs the rows of the triangle
+    n, k = 896, 512
+    Az = g.integers(-3, 4, (n, k)) + 1j * g.integers(-3, 4, (n, k))
+    Cz = tri(g.integers(-3, 4, (n, n)) + 1j * g.integers(-3, 4, (n, n)))
+    Cz[np.diag_indices(n)] = Cz[np.diag_indices(n)].real
+    store = np.asfortranarray(Cz.astype(np.complex128))
+    other = np.triu_indices(n, 1) if uplo == Lower else np.tril_indices(n, -1)
+    store[other] = np.nan + 1j * np.nan
+    dA = dev(np.asfortranarray(Az.astype(np.complex128)).ravel(order="F").copy().view(np.float64))
+    dC = dev(store.ravel(order="F").copy().view(np.float64))
+    st = lib.clblasZherk(ColumnMajor, uplo, NoTrans, n, k, 2.0, dA, 0, n, -1.0, dC, 0, n)
+    torch.cuda.synchronize()
+    assert st == lib.clblasSuccess and lib.last_gemm_variant().endswith("+tri+streamk"), lib.last_gemm_variant()
+    got = dC.cpu().numpy().view(np.complex128).reshape(n, n).T
+    want = 2.0 * (Az @ Az.conj().T) - Cz
+    keep = np.tril_indices(n) if uplo == Lower else np.triu_indices(n)
+    assert np.array_equal(got[keep], want[keep])
+    assert np.all(np.isnan(got[other].real))
+    assert lib.device_fault() == 0
+
+
 @pytest.mark.parametrize("nq", [2, 3, 7])
 def test_gemm_over_several_queues_of_one_device(lib, nq):
     """numCommandQueues > 1: one stripe of N per queue, every queue's event recorded when its stripe is done."""
