@@ -1339,6 +1339,13 @@ cudaError_t launch_sgemm_ffma_tma(const GemmProblem<float>& p, cudaStream_t s, i
     if (p.tri == TRI_FULL && min_bn < 128 && p.K >= 256 && tiles128 >= 64 && tiles128 < (size_t)sm_count() * 12) {
         Plan plan = choose_plan_8x8(tiles128, p.K, (size_t)sm_count(), p.ta ? 1 : 2, may_split);
         if (tiles128 < 96 && plan.kind != 2) plan = Plan{0, 1};      // below 96 tiles the 128 x 64 tiles further down beat a split
+        // Where the rounds would come out uneven, N/T products with 24 to 35 K slabs are better off with the eight-warp
+        // 16 x 8 stream-K kernel than with a split (2048 x 2048 x 1024: 47.4 against 44.1 TFLOP/s, 2560 x 2560 x 1024 49.9 / 45.5,
+        // 2048 x 2048 x 768 43.9 / 43.1); where one CTA per tile fills its rounds it is not (3072 x 3072 x 1024: 51.4 / 55.3).
+        if (plan.kind != 0 && !p.ta && p.tb && share_k && c_vec && (p.K + BK - 1) / BK >= 24) {
+            const cudaError_t e = launch_nt_16x8w_streamk<false>(p, s);
+            if (e != cudaErrorNotSupported) return e;
+        }
         if (plan.kind == 2) {
             const cudaError_t e = launch_streamk_any(p, s);
             if (e != cudaErrorNotSupported) return e;

@@ -113,34 +113,34 @@ def test_sgemm_16x8_register_tile_kernel_is_exact(lib):
 
 
 def test_sgemm_split_k_against_wave_quantisation_is_exact(lib):
-    """784 tiles of 128 x 128 are 2.65 rounds of CTAs and K = 768 is short: the dispatcher cuts K in three so that the rounds
+    """784 tiles of 128 x 128 are 2.65 rounds of CTAs and K = 704 is short: the dispatcher cuts K in two so that the rounds
     come out even.  Same bits as the unsplit product (integer inputs), the same call twice gives the same bits (fixed
     reduction order)."""
-    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3584, 3584, 768, seed=8012)
-    assert v == "sgemm_ffma_tma<N,T,128,3,2>+splitk3", v
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3584, 3584, 704, seed=8012)
+    assert v == "sgemm_ffma_tma<N,T,128,3,2>+splitk2", v
     import oracle as _o
     g = _o.rng(8013, 0)
-    n, k = 3584, 768
+    n, k = 3584, 704
     A, B = (torch.from_numpy(g.standard_normal(n * k).astype(np.float32)).cuda() for _ in range(2))
     C1, C2 = torch.zeros(n * n, device="cuda"), torch.zeros(n * n, device="cuda")
     for C in (C1, C2):
         assert lib.clblasSgemm(ColumnMajor, NoTrans, Trans, n, n, k, 1.0, A, 0, n, B, 0, n, 0.0, C, 0, n) == lib.clblasSuccess
     torch.cuda.synchronize()
-    assert lib.last_gemm_variant().endswith("+splitk3") and torch.equal(C1, C2)
+    assert lib.last_gemm_variant().endswith("+splitk2") and torch.equal(C1, C2)
 
 
 def test_sgemm_stream_k_is_exact_and_deterministic(lib):
     """Products of about one round of CTAs go to the stream-K kernel (every CTA the same number of K slabs, partial
     tiles added in slot order by the CTA that finishes a tile last): exact on integer inputs, ragged edges included,
     for M-contiguous and K-contiguous A, and bit-identical when repeated."""
-    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1408, 1408, 1056, seed=8040)
+    v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1408, 1408, 704, seed=8040)
     assert v == "sgemm_streamk<N,T>", v
     v = _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 1397, 1401, 1100, alpha=-1.0, beta=0.0, pad=(3, 3, 0), seed=8041)      # 11 x 11 tiles
     assert v == "sgemm_streamk<N,T>", v
     v = _exact_gemm(lib, "s", ColumnMajor, Trans, NoTrans, 1408, 1408, 992, seed=8042)           # K-contiguous A: one CTA per SM
     assert v == "sgemm_streamk<T,N>", v
     g = oracle.rng(8043, 0)
-    n, k = 1408, 1056
+    n, k = 1408, 704
     A, B = (torch.from_numpy(g.standard_normal(n * k).astype(np.float32)).cuda() for _ in range(2))
     C1, C2 = torch.zeros(n * n, device="cuda"), torch.zeros(n * n, device="cuda")
     for C in (C1, C2):
@@ -162,6 +162,7 @@ def test_sgemm_eight_warp_16x8_stream_k_is_exact_and_deterministic(lib):
     assert _exact_gemm(lib, "s", RowMajor, Trans, NoTrans, 2200, 2056, 1153, seed=8052) == name
     assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 300, 200, 8000, seed=8053) == name             # six tiles, 250 slabs
     assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 3584, 3584, 1536, seed=8054) == name           # 784 tiles
+    assert _exact_gemm(lib, "s", ColumnMajor, NoTrans, Trans, 2048, 2048, 1024, seed=8057) == name           # 32 slabs, uneven rounds
     g = oracle.rng(8055, 0)
     n, k = 2048, 1536
     A, B = (torch.from_numpy(g.standard_normal(n * k).astype(np.float32)).cuda() for _ in range(2))
