@@ -975,6 +975,8 @@ sgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
 // 0-1 and receives group 1's sums for them, group 1 keeps row groups 2-3 -- and each finishes its half: straight to C
 // when the segment is the whole tile, else to the CTA's slot of the workspace, ticket, and the CTA that draws the last
 // ticket adds the slots in slot order (a fixed order) and writes C.  Nobody waits for anybody.
+// TRI: a triangular update (SYRK, HERK): the tiles are those that touch the triangle, in the order of tri_tile_coords, and
+// tiles on the diagonal mask their stores.
 constexpr int T16W_THREADS = 256;
 constexpr int T16W_STAGES = 4;
 constexpr int T16W_RED_BYTES = 64 * 128 * 8;         // the halves the two groups hand each other
