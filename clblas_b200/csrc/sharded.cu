@@ -15,8 +15,7 @@
 //    reference's own K split, src/library/blas/specialCases/GemmSpecialCases.cpp:127-191); with
 //    transA = T a panel is a block of rows of C.  For TRSM the blocked solve itself waits for the panels
 //    (TrsmPanelGate): each step needs only the columns of A up to where the substitution has got.
-//    The first panel is small, so little of the broadcast is exposed (GEMM: later panels grow; TRSM:
-//    equal panels of 2048 columns).
+//    The first panel is small, so little of the broadcast is exposed; later panels grow.
 //  * one process, several queues -- gemm_multi_queue, reached from clblasSgemm / clblasDgemm with
 //    numCommandQueues > 1: stripes of N as in the reference; a queue on another device gets copies of
 //    A and of its stripes of B and C (peer copies), computes there and copies its stripe of C back.
@@ -139,15 +138,25 @@ std::vector<size_t> growing_panels(size_t cols, size_t min_cols, size_t max_pane
     return b;
 }
 
-// Panels of the triangular matrix of a sharded solve: equal panels of 2048 columns (CLBLAS_B200_TRSM_PANEL_COLS changes
-// the width for measurements), wider only to keep their number at 32.
-std::vector<size_t> trsm_panel_bounds(size_t n)
+// Panels of the triangular matrix of a sharded solve: a first panel of 1/32 of the columns (at least 128), each next one
+// four times as wide, small panels where the substitution starts (`ascending`: at the first column).  The time the solve
+// needs to reach column c grows like c^2 while the panels arrive at a constant rate, so what is exposed is the first panel
+// and the waits for the next ones while the solve is still faster than the link; every broadcast costs about 45 us of its
+// own.  Measured, order 8192, time per call above the rank's solve alone: this plan (256, 1024, 4096, 2816 columns) +0.55 ms
+// on 2 GPUs (8192 columns per rank) and +0.66 ms on 8 (2048 per rank); equal panels of 2048 columns +0.67 / +0.83, of 512
+// columns +1.22 on 2 GPUs, one broadcast of everything +0.85.
+std::vector<size_t> trsm_panel_bounds(size_t n, bool ascending)
 {
-    static const size_t w0 = [] { const char* e = getenv("CLBLAS_B200_TRSM_PANEL_COLS"); const long v = e ? atol(e) : 0; return v >= (long)kAlign ? (size_t)v / kAlign * kAlign : 16 * kAlign; }();
-    size_t w = w0;
-    while ((n + w - 1) / w > 32) w *= 2;
-    std::vector<size_t> b{0};
-    while (b.back() < n) b.push_back(std::min(n, b.back() + w));
+    std::vector<size_t> b = growing_panels(n, kAlign, 10);
+    if (!ascending) {           // mirror the plan: small panels at the end of the matrix
+        std::vector<size_t> m(b.size());
+        for (size_t i = 0; i < b.size(); i++) {
+            const size_t v = n - b[b.size() - 1 - i];
+            m[i] = (i == 0) ? 0 : (i + 1 == b.size() ? n : (v + kAlign - 1) / kAlign * kAlign);
+        }
+        m.erase(std::unique(m.begin(), m.end()), m.end());
+        b = m;
+    }
     return b;
 }
 
@@ -233,12 +242,7 @@ cudaError_t trsm_sharded_colmajor(ShardComm* c, int root, bool right, bool lower
     // order -- a transposed A -- in which case that step waits for them; by then they have long arrived,
     // because the solve takes far longer than the broadcast).
     const bool ascending = ((lower != trans) != right);
-    // Equal panels of 2048 columns, wider only to keep their number at 32.  The time the solve needs to reach column c
-    // grows like c^2 while the panels arrive at a constant rate, so what is exposed is the first panel and whatever
-    // the solve has to wait for the second; every further broadcast costs about 45 us of its own.  Measured on 2 GPUs,
-    // order 8192 with 8192 columns per rank, time per call above the 17.18 ms of the solve alone: panels of 512
-    // columns +1.22 ms, 1024 +0.81, 2048 +0.67, 4096 +0.66, one broadcast of everything +0.85.
-    const std::vector<size_t> b = trsm_panel_bounds(n);
+    const std::vector<size_t> b = trsm_panel_bounds(n, ascending);
     const size_t np = b.size() - 1;
 
     cudaError_t e;
@@ -447,9 +451,10 @@ clblasStatus clblasB200CommInfo(clblasB200Comm comm, int* nranks, int* rank)
 clblasStatus clblasB200PanelPlan(size_t columns, size_t min_columns, unsigned max_panels, size_t* bounds, unsigned* count)
 {
     if (bounds == nullptr || count == nullptr || max_panels == 0) return clblasInvalidValue;
-    // min_columns == 0: the plan of the sharded triangular solves (equal panels); otherwise that of the sharded products
-    if (min_columns == 0 && max_panels < 32) return clblasInvalidValue;
-    const std::vector<size_t> b = min_columns == 0 ? trsm_panel_bounds(columns) : growing_panels(columns, min_columns, max_panels);
+    // min_columns 0 / 1: the plan of the sharded triangular solves whose substitution starts at the first / at the last
+    // column (ten panels at most); otherwise that of the sharded products
+    if (min_columns <= 1 && max_panels < 10) return clblasInvalidValue;
+    const std::vector<size_t> b = min_columns <= 1 ? trsm_panel_bounds(columns, min_columns == 0) : growing_panels(columns, min_columns, max_panels);
     for (size_t i = 0; i < b.size(); i++) bounds[i] = b[i];
     *count = (unsigned)(b.size() - 1);
     return clblasSuccess;

@@ -46,11 +46,11 @@ def gemm_panels(prec: str, transA: int, M: int, n_local: int, K: int, sm_count: 
 
 
 def trsm_panels(uplo: int, transA: int, n: int, right: bool = False) -> List[Tuple[int, int]]:
-    """Column ranges of the stored triangular matrix in broadcast order: equal panels, first the one where the
+    """Column ranges of the stored triangular matrix in broadcast order: growing panels, first the small one where the
     substitution starts (the plan of trsm_sharded_colmajor)."""
-    b = cb.panel_plan(n, 0, 32)
     lower, trans = uplo == cb.clblasLower, transA != cb.clblasNoTrans
     ascending = ((lower != trans) != right)
+    b = cb.panel_plan(n, 0 if ascending else 1, 10)
     plan = [(b[i], b[i + 1]) for i in range(len(b) - 1)]
     return plan if ascending else plan[::-1]
 

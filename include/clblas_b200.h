@@ -407,8 +407,8 @@ clblasStatus clblasB200DgemmSharded(
 /*      clblasB200{S,D}trsmSharded: the argument list of clblasStrsm / clblasDtrsm on one rank's shard of the
  *      right-hand sides: the dimension of B that is not the order of A (N for Left, M for Right) counts what
  *      this rank owns (zero is legal) and B points at the rank's own block.  A is the whole triangular matrix
- *      on the root and a buffer of the same extent elsewhere; it is broadcast in column panels of 2048 columns
- *      (wider beyond 65536) in the order the substitution reaches them, and each step of the blocked solve waits
+ *      on the root and a buffer of the same extent elsewhere; it is broadcast in column panels (a first one of 1/32 of the
+ *      columns where the substitution starts, each next one four times as wide) in the order the substitution reaches them, and each step of the blocked solve waits
  *      only for the panels it reads, so the solve starts after the first panel and the rest of the transfer is
  *      hidden behind it.  No other exchange takes place: right-hand sides are independent
  *      (the reference's split, src/library/blas/generic/solution_seq_make.c:785-866). */
@@ -434,8 +434,9 @@ clblasStatus clblasB200DtrsmSharded(
 
 /*      The panel plans the sharded calls use for a matrix of `columns` stored columns.  min_columns > 0 (products):
  *      a first panel of about 1/32 of the columns (at least min_columns), each next one four times as wide,
- *      boundaries multiples of 128, at most max_panels panels.  min_columns == 0 (triangular solves; max_panels >= 32):
- *      equal panels of 2048 columns, wider only to keep their number at 32.  Writes count+1 boundaries (bounds needs
+ *      boundaries multiples of 128, at most max_panels panels.  min_columns 0 / 1 (triangular solves whose substitution
+ *      starts at the first / at the last column; max_panels >= 10): the same growth from a first panel of at least 128
+ *      columns, the small panels at the end the substitution starts from.  Writes count+1 boundaries (bounds needs
  *      max_panels+1 entries).  Pure host arithmetic, exported for the tests. */
 clblasStatus clblasB200PanelPlan(size_t columns, size_t min_columns, unsigned max_panels, size_t* bounds, unsigned* count);
 

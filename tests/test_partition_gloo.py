@@ -36,9 +36,6 @@ def _oracle_trsm(order, side, uplo, transA, diag, M, N, alpha, A, offA, lda, B, 
 
 def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
-    # the library's panel width for the sharded solves (default 2048 columns) is read once per process: narrow panels here,
-    # so that a matrix the CPU checker solves quickly still spans several
-    os.environ["CLBLAS_B200_TRSM_PANEL_COLS"] = "512"
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from clblas_b200 import partition
@@ -77,7 +74,7 @@ def _worker(rank, world, port, q):
         # several broadcast panels, both substitution directions (panels sent from the first or from the last column)
         from oracle import Upper
         for name, uplo in (("trsm_panels_lower", Lower), ("trsm_panels_upper", Upper)):
-            n2 = 1300                  # three panels of 512 columns (the width set at the top of this worker)
+            n2 = 1300                  # three panels: 128, 512 and 660 columns
             T2 = np.tril(g.uniform(-1, 1, (n2, n2)) / n2) + np.diag(g.uniform(1, 2, n2))
             T2 = T2 if uplo == Lower else T2.T.copy()
             B2 = g.standard_normal((n2, nrhs))
