@@ -229,7 +229,7 @@ template <bool TA, bool TB, bool TRI>
 __global__ void __launch_bounds__(THREADS, 1)
 dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      double* __restrict__ C, size_t ldc, size_t M, size_t N, size_t K, double alpha, double beta,
-                     unsigned tilesM, unsigned tilesN, unsigned tile0, unsigned units, unsigned upc, unsigned maxc,
+                     unsigned tilesM, unsigned tilesN, unsigned tile0, unsigned units, unsigned upc,
                      double* __restrict__ ws, unsigned* __restrict__ counters, int tri)
 {
     auto coords = [&](unsigned tile, unsigned& tm, unsigned& tn) {
@@ -369,10 +369,11 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         if (seg_first == 0 && seg_last == nk - 1) {
             epilogue(m0, n0);
         } else {
+            // Two slots per CTA: a partial tile is either the CTA's first segment (slot 0) or, begun at a tile boundary and
+            // cut short by the end of the share, its last (slot 1); whole tiles in between need none.
             const unsigned first_cta = (t * nk) / upc;
-            const unsigned idx = blockIdx.x - first_cta;
             const unsigned count = ((t + 1) * nk - 1) / upc - first_cta + 1;
-            double* slot = ws + ((size_t)t * maxc + idx) * (size_t)(BM * BN);
+            double* slot = ws + ((size_t)blockIdx.x * 2 + (u == u0 ? 0 : 1)) * (size_t)(BM * BN);
 #pragma unroll
             for (int mi = 0; mi < 8; mi++)
 #pragma unroll
@@ -387,13 +388,14 @@ dgemm_streamk_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
                 __threadfence();
                 // slot by slot (the 64 loads of a slot are independent and overlap; a loop over the slots inside each
                 // element would be a chain of dependent L2 latencies), always in slot order
-                const double* base = ws + (size_t)t * maxc * (size_t)(BM * BN) + ctid;
+
 #pragma unroll
                 for (int mi = 0; mi < 8; mi++)
 #pragma unroll
                     for (int ni = 0; ni < NI; ni++) acc[mi][ni][0] = acc[mi][ni][1] = 0.0;
-                for (unsigned c = 0; c < count; c++) {
-                    const double* sl = base + (size_t)c * (BM * BN);
+                for (unsigned c = first_cta; c < first_cta + count; c++) {
+                    // CTA c's part of this tile is its first segment if its share starts inside the tile
+                    const double* sl = ws + ((size_t)c * 2 + (c * upc >= t * nk ? 0 : 1)) * (size_t)(BM * BN) + ctid;
                     double v[8][NI][2];
 #pragma unroll
                     for (int mi = 0; mi < 8; mi++)
@@ -486,9 +488,8 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
         const size_t T = tri_tile_count(p.tri, tilesM, tilesN), S = (size_t)sm_count(), nk = (p.K + BK - 1) / BK;
         const size_t units = T * nk;
         const size_t ctas = std::max<size_t>(1, std::min<size_t>(S, units / SK_MIN_SLABS));
-        const size_t upc = (units + ctas - 1) / ctas;
-        const size_t maxc = (nk + upc - 1) / upc + 1;
-        const size_t ws_doubles = T * maxc * (size_t)(BM * 128);
+        const size_t upc = (units + ctas - 1) / ctas, grid = (units + upc - 1) / upc;
+        const size_t ws_doubles = grid * 2 * (size_t)(BM * 128);               // two partial-tile slots per CTA
         double* ws = nullptr;
         cudaError_t e = ws_alloc(reinterpret_cast<void**>(&ws), ws_doubles * sizeof(double) + T * sizeof(unsigned) + 256, s);
         if (e == cudaSuccess) {
@@ -497,9 +498,9 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
             if (e == cudaSuccess) e = prepare_streamk<TA, TB, true>();
             if (e == cudaSuccess) {
                 set_last_variant(variant_name(TA, TB, BN, true, true));
-                e = launch_pdl(dgemm_streamk_kernel<TA, TB, true>, dim3((unsigned)((units + upc - 1) / upc)), dim3(THREADS), smem_bytes(128), s,
+                e = launch_pdl(dgemm_streamk_kernel<TA, TB, true>, dim3((unsigned)grid), dim3(THREADS), smem_bytes(128), s,
                                mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
-                               0u, (unsigned)units, (unsigned)upc, (unsigned)maxc, ws, counters, p.tri);
+                               0u, (unsigned)units, (unsigned)upc, ws, counters, p.tri);
                 count_launch();
             }
             const cudaError_t e2 = ws_free(ws, s);
@@ -519,9 +520,8 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
             p.C != p.A && p.C != p.B && getenv("CLBLAS_B200_NO_STREAMK") == nullptr) {
             const size_t units = R * nk;
             const size_t ctas = std::max<size_t>(1, std::min<size_t>(S, units / SK_MIN_SLABS));
-            const size_t upc = (units + ctas - 1) / ctas;
-            const size_t maxc = (nk + upc - 1) / upc + 1;
-            const size_t ws_doubles = R * maxc * (size_t)(BM * 128);
+            const size_t upc = (units + ctas - 1) / ctas, grid = (units + upc - 1) / upc;
+            const size_t ws_doubles = grid * 2 * (size_t)(BM * 128);               // two partial-tile slots per CTA
             double* ws = nullptr;
             cudaError_t e = ws_alloc(reinterpret_cast<void**>(&ws), ws_doubles * sizeof(double) + R * sizeof(unsigned) + 256, s);
             if (e == cudaSuccess) {
@@ -537,9 +537,9 @@ cudaError_t launch(const GemmProblem<double>& p, cudaStream_t s)
                         count_launch();
                     }
                     if (e == cudaSuccess) {
-                        e = launch_pdl(dgemm_streamk_kernel<TA, TB, false>, dim3((unsigned)((units + upc - 1) / upc)), dim3(THREADS), smem_bytes(128), s,
+                        e = launch_pdl(dgemm_streamk_kernel<TA, TB, false>, dim3((unsigned)grid), dim3(THREADS), smem_bytes(128), s,
                                        mapA, mapB, p.C, p.ldc, p.M, p.N, p.K, p.alpha, p.beta, (unsigned)tilesM, (unsigned)tilesN,
-                                       (unsigned)main_tiles, (unsigned)units, (unsigned)upc, (unsigned)maxc, ws, counters, 0);
+                                       (unsigned)main_tiles, (unsigned)units, (unsigned)upc, ws, counters, 0);
                         count_launch();
                     }
                 }
